@@ -1,0 +1,163 @@
+/*
+ * swc_b200.h -- C-ABI kernel table: B200 (sm_100a) replacements for the operator
+ * kernels SWCompiler's code generator emits calls to.
+ *
+ * The reference has no FFI; its boundary is textual.  Codegen prints
+ * `#include "utils/kernels.h"` (src/codegen/Codegen.cpp:260) and, per op node,
+ * one call `<kernel>_<dtype flag>(...)` (Codegen.cpp:1171-2494 for CPU,
+ * :2602-2674 for its CUDA sketch).  Every entry point below keeps the name and
+ * the argument order of the function it replaces, with two changes: a context
+ * comes first and an int status comes back (0 = ok), because the reference's
+ * void calls have no way to report an error.
+ *
+ * Conventions
+ *   - every tensor pointer is a DEVICE pointer into memory the caller owns;
+ *     shape/attribute arrays (`const size_t*`) are HOST arrays, read during the
+ *     call, exactly as the emitted program passes them (Codegen.cpp:1761-1782);
+ *   - calls are asynchronous on the context's stream; swcb200_sync waits;
+ *   - a context belongs to one host thread at a time (the emitted main() is
+ *     single-threaded, Codegen.cpp:1037-1058);
+ *   - nothing here falls back to the CPU: without a usable device every call
+ *     returns SWCB200_ERR_NO_DEVICE or SWCB200_ERR_CUDA.
+ */
+#ifndef SWC_B200_H_
+#define SWC_B200_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef struct swcb200_ctx swcb200_ctx;
+
+enum swcb200_status {
+    SWCB200_OK = 0,
+    SWCB200_ERR_BAD_ARG = 1,     /* null pointer, negative size, unknown enum            */
+    SWCB200_ERR_BAD_SHAPE = 2,   /* shapes inconsistent with each other                  */
+    SWCB200_ERR_MISALIGNED = 3,  /* pointer / leading dimension breaks a stated alignment */
+    SWCB200_ERR_UNSUPPORTED = 4, /* valid in the reference's signature, not built here   */
+    SWCB200_ERR_CUDA = 5,        /* a CUDA runtime/driver call failed; see last_error    */
+    SWCB200_ERR_NCCL = 6,        /* NCCL missing or a collective failed                  */
+    SWCB200_ERR_TIMEOUT = 7,     /* a bounded device- or host-side wait gave up          */
+    SWCB200_ERR_NO_DEVICE = 8,   /* no CUDA device / not an sm_100 device                */
+    SWCB200_ERR_TOO_LARGE = 9    /* exceeds a documented size limit                      */
+};
+
+/* How the fp32 entry points matrixMatrixMul_f and conv2d_f compute. */
+enum swcb200_precision {
+    SWCB200_STRICT_F32 = 0, /* fp32 products and sums, one rounding each, in the reference's order:
+                               results equal the reference's generated C bit for bit              */
+    SWCB200_TC_BF16 = 1     /* operands rounded to bf16, tcgen05 tensor cores, fp32 accumulation  */
+};
+
+enum swcb200_dtype { SWCB200_F32 = 0, SWCB200_BF16 = 1, SWCB200_I32 = 2 };
+enum swcb200_act { SWCB200_ACT_NONE = 0, SWCB200_ACT_RELU = 1, SWCB200_ACT_TANH = 2 };
+
+/* ------------------------------------------------------------------ context */
+
+/* Creates a context on `device` with its own stream.  Replaces the emitted
+ * environment set-up (cublasCreate + cudaStreamCreate, Codegen.cpp:142-173). */
+int swcb200_init(int device, int precision, swcb200_ctx **out);
+/* Same, but work is issued on `cuda_stream` (a cudaStream_t; NULL = the legacy default stream),
+ * which the caller keeps owning. */
+int swcb200_init_on_stream(int device, int precision, void *cuda_stream, swcb200_ctx **out);
+int swcb200_destroy(swcb200_ctx *ctx);
+int swcb200_sync(swcb200_ctx *ctx);
+int swcb200_set_precision(swcb200_ctx *ctx, int precision);
+void *swcb200_stream(swcb200_ctx *ctx);
+const char *swcb200_status_string(int status);
+const char *swcb200_last_error(swcb200_ctx *ctx);
+/* Kernel launches issued through this context since it was created. */
+uint64_t swcb200_launch_count(swcb200_ctx *ctx);
+/* Library version, e.g. 100 = 0.1.0. */
+int swcb200_version(void);
+
+/* ----------------------------------------------- dense ops (row-major, 2-D) */
+
+/* C[m,n] = A[m,k] . B[k,n].  Replaces matrixMatrixMul_f (kernels.h:41-56; call site
+ * Codegen.cpp:1334-1337) and the cublasSgemm sketch (Codegen.cpp:2610-2632). */
+int swcb200_matrixMatrixMul_f(swcb200_ctx *ctx, int m, int n, int k, const float *a, int lda,
+                              const float *b, int ldb, float *c, int ldc);
+/* dest[r,:] = batch[r,:] + slice[:].  Replaces batchedadd_f (kernels.h:542-552;
+ * Codegen.cpp:1501-1516) and batchedadd_float (cuda_kernels.h:29-37). */
+int swcb200_batchedadd_f(swcb200_ctx *ctx, float *dest, const float *batch, const float *slice,
+                         size_t numSlice, size_t sliceSize);
+/* b = 1 - 2/(exp(2a)+1).  Replaces matrixTanh_f (kernels.h:58-64; Codegen.cpp:2286-2296)
+ * and matrixTanh_float (cuda_kernels.h:22-27). */
+int swcb200_matrixTanh_f(swcb200_ctx *ctx, int m, int n, const float *a, int lda, float *b,
+                         int ldb);
+/* Row softmax.  Replaces matrixSoftmax_f (kernels.h:88-103; Codegen.cpp:2349-2354)
+ * and matrixSoftmax_float (cuda_kernels.h:4-20). */
+int swcb200_matrixSoftmax_f(swcb200_ctx *ctx, int m, int n, const float *a, int lda, float *b,
+                            int ldb);
+/* Top-k column indices per row, ties to the higher index.  Replaces argMax_i
+ * (kernels.h:601-613; Codegen.cpp:2372-2386).  top_k <= n. */
+int swcb200_argMax_i(swcb200_ctx *ctx, const float *input, int *idx, int m, int n, int top_k);
+
+/* ------------------------------------------------------- flat elementwise */
+
+/* dest = src > 0 ? src : 0.  Replaces relu_f (kernels.h:575-580; Codegen.cpp:2133-2135). */
+int swcb200_relu_f(swcb200_ctx *ctx, const float *src, float *dest, size_t size);
+/* c = a + b.  Replaces vecAdd_f (kernels.h:592-596; Codegen.cpp:1606-1610). */
+int swcb200_vecAdd_f(swcb200_ctx *ctx, int size, const float *a, const float *b, float *c);
+
+/* ------------------------------------------------------------- NHWC ops */
+
+/* Replaces conv2d_f (kernels.h:177-243; Codegen.cpp:1761-1782).  dims arrays have 4 entries
+ * (NHWC; filter [oC,kh,kw,iC]); kernels/strides 2; pads 4 of which [0]=top and [1]=left are
+ * read, as in the reference.  group must be 1 (the reference's own group > 1 indexing reads
+ * past its filter, kernels.h:208-209). */
+int swcb200_conv2d_f(swcb200_ctx *ctx, float *output, const float *input, const float *filter,
+                     const float *bias, const size_t *odims, const size_t *idims,
+                     const size_t *fdims, const size_t *bdims, const size_t *kernels,
+                     const size_t *strides, const size_t *pads, size_t group);
+/* Replaces maxpool_f (kernels.h:323-377; Codegen.cpp:2020-2037). */
+int swcb200_maxpool_f(swcb200_ctx *ctx, const float *input, float *output, const size_t *idims,
+                      const size_t *odims, const size_t *kernels, const size_t *strides,
+                      const size_t *pads);
+/* Replaces avgpool_f (kernels.h:444-493): divides by the full window. */
+int swcb200_avgpool_f(swcb200_ctx *ctx, const float *input, float *output, const size_t *idims,
+                      const size_t *odims, const size_t *kernels, const size_t *strides,
+                      const size_t *pads);
+/* Replaces batchnormalization_f (kernels.h:496-517; Codegen.cpp:1907-1915). */
+int swcb200_batchnormalization_f(swcb200_ctx *ctx, float *output, const float *input,
+                                 const float *mean, const float *var, const float *scale,
+                                 const float *bias, const size_t *idims, float epsilon);
+/* Replace transpose2d_f / transpose4d_f (kernels.h:519-540): out[idx[shuffle]] = in[idx]. */
+int swcb200_transpose2d_f(swcb200_ctx *ctx, const float *input, float *output,
+                          const size_t *idims, const size_t *odims, const size_t *shuffle);
+int swcb200_transpose4d_f(swcb200_ctx *ctx, const float *input, float *output,
+                          const size_t *idims, const size_t *odims, const size_t *shuffle);
+
+/* ------------------------------------- tensor-core path with bf16 storage
+ * The graph IR has no 16-bit type (src/common.h:17), so bf16 is a storage mode of the backend:
+ * the generator keeps activations and packed weights as bf16 in its arena and calls these
+ * instead of the fp32 entry points.  One call covers the chain the lowering pass produces for
+ * an FC layer, MatrixMatrixMul -> MatrixVectorAdd -> activation
+ * (src/op/dlOp/dlOpEinsum.cpp:154-237). */
+
+int swcb200_cast_f32_to_bf16(swcb200_ctx *ctx, const float *src, void *dst_bf16, size_t count);
+int swcb200_cast_bf16_to_f32(swcb200_ctx *ctx, const void *src_bf16, float *dst, size_t count);
+/* W[k,n] row-major fp32 (the reference's weight layout) -> Wp[n,k] row-major bf16, the K-major
+ * operand layout the tensor-core kernel reads.  Done once per weight, at load time. */
+int swcb200_pack_weight_bf16(swcb200_ctx *ctx, const float *w, int k, int n, int ldb,
+                             void *wp_bf16);
+/* C[m,n] = act(A[m,k] . Wp[n,k]^T + bias[n]).  A, Wp bf16; bias fp32 or NULL; C fp32 or bf16
+ * (c_dtype).  lda, ldw multiples of 8 elements and A, Wp 16-byte aligned (TMA rule); C may have
+ * any pitch (128-bit stores are used when C and ldc*elem are 16-byte aligned).  fp32 accumulation
+ * in tensor memory. */
+int swcb200_fc_bf16(swcb200_ctx *ctx, int m, int n, int k, const void *a_bf16, int lda,
+                    const void *wp_bf16, int ldw, const float *bias, int act, void *c,
+                    int c_dtype, int ldc);
+
+/* MaxPool / ReLU / add on bf16 NHWC storage (same semantics as the fp32 entry points). */
+int swcb200_maxpool_bf16(swcb200_ctx *ctx, const void *input, void *output, const size_t *idims,
+                         const size_t *odims, const size_t *kernels, const size_t *strides,
+                         const size_t *pads);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* SWC_B200_H_ */

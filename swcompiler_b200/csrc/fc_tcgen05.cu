@@ -1,0 +1,386 @@
+// Fully-connected layer on the 5th-generation tensor cores:
+//     C[m,n] = act( A[m,k] . Wp[n,k]^T + bias[n] )       A, Wp bf16 (K-major), fp32 accumulate
+// One launch covers the MatrixMatrixMul -> MatrixVectorAdd -> ReLU/Tanh chain the reference's
+// lowering produces for an FC layer (src/op/dlOp/dlOpEinsum.cpp:154-237; arithmetic of
+// kernels.h:41-56, :542-552, :575-580, :58-64).
+//
+// Shape of the kernel
+//   * persistent: one CTA per SM, tiles of 128 x BN outputs (BN <= 256) taken round-robin, the n
+//     index fastest so the CTAs running together share a few A row panels and keep Wp in L2;
+//   * warp 0: TMA producer -- per 64-deep k block one 128x64 box of A and one BNx64 box of Wp into a
+//     4-stage shared-memory ring (128-byte swizzle), completion counted on an mbarrier per stage;
+//   * warp 1: MMA issuer -- one elected thread issues 4 tcgen05.mma (K = 16 each) per stage into a
+//     128-lane x BN-column fp32 accumulator in tensor memory; tcgen05.commit releases the stage back
+//     to the producer and, after the last k block, publishes the accumulator;
+//   * warps 2-5: epilogue -- tcgen05.ld 32 lanes x 32 columns at a time, + bias, activation, convert,
+//     128-bit global stores.  Two accumulators (2 x 256 columns = all 512 of the SM) alternate, so the
+//     epilogue of tile i overlaps the main loop of tile i+1.
+//   Out-of-range rows/columns/k are zero-filled by TMA on the way in and masked on the way out.
+#include <mutex>
+#include <unordered_map>
+
+#include "tc_common.cuh"
+
+namespace tc {
+
+EncodeTiledFn encode_tiled_fn() {
+    static EncodeTiledFn fn = nullptr;
+    static std::once_flag once;
+    std::call_once(once, [] {
+        void *p = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess &&
+            q == cudaDriverEntryPointSuccess)
+            fn = (EncodeTiledFn)p;
+    });
+    return fn;
+}
+
+int make_tmap_bf16(swcb200_ctx *ctx, CUtensorMap *out, const void *base, int rank, const uint64_t *dims,
+                   const uint64_t *strides_bytes, const uint32_t *box) {
+    EncodeTiledFn fn = encode_tiled_fn();
+    SWC_REQUIRE(ctx, fn != nullptr, SWCB200_ERR_CUDA, "cuTensorMapEncodeTiled entry point not found");
+    cuuint64_t gdim[5], gstr[5];
+    cuuint32_t bx[5], es[5];
+    for (int i = 0; i < rank; i++) {
+        gdim[i] = dims[i];
+        bx[i] = box[i];
+        es[i] = 1;
+        if (i > 0) gstr[i - 1] = strides_bytes[i];
+    }
+    CUresult r = fn(out, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, (cuuint32_t)rank, const_cast<void *>(base), gdim, gstr, bx, es,
+                    CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                    CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    SWC_REQUIRE(ctx, r == CUDA_SUCCESS, SWCB200_ERR_CUDA, "cuTensorMapEncodeTiled failed with CUresult %d", (int)r);
+    return SWCB200_OK;
+}
+
+}  // namespace tc
+
+namespace {
+
+using namespace tc;
+
+constexpr int BM = 128;        // UMMA M
+constexpr int BN_MAX = 256;    // UMMA N upper bound
+constexpr int BK = 64;         // one 128-byte swizzle row of bf16
+constexpr int UMMA_K = 16;     // K per tcgen05.mma for 16-bit inputs
+constexpr int kStages = 4;
+constexpr int A_BYTES = BM * BK * 2;                 // 16 KiB
+constexpr int B_BYTES = BN_MAX * BK * 2;             // 32 KiB
+constexpr int STAGE_BYTES = A_BYTES + B_BYTES;       // 48 KiB
+constexpr int kTmemCols = 512;                       // two 256-column accumulators
+constexpr int kThreads = 192;                        // TMA warp, MMA warp, 4 epilogue warps
+constexpr int kEpilogueThreads = 128;
+constexpr size_t kSmemBytes = (size_t)kStages * STAGE_BYTES + 1024 /*alignment slack*/ + 256 /*barriers*/;
+
+struct FcParams {
+    int m, n, k;
+    int bn;  // tile width actually used: 32, 64, 128 or 256
+    int tiles_m, tiles_n;
+    const float *bias;
+    int act;
+    void *c;
+    int c_is_bf16;
+    int ldc;
+    int c_vec;  // C base and row pitch are 16-byte aligned: 128-bit stores allowed
+    int *status;
+};
+
+__device__ __forceinline__ float apply_act(float v, int act) {
+    if (act == SWCB200_ACT_RELU) return (v > 0.f) ? v : 0.f;
+    if (act == SWCB200_ACT_TANH) return 1.0f - __fdividef(2.0f, __expf(2.0f * v) + 1.0f);
+    return v;
+}
+
+__global__ void __launch_bounds__(kThreads, 1)
+fc_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB, const FcParams p) {
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t *smem = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
+    uint64_t *full = reinterpret_cast<uint64_t *>(smem + (size_t)kStages * STAGE_BYTES);
+    uint64_t *empty = full + kStages;
+    uint64_t *tmem_full = empty + kStages;
+    uint64_t *tmem_empty = tmem_full + 2;
+    uint32_t *tmem_holder = reinterpret_cast<uint32_t *>(tmem_empty + 2);
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int num_tiles = p.tiles_m * p.tiles_n;
+    const int kblocks = (p.k + BK - 1) / BK;
+
+    if (threadIdx.x == 0) {
+        tma_prefetch_desc(&tmA);
+        tma_prefetch_desc(&tmB);
+        for (int s = 0; s < kStages; s++) {
+            mbar_init(&full[s], 1);
+            mbar_init(&empty[s], 1);
+        }
+        for (int b = 0; b < 2; b++) {
+            mbar_init(&tmem_full[b], 1);
+            mbar_init(&tmem_empty[b], kEpilogueThreads);
+        }
+        fence_barrier_init();
+        fence_proxy_async();
+    }
+    if (warp == 1) {
+        tmem_alloc(tmem_holder, kTmemCols);
+        tmem_relinquish();
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = *tmem_holder;
+
+    if (warp == 0) {
+        // ------------------------------------------------------------ TMA producer
+        if (lane == 0) {
+            const uint32_t tx_bytes = (uint32_t)(A_BYTES + p.bn * BK * 2);
+            uint32_t g = 0;  // k blocks issued so far (ring position)
+            bool ok = true;
+            for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x) {
+                const int tm = t / p.tiles_n, tn = t - tm * p.tiles_n;
+                for (int kb = 0; kb < kblocks; kb++, g++) {
+                    const int s = g % kStages;
+                    const uint32_t ph = (g / kStages) & 1;
+                    if (!mbar_wait(&empty[s], ph ^ 1, p.status, kWaitEmpty)) {
+                        ok = false;
+                        break;
+                    }
+                    mbar_expect_tx(&full[s], tx_bytes);
+                    uint8_t *sa = smem + (size_t)s * STAGE_BYTES;
+                    tma_load_2d(sa, &tmA, &full[s], kb * BK, tm * BM);
+                    tma_load_2d(sa + A_BYTES, &tmB, &full[s], kb * BK, tn * p.bn);
+                }
+            }
+            // Drain: do not leave the CTA while copies may still be landing in its shared memory.
+            // Every issued stage either was consumed (its empty barrier completes) or still has to
+            // complete its full barrier; waiting for the last kStages fills covers both.
+            const uint32_t issued = g;
+            for (uint32_t back = 0; back < (uint32_t)kStages && back < issued; back++) {
+                const uint32_t gi = issued - 1 - back;
+                if (!mbar_wait(&full[gi % kStages], (gi / kStages) & 1, p.status, kWaitDrain)) break;
+            }
+        }
+    } else if (warp == 1) {
+        // ------------------------------------------------------------ MMA issuer
+        if (lane == 0) {
+            const uint32_t idesc = idesc_bf16_f32(BM, p.bn);
+            uint32_t g = 0, it = 0;
+            bool ok = true;
+            for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x, it++) {
+                const uint32_t buf = it & 1, aph = (it >> 1) & 1;
+                if (!mbar_wait(&tmem_empty[buf], aph ^ 1, p.status, kWaitTmemEmpty)) break;
+                tc_fence_after();
+                const uint32_t d_tmem = tmem_base + buf * BN_MAX;
+                for (int kb = 0; kb < kblocks; kb++, g++) {
+                    const int s = g % kStages;
+                    const uint32_t ph = (g / kStages) & 1;
+                    if (!mbar_wait(&full[s], ph, p.status, kWaitFull)) {
+                        ok = false;
+                        break;
+                    }
+                    tc_fence_after();
+                    const uint32_t sa = smem_u32(smem + (size_t)s * STAGE_BYTES);
+                    const uint64_t da = smem_desc_sw128(sa), db = smem_desc_sw128(sa + A_BYTES);
+#pragma unroll
+                    for (int j = 0; j < BK / UMMA_K; j++) {
+                        // advancing K by 16 elements = 32 bytes inside the swizzle row: +2 in the >>4 address field
+                        umma_bf16(d_tmem, da + 2 * j, db + 2 * j, idesc, (uint32_t)((kb | j) != 0));
+                    }
+                    umma_commit(&empty[s]);  // stage reusable once these MMAs have read it
+                }
+                if (ok) umma_commit(&tmem_full[buf]);
+            }
+        }
+    } else {
+        // ------------------------------------------------------------ epilogue (warps 2..5)
+        const int quarter = warp & 3;  // the TMEM lane quarter this warp may read
+        uint32_t it = 0;
+        for (int t = blockIdx.x; t < num_tiles; t += gridDim.x, it++) {
+            const uint32_t buf = it & 1, aph = (it >> 1) & 1;
+            const int tm = t / p.tiles_n, tn = t - tm * p.tiles_n;
+            bool ok = mbar_wait(&tmem_full[buf], aph, p.status, kWaitTmemFull);
+            ok = __all_sync(0xffffffffu, ok);
+            if (!ok) break;
+            tc_fence_after();
+            const int row = tm * BM + quarter * 32 + lane;
+            const bool row_ok = row < p.m;
+            const int col_base = tn * p.bn;
+            for (int c0 = 0; c0 < p.bn; c0 += 32) {
+                uint32_t r[32];
+                __syncwarp();  // tcgen05.ld is warp-collective
+                tmem_ld_32x32(tmem_base + ((uint32_t)(quarter * 32) << 16) + buf * BN_MAX + c0, r);
+                tmem_ld_wait();
+                const int col = col_base + c0;
+                if (!row_ok || col >= p.n) continue;
+                float v[32];
+#pragma unroll
+                for (int j = 0; j < 32; j++) {
+                    float x = __uint_as_float(r[j]);
+                    if (p.bias != nullptr && col + j < p.n) x += __ldg(p.bias + col + j);
+                    v[j] = apply_act(x, p.act);
+                }
+                if (p.c_is_bf16) {
+                    __nv_bfloat16 *dst = reinterpret_cast<__nv_bfloat16 *>(p.c) + (size_t)row * p.ldc + col;
+#pragma unroll
+                    for (int j = 0; j < 32; j += 8) {
+                        if (p.c_vec && col + j + 8 <= p.n) {
+                            uint4 o;
+                            __nv_bfloat162 *h = reinterpret_cast<__nv_bfloat162 *>(&o);
+                            h[0] = __floats2bfloat162_rn(v[j], v[j + 1]);
+                            h[1] = __floats2bfloat162_rn(v[j + 2], v[j + 3]);
+                            h[2] = __floats2bfloat162_rn(v[j + 4], v[j + 5]);
+                            h[3] = __floats2bfloat162_rn(v[j + 6], v[j + 7]);
+                            *reinterpret_cast<uint4 *>(dst + j) = o;
+                        } else {
+                            for (int e = 0; e < 8; e++)
+                                if (col + j + e < p.n) dst[j + e] = __float2bfloat16_rn(v[j + e]);
+                        }
+                    }
+                } else {
+                    float *dst = reinterpret_cast<float *>(p.c) + (size_t)row * p.ldc + col;
+#pragma unroll
+                    for (int j = 0; j < 32; j += 4) {
+                        if (p.c_vec && col + j + 4 <= p.n) {
+                            *reinterpret_cast<float4 *>(dst + j) = make_float4(v[j], v[j + 1], v[j + 2], v[j + 3]);
+                        } else {
+                            for (int e = 0; e < 4; e++)
+                                if (col + j + e < p.n) dst[j + e] = v[j + e];
+                        }
+                    }
+                }
+            }
+            tc_fence_before();
+            mbar_arrive(&tmem_empty[buf]);
+        }
+    }
+
+    // tear-down: everyone meets, then the allocating warp frees tensor memory
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 1) {
+        __syncwarp();
+        tc_fence_after();
+        tmem_dealloc(tmem_base, kTmemCols);
+    }
+}
+
+struct TmapKey {
+    const void *base;
+    uint64_t rows, cols, ld;
+    uint32_t box_rows;
+    bool operator==(const TmapKey &o) const {
+        return base == o.base && rows == o.rows && cols == o.cols && ld == o.ld && box_rows == o.box_rows;
+    }
+};
+struct TmapKeyHash {
+    size_t operator()(const TmapKey &k) const {
+        size_t h = (size_t)k.base;
+        h = h * 1000003u ^ k.rows;
+        h = h * 1000003u ^ k.cols;
+        h = h * 1000003u ^ k.ld;
+        h = h * 1000003u ^ k.box_rows;
+        return h;
+    }
+};
+
+// row-major [rows, cols] bf16 with leading dimension ld; box = box_rows x 64
+int tmap_2d(swcb200_ctx *ctx, const void *base, uint64_t rows, uint64_t cols, uint64_t ld, uint32_t box_rows,
+            CUtensorMap *out) {
+    // Encoding costs a few microseconds of host time; the same few operands recur every forward pass.
+    static thread_local std::unordered_map<TmapKey, CUtensorMap, TmapKeyHash> cache;
+    TmapKey key{base, rows, cols, ld, box_rows};
+    auto it = cache.find(key);
+    if (it != cache.end()) {
+        *out = it->second;
+        return SWCB200_OK;
+    }
+    uint64_t dims[2] = {cols, rows};
+    uint64_t strides[2] = {2, ld * 2};
+    uint32_t box[2] = {(uint32_t)BK, box_rows};
+    int rc = make_tmap_bf16(ctx, out, base, 2, dims, strides, box);
+    if (rc) return rc;
+    if (cache.size() > 4096) cache.clear();
+    cache.emplace(key, *out);
+    return SWCB200_OK;
+}
+
+}  // namespace
+
+int swc_fc_tc(swcb200_ctx *ctx, int m, int n, int k, const void *a, int lda, const void *wp, int ldw, const float *bias,
+              int act, void *c, int c_dtype, int ldc) {
+    SWC_REQUIRE(ctx, swc_aligned16(a) && swc_aligned16(wp), SWCB200_ERR_MISALIGNED,
+                "fc_bf16: A and Wp must be 16-byte aligned");
+    SWC_REQUIRE(ctx, lda % 8 == 0 && ldw % 8 == 0, SWCB200_ERR_MISALIGNED,
+                "fc_bf16: lda (%d) and ldw (%d) must be multiples of 8 elements", lda, ldw);
+    SWC_REQUIRE(ctx, lda >= k && ldw >= k && ldc >= n, SWCB200_ERR_BAD_SHAPE, "fc_bf16: leading dimension too small");
+    const size_t celem = c_dtype == SWCB200_BF16 ? 2 : 4;
+    int bn = 32;  // smallest tile width: the epilogue reads tensor memory 32 columns at a time
+    while (bn < n && bn < BN_MAX) bn <<= 1;
+    FcParams p;
+    p.m = m;
+    p.n = n;
+    p.k = k;
+    p.bn = bn;
+    p.tiles_m = (m + BM - 1) / BM;
+    p.tiles_n = (n + bn - 1) / bn;
+    p.bias = bias;
+    p.act = act;
+    p.c = c;
+    p.c_is_bf16 = c_dtype == SWCB200_BF16;
+    p.ldc = ldc;
+    p.c_vec = swc_aligned16(c) && ((size_t)ldc * celem) % 16 == 0;
+    p.status = ctx->dev_status;
+    CUtensorMap tmA, tmB;
+    int rc = tmap_2d(ctx, a, (uint64_t)m, (uint64_t)k, (uint64_t)lda, BM, &tmA);
+    if (rc) return rc;
+    rc = tmap_2d(ctx, wp, (uint64_t)n, (uint64_t)k, (uint64_t)ldw, (uint32_t)bn, &tmB);
+    if (rc) return rc;
+    if (!ctx->fc_attr_set) {
+        SWC_CUDA(ctx, cudaFuncSetAttribute(fc_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSmemBytes));
+        ctx->fc_attr_set = true;
+    }
+    const long long tiles = (long long)p.tiles_m * p.tiles_n;
+    unsigned grid = (unsigned)(tiles < ctx->sm_count ? tiles : ctx->sm_count);
+    fc_tc_kernel<<<grid, kThreads, kSmemBytes, ctx->stream>>>(tmA, tmB, p);
+    return swc_check_launch(ctx, "fc_bf16");
+}
+
+SWC_EXPORT int swcb200_fc_bf16(swcb200_ctx *ctx, int m, int n, int k, const void *a_bf16, int lda, const void *wp_bf16,
+                               int ldw, const float *bias, int act, void *c, int c_dtype, int ldc) {
+    SWC_CTX(ctx);
+    SWC_REQUIRE(ctx, m >= 0 && n >= 0 && k > 0, SWCB200_ERR_BAD_ARG, "fc_bf16: bad shape %d x %d x %d", m, n, k);
+    SWC_REQUIRE(ctx, act >= SWCB200_ACT_NONE && act <= SWCB200_ACT_TANH, SWCB200_ERR_BAD_ARG, "fc_bf16: unknown activation");
+    SWC_REQUIRE(ctx, c_dtype == SWCB200_F32 || c_dtype == SWCB200_BF16, SWCB200_ERR_BAD_ARG, "fc_bf16: unknown output dtype");
+    if (m == 0 || n == 0) return SWCB200_OK;
+    SWC_REQUIRE(ctx, a_bf16 && wp_bf16 && c, SWCB200_ERR_BAD_ARG, "fc_bf16: null tensor");
+    return swc_fc_tc(ctx, m, n, k, a_bf16, lda, wp_bf16, ldw, bias, act, c, c_dtype, ldc);
+}
+
+int swc_fc_strict(swcb200_ctx *ctx, int m, int n, int k, const float *a, int lda, const float *b, int ldb, float *c,
+                  int ldc);
+
+// fp32 entry point.  Strict mode: the bit-exact FFMA-pipe kernel.  Tensor-core mode: A and B are
+// rounded to bf16 into the context's private scratch (B transposed to K-major on the way) and the
+// tcgen05 kernel writes fp32 C.
+SWC_EXPORT int swcb200_matrixMatrixMul_f(swcb200_ctx *ctx, int m, int n, int k, const float *a, int lda, const float *b,
+                                         int ldb, float *c, int ldc) {
+    SWC_CTX(ctx);
+    SWC_REQUIRE(ctx, m >= 0 && n >= 0 && k >= 0, SWCB200_ERR_BAD_ARG, "matrixMatrixMul_f: negative shape");
+    SWC_REQUIRE(ctx, lda >= k && ldb >= n && ldc >= n, SWCB200_ERR_BAD_SHAPE,
+                "matrixMatrixMul_f: leading dimension too small");
+    if (m == 0 || n == 0) return SWCB200_OK;
+    SWC_REQUIRE(ctx, c && (k == 0 || (a && b)), SWCB200_ERR_BAD_ARG, "matrixMatrixMul_f: null tensor");
+    const bool tc_ok = ctx->precision == SWCB200_TC_BF16 && k > 0;
+    if (!tc_ok) return swc_fc_strict(ctx, m, n, k, a, lda, b, ldb, c, ldc);
+    const size_t kp = ((size_t)k + 7) & ~(size_t)7;  // padded K so that row pitches are 16-byte multiples
+    const size_t a_bytes = ((size_t)m * kp * 2 + 255) & ~(size_t)255, b_bytes = (size_t)n * kp * 2;
+    void *scratch = nullptr;
+    int rc = swc_scratch(ctx, a_bytes + b_bytes, &scratch);
+    if (rc) return rc;
+    void *a16 = scratch, *b16 = (uint8_t *)scratch + a_bytes;
+    rc = swc_cast_pad_rows(ctx, a, m, k, lda, a16, (int)kp);
+    if (rc) return rc;
+    rc = swc_pack_weight_padded(ctx, b, k, n, ldb, b16, (int)kp);
+    if (rc) return rc;
+    return swc_fc_tc(ctx, m, n, k, a16, (int)kp, b16, (int)kp, nullptr, SWCB200_ACT_NONE, c, SWCB200_F32, ldc);
+}

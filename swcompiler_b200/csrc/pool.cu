@@ -1,0 +1,209 @@
+// NHWC pooling: MaxPool (fp32 and bf16 storage) and AvgPool.
+//
+// One thread produces one output pixel x one group of channels (4 fp32 or 8 bf16 = 16 bytes when the
+// channel count allows, else one channel).  Channels are the fastest thread index, so a warp reads
+// whole 128-byte lines of every tap; with a 2x2/2 window every input byte is read exactly once.
+#include <cuda_bf16.h>
+
+#include "common.cuh"
+
+namespace {
+
+struct PoolGeom {
+    int N, H, W, C, OH, OW, kh, kw, sh, sw, pt, pl;
+};
+
+// maxpool_f semantics (kernels.h:347-371): first in-range tap initialises, later taps replace only
+// when strictly greater, out-of-range taps are ignored, no in-range tap -> 0.
+struct MaxAcc {
+    float v = 0.f;
+    bool init = false;
+    __device__ __forceinline__ void tap(float x) {
+        if (!init || x > v) {
+            v = x;
+            init = true;
+        }
+    }
+};
+
+template <int kVec>  // 4: float4 over channels, 1: scalar
+__global__ void __launch_bounds__(256) maxpool_f32_kernel(const float *__restrict__ in, float *__restrict__ out,
+                                                          PoolGeom g) {
+    const int cg = g.C / kVec;
+    const size_t total = (size_t)g.N * g.OH * g.OW * cg;
+    for (size_t t = (size_t)blockIdx.x * blockDim.x + threadIdx.x; t < total; t += (size_t)gridDim.x * blockDim.x) {
+        int c = (int)(t % cg) * kVec;
+        size_t p = t / cg;
+        int ow = (int)(p % g.OW);
+        p /= g.OW;
+        int oh = (int)(p % g.OH);
+        int n = (int)(p / g.OH);
+        MaxAcc acc[kVec];
+        for (int kx = 0; kx < g.kh; kx++) {
+            int ih = oh * g.sh - g.pt + kx;
+            if (ih < 0 || ih >= g.H) continue;
+            for (int ky = 0; ky < g.kw; ky++) {
+                int iw = ow * g.sw - g.pl + ky;
+                if (iw < 0 || iw >= g.W) continue;
+                const float *src = in + (((size_t)n * g.H + ih) * g.W + iw) * g.C + c;
+                if (kVec == 4) {
+                    float4 x = __ldcs(reinterpret_cast<const float4 *>(src));
+                    acc[0].tap(x.x);
+                    acc[1 % kVec].tap(x.y);
+                    acc[2 % kVec].tap(x.z);
+                    acc[3 % kVec].tap(x.w);
+                } else {
+                    acc[0].tap(__ldcs(src));
+                }
+            }
+        }
+        float *dst = out + (((size_t)n * g.OH + oh) * g.OW + ow) * g.C + c;
+        if (kVec == 4)
+            __stcs(reinterpret_cast<float4 *>(dst), make_float4(acc[0].v, acc[1 % kVec].v, acc[2 % kVec].v, acc[3 % kVec].v));
+        else
+            *dst = acc[0].v;
+    }
+}
+
+template <int kVec>  // 8: uint4 (8 bf16) over channels, 1: scalar
+__global__ void __launch_bounds__(256) maxpool_bf16_kernel(const __nv_bfloat16 *__restrict__ in,
+                                                           __nv_bfloat16 *__restrict__ out, PoolGeom g) {
+    const int cg = g.C / kVec;
+    const size_t total = (size_t)g.N * g.OH * g.OW * cg;
+    for (size_t t = (size_t)blockIdx.x * blockDim.x + threadIdx.x; t < total; t += (size_t)gridDim.x * blockDim.x) {
+        int c = (int)(t % cg) * kVec;
+        size_t p = t / cg;
+        int ow = (int)(p % g.OW);
+        p /= g.OW;
+        int oh = (int)(p % g.OH);
+        int n = (int)(p / g.OH);
+        MaxAcc acc[kVec];
+        for (int kx = 0; kx < g.kh; kx++) {
+            int ih = oh * g.sh - g.pt + kx;
+            if (ih < 0 || ih >= g.H) continue;
+            for (int ky = 0; ky < g.kw; ky++) {
+                int iw = ow * g.sw - g.pl + ky;
+                if (iw < 0 || iw >= g.W) continue;
+                const __nv_bfloat16 *src = in + (((size_t)n * g.H + ih) * g.W + iw) * g.C + c;
+                if (kVec == 8) {
+                    uint4 x = __ldcs(reinterpret_cast<const uint4 *>(src));
+                    const __nv_bfloat16 *e = reinterpret_cast<const __nv_bfloat16 *>(&x);
+#pragma unroll
+                    for (int i = 0; i < kVec; i++) acc[i].tap(__bfloat162float(e[i]));
+                } else {
+                    acc[0].tap(__bfloat162float(*src));
+                }
+            }
+        }
+        __nv_bfloat16 *dst = out + (((size_t)n * g.OH + oh) * g.OW + ow) * g.C + c;
+        if (kVec == 8) {
+            uint4 o;
+            __nv_bfloat16 *e = reinterpret_cast<__nv_bfloat16 *>(&o);
+#pragma unroll
+            for (int i = 0; i < kVec; i++) e[i] = __float2bfloat16_rn(acc[i].v);  // exact: the value came from bf16
+            __stcs(reinterpret_cast<uint4 *>(dst), o);
+        } else {
+            *dst = __float2bfloat16_rn(acc[0].v);
+        }
+    }
+}
+
+// avgpool_f (kernels.h:444-493): in-range taps summed kx then ky, divided by kh*kw regardless of padding
+__global__ void __launch_bounds__(256) avgpool_f32_kernel(const float *__restrict__ in, float *__restrict__ out,
+                                                          PoolGeom g) {
+    const size_t total = (size_t)g.N * g.OH * g.OW * g.C;
+    const float cnt = (float)((size_t)g.kh * g.kw);
+    for (size_t t = (size_t)blockIdx.x * blockDim.x + threadIdx.x; t < total; t += (size_t)gridDim.x * blockDim.x) {
+        int c = (int)(t % g.C);
+        size_t p = t / g.C;
+        int ow = (int)(p % g.OW);
+        p /= g.OW;
+        int oh = (int)(p % g.OH);
+        int n = (int)(p / g.OH);
+        float sum = 0.f;
+        for (int kx = 0; kx < g.kh; kx++) {
+            int ih = oh * g.sh - g.pt + kx;
+            if (ih < 0 || ih >= g.H) continue;
+            for (int ky = 0; ky < g.kw; ky++) {
+                int iw = ow * g.sw - g.pl + ky;
+                if (iw < 0 || iw >= g.W) continue;
+                sum = __fadd_rn(sum, in[(((size_t)n * g.H + ih) * g.W + iw) * g.C + c]);
+            }
+        }
+        out[t] = __fdiv_rn(sum, cnt);
+    }
+}
+
+int make_geom(swcb200_ctx *ctx, const char *what, const size_t *idims, const size_t *odims, const size_t *kernels,
+              const size_t *strides, const size_t *pads, PoolGeom *g) {
+    SWC_REQUIRE(ctx, idims && odims && kernels && strides && pads, SWCB200_ERR_BAD_ARG, "%s: null attribute array", what);
+    for (int i = 0; i < 4; i++)
+        SWC_REQUIRE(ctx, idims[i] <= 0x7fffffff && odims[i] <= 0x7fffffff, SWCB200_ERR_TOO_LARGE,
+                    "%s: dimension beyond 2^31", what);
+    SWC_REQUIRE(ctx, strides[0] > 0 && strides[1] > 0, SWCB200_ERR_BAD_ARG, "%s: zero stride", what);
+    SWC_REQUIRE(ctx, odims[0] == idims[0] && odims[3] == idims[3], SWCB200_ERR_BAD_SHAPE,
+                "%s: batch/channel of output differ from input", what);
+    *g = PoolGeom{(int)idims[0], (int)idims[1], (int)idims[2], (int)idims[3], (int)odims[1], (int)odims[2],
+                  (int)kernels[0], (int)kernels[1], (int)strides[0], (int)strides[1], (int)pads[0], (int)pads[1]};
+    return SWCB200_OK;
+}
+
+}  // namespace
+
+SWC_EXPORT int swcb200_maxpool_f(swcb200_ctx *ctx, const float *input, float *output, const size_t *idims,
+                                 const size_t *odims, const size_t *kernels, const size_t *strides,
+                                 const size_t *pads) {
+    SWC_CTX(ctx);
+    PoolGeom g;
+    int rc = make_geom(ctx, "maxpool_f", idims, odims, kernels, strides, pads, &g);
+    if (rc) return rc;
+    size_t total = (size_t)g.N * g.OH * g.OW * g.C;
+    if (total == 0) return SWCB200_OK;
+    SWC_REQUIRE(ctx, input && output, SWCB200_ERR_BAD_ARG, "maxpool_f: null tensor");
+    bool vec = (g.C % 4 == 0) && swc_aligned16(input) && swc_aligned16(output);
+    if (vec) {
+        unsigned grid = swc_grid(ctx, total / 4, 256, 8);
+        maxpool_f32_kernel<4><<<grid, 256, 0, ctx->stream>>>(input, output, g);
+    } else {
+        unsigned grid = swc_grid(ctx, total, 256, 8);
+        maxpool_f32_kernel<1><<<grid, 256, 0, ctx->stream>>>(input, output, g);
+    }
+    return swc_check_launch(ctx, "maxpool_f");
+}
+
+SWC_EXPORT int swcb200_maxpool_bf16(swcb200_ctx *ctx, const void *input, void *output, const size_t *idims,
+                                    const size_t *odims, const size_t *kernels, const size_t *strides,
+                                    const size_t *pads) {
+    SWC_CTX(ctx);
+    PoolGeom g;
+    int rc = make_geom(ctx, "maxpool_bf16", idims, odims, kernels, strides, pads, &g);
+    if (rc) return rc;
+    size_t total = (size_t)g.N * g.OH * g.OW * g.C;
+    if (total == 0) return SWCB200_OK;
+    SWC_REQUIRE(ctx, input && output, SWCB200_ERR_BAD_ARG, "maxpool_bf16: null tensor");
+    bool vec = (g.C % 8 == 0) && swc_aligned16(input) && swc_aligned16(output);
+    if (vec) {
+        unsigned grid = swc_grid(ctx, total / 8, 256, 8);
+        maxpool_bf16_kernel<8><<<grid, 256, 0, ctx->stream>>>((const __nv_bfloat16 *)input, (__nv_bfloat16 *)output, g);
+    } else {
+        unsigned grid = swc_grid(ctx, total, 256, 8);
+        maxpool_bf16_kernel<1><<<grid, 256, 0, ctx->stream>>>((const __nv_bfloat16 *)input, (__nv_bfloat16 *)output, g);
+    }
+    return swc_check_launch(ctx, "maxpool_bf16");
+}
+
+SWC_EXPORT int swcb200_avgpool_f(swcb200_ctx *ctx, const float *input, float *output, const size_t *idims,
+                                 const size_t *odims, const size_t *kernels, const size_t *strides,
+                                 const size_t *pads) {
+    SWC_CTX(ctx);
+    PoolGeom g;
+    int rc = make_geom(ctx, "avgpool_f", idims, odims, kernels, strides, pads, &g);
+    if (rc) return rc;
+    SWC_REQUIRE(ctx, g.kh > 0 && g.kw > 0, SWCB200_ERR_BAD_ARG, "avgpool_f: empty window");
+    size_t total = (size_t)g.N * g.OH * g.OW * g.C;
+    if (total == 0) return SWCB200_OK;
+    SWC_REQUIRE(ctx, input && output, SWCB200_ERR_BAD_ARG, "avgpool_f: null tensor");
+    unsigned grid = swc_grid(ctx, total, 256, 8);
+    avgpool_f32_kernel<<<grid, 256, 0, ctx->stream>>>(input, output, g);
+    return swc_check_launch(ctx, "avgpool_f");
+}

@@ -1,0 +1,241 @@
+"""Host-side mirror of the reference's kernel interface, on torch CUDA tensors.
+
+`Backend` owns one library context (device + stream) and exposes one method per function of the
+reference's kernel header (src/codegen/utils/kernels.h), same name, same argument meaning, with
+tensors in place of raw pointers and shapes taken from the tensors.  Every method only validates,
+allocates the output with torch and calls through the C-ABI; all arithmetic happens in the CUDA
+library.  torch is used for device memory and streams, nothing else.
+"""
+from __future__ import annotations
+
+import ctypes as C
+
+import torch
+
+from . import _lib as L
+
+
+def _p(t):
+    return C.c_void_p(t.data_ptr() if t is not None else 0)
+
+
+def _dims(seq):
+    return (C.c_size_t * len(seq))(*[int(x) for x in seq])
+
+
+def conv_out_dims(idims, fdims, kernels, strides, pads):
+    """Conv2dOp shape inference, src/op/dlOp.cpp:195-196."""
+    n, h, w, _ = idims
+    return (n, (h + pads[0] + pads[2] - kernels[0]) // strides[0] + 1,
+            (w + pads[1] + pads[3] - kernels[1]) // strides[1] + 1, fdims[0])
+
+
+def pool_out_dims(idims, kernels, strides, pads):
+    n, h, w, c = idims
+    return (n, (h + pads[0] + pads[2] - kernels[0]) // strides[0] + 1,
+            (w + pads[1] + pads[3] - kernels[1]) // strides[1] + 1, c)
+
+
+class Backend:
+    def __init__(self, device: int | torch.device = 0, precision: int = L.STRICT_F32, own_stream: bool = False):
+        if not torch.cuda.is_available():
+            raise RuntimeError("swcompiler_b200 needs a CUDA device; there is no CPU path")
+        self.lib = L.lib()
+        self.device = torch.device("cuda", device if isinstance(device, int) else device.index or 0)
+        self._ctx = C.c_void_p()
+        with torch.cuda.device(self.device):
+            if own_stream:
+                rc = self.lib.swcb200_init(C.c_int(self.device.index), C.c_int(precision), C.byref(self._ctx))
+            else:
+                s = torch.cuda.current_stream(self.device).cuda_stream
+                rc = self.lib.swcb200_init_on_stream(C.c_int(self.device.index), C.c_int(precision), C.c_void_p(s),
+                                                     C.byref(self._ctx))
+        if rc != L.OK:
+            raise L.SwcError(rc, "swcb200_init")
+        self.precision = precision
+
+    # ---- plumbing -----------------------------------------------------------
+    def close(self):
+        if self._ctx:
+            self.lib.swcb200_destroy(self._ctx)
+            self._ctx = C.c_void_p()
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
+
+    def _check(self, rc: int, what: str):
+        if rc != L.OK:
+            raise L.SwcError(rc, what, self.lib.swcb200_last_error(self._ctx).decode())
+
+    def _call(self, name: str, *args):
+        self._check(getattr(self.lib, "swcb200_" + name)(self._ctx, *args), name)
+
+    def sync(self):
+        self._call("sync")
+
+    def set_precision(self, precision: int):
+        self._call("set_precision", C.c_int(precision))
+        self.precision = precision
+
+    @property
+    def launches(self) -> int:
+        return int(self.lib.swcb200_launch_count(self._ctx))
+
+    def _f32(self, *ts):
+        for t in ts:
+            if t is None:
+                continue
+            if not (t.is_cuda and t.dtype == torch.float32 and t.is_contiguous()):
+                raise ValueError("expected a contiguous fp32 CUDA tensor")
+
+    def _new(self, shape, dtype=torch.float32):
+        return torch.empty(tuple(int(s) for s in shape), dtype=dtype, device=self.device)
+
+    # ---- dense --------------------------------------------------------------
+    def matrixMatrixMul_f(self, a, b, out=None):
+        self._f32(a, b)
+        (m, k), (k2, n) = a.shape, b.shape
+        if k != k2:
+            raise ValueError("inner dimensions differ")
+        c = out if out is not None else self._new((m, n))
+        self._call("matrixMatrixMul_f", C.c_int(m), C.c_int(n), C.c_int(k), _p(a), C.c_int(k), _p(b), C.c_int(n),
+                   _p(c), C.c_int(n))
+        return c
+
+    def batchedadd_f(self, batch, slice_, out=None):
+        self._f32(batch, slice_)
+        rows, cols = batch.shape
+        out = out if out is not None else torch.empty_like(batch)
+        self._call("batchedadd_f", _p(out), _p(batch), _p(slice_), C.c_size_t(rows), C.c_size_t(cols))
+        return out
+
+    def matrixTanh_f(self, a, out=None):
+        self._f32(a)
+        m, n = a.shape
+        out = out if out is not None else torch.empty_like(a)
+        self._call("matrixTanh_f", C.c_int(m), C.c_int(n), _p(a), C.c_int(n), _p(out), C.c_int(n))
+        return out
+
+    def matrixSoftmax_f(self, a, out=None):
+        self._f32(a)
+        m, n = a.shape
+        out = out if out is not None else torch.empty_like(a)
+        self._call("matrixSoftmax_f", C.c_int(m), C.c_int(n), _p(a), C.c_int(n), _p(out), C.c_int(n))
+        return out
+
+    def argMax_i(self, a, top_k: int):
+        self._f32(a)
+        m, n = a.shape
+        idx = self._new((m, top_k), torch.int32)
+        self._call("argMax_i", _p(a), _p(idx), C.c_int(m), C.c_int(n), C.c_int(top_k))
+        return idx
+
+    def relu_f(self, a, out=None):
+        self._f32(a)
+        out = out if out is not None else torch.empty_like(a)
+        self._call("relu_f", _p(a), _p(out), C.c_size_t(a.numel()))
+        return out
+
+    def vecAdd_f(self, a, b, out=None):
+        self._f32(a, b)
+        out = out if out is not None else torch.empty_like(a)
+        self._call("vecAdd_f", C.c_int(a.numel()), _p(a), _p(b), _p(out))
+        return out
+
+    # ---- NHWC ---------------------------------------------------------------
+    def conv2d_f(self, x, filt, bias, kernels, strides, pads, group=1, out=None):
+        self._f32(x, filt, bias)
+        odims = conv_out_dims(x.shape, filt.shape, kernels, strides, pads)
+        out = out if out is not None else self._new(odims)
+        self._call("conv2d_f", _p(out), _p(x), _p(filt), _p(bias), _dims(odims), _dims(x.shape), _dims(filt.shape),
+                   _dims(bias.shape), _dims(kernels), _dims(strides), _dims(pads), C.c_size_t(group))
+        return out
+
+    def maxpool_f(self, x, kernels, strides, pads, out=None):
+        self._f32(x)
+        odims = pool_out_dims(x.shape, kernels, strides, pads)
+        out = out if out is not None else self._new(odims)
+        self._call("maxpool_f", _p(x), _p(out), _dims(x.shape), _dims(odims), _dims(kernels), _dims(strides),
+                   _dims(pads))
+        return out
+
+    def avgpool_f(self, x, kernels, strides, pads, out=None):
+        self._f32(x)
+        odims = pool_out_dims(x.shape, kernels, strides, pads)
+        out = out if out is not None else self._new(odims)
+        self._call("avgpool_f", _p(x), _p(out), _dims(x.shape), _dims(odims), _dims(kernels), _dims(strides),
+                   _dims(pads))
+        return out
+
+    def batchnormalization_f(self, x, mean, var, scale, bias, eps, out=None):
+        self._f32(x, mean, var, scale, bias)
+        out = out if out is not None else torch.empty_like(x)
+        self._call("batchnormalization_f", _p(out), _p(x), _p(mean), _p(var), _p(scale), _p(bias), _dims(x.shape),
+                   C.c_float(eps))
+        return out
+
+    def transpose2d_f(self, x, shuffle):
+        self._f32(x)
+        odims = tuple(x.shape[s] for s in shuffle)
+        out = self._new(odims)
+        self._call("transpose2d_f", _p(x), _p(out), _dims(x.shape), _dims(odims), _dims(shuffle))
+        return out
+
+    def transpose4d_f(self, x, shuffle):
+        self._f32(x)
+        odims = tuple(x.shape[s] for s in shuffle)
+        out = self._new(odims)
+        self._call("transpose4d_f", _p(x), _p(out), _dims(x.shape), _dims(odims), _dims(shuffle))
+        return out
+
+    # ---- chains as the lowered graph has them ---------------------------------
+    def fc(self, x, w, b=None):
+        """MatrixMatrixMul then MatrixVectorAdd (src/op/dlOp/dlOpEinsum.cpp:154-237); a 4-D NHWC input is
+        viewed as [N, H*W*C] (src/tensor/tensor.cpp:128-138)."""
+        y = self.matrixMatrixMul_f(x.reshape(x.shape[0], -1), w)
+        return y if b is None else self.batchedadd_f(y, b)
+
+    def mlp_forward(self, x, w0, b0, w1, b1):
+        return self.matrixSoftmax_f(self.fc(self.matrixTanh_f(self.fc(x, w0, b0)), w1, b1))
+
+    # ---- bf16 storage / tensor-core path ---------------------------------------
+    def cast_f32_to_bf16(self, x, out=None):
+        self._f32(x)
+        out = out if out is not None else self._new(x.shape, torch.bfloat16)
+        self._call("cast_f32_to_bf16", _p(x), _p(out), C.c_size_t(x.numel()))
+        return out
+
+    def cast_bf16_to_f32(self, x, out=None):
+        out = out if out is not None else self._new(x.shape, torch.float32)
+        self._call("cast_bf16_to_f32", _p(x), _p(out), C.c_size_t(x.numel()))
+        return out
+
+    def pack_weight_bf16(self, w):
+        """fp32 W[k, n] -> bf16 Wp[n, k]."""
+        self._f32(w)
+        k, n = w.shape
+        wp = self._new((n, k), torch.bfloat16)
+        self._call("pack_weight_bf16", _p(w), C.c_int(k), C.c_int(n), C.c_int(n), _p(wp))
+        return wp
+
+    def fc_bf16(self, a, wp, bias=None, act=L.ACT_NONE, out_dtype=torch.bfloat16, out=None):
+        """act(A[m,k] . Wp[n,k]^T + bias) in one launch; A, Wp bf16."""
+        if a.dtype != torch.bfloat16 or wp.dtype != torch.bfloat16 or not (a.is_contiguous() and wp.is_contiguous()):
+            raise ValueError("fc_bf16 wants contiguous bf16 operands")
+        (m, k), (n, k2) = a.shape, wp.shape
+        if k != k2:
+            raise ValueError("inner dimensions differ")
+        out = out if out is not None else self._new((m, n), out_dtype)
+        self._call("fc_bf16", C.c_int(m), C.c_int(n), C.c_int(k), _p(a), C.c_int(k), _p(wp), C.c_int(k), _p(bias),
+                   C.c_int(act), _p(out), C.c_int(L.BF16 if out.dtype == torch.bfloat16 else L.F32), C.c_int(n))
+        return out
+
+    def maxpool_bf16(self, x, kernels, strides, pads, out=None):
+        odims = pool_out_dims(x.shape, kernels, strides, pads)
+        out = out if out is not None else self._new(odims, torch.bfloat16)
+        self._call("maxpool_bf16", _p(x), _p(out), _dims(x.shape), _dims(odims), _dims(kernels), _dims(strides),
+                   _dims(pads))
+        return out

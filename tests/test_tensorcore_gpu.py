@@ -1,0 +1,109 @@
+"""GPU: the tcgen05 path (bf16 operands, fp32 accumulation in tensor memory) against the fp32 oracle.
+
+Inputs are bf16-representable, so the oracle multiplies exactly the same numbers; what differs is the
+summation (tensor-core accumulation order, and bf16 rounding of activations between layers).  Bars, as
+stated for the tensor-core path: max-abs error <= 2e-2 on logits, argmax agreement >= 99.9 %."""
+import numpy as np
+import pytest
+import torch
+
+import cases
+import swcompiler_b200 as swc
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.fixture(scope="module")
+def be():
+    return swc.Backend(0, swc.TC_BF16)
+
+
+def _bf16(x):
+    return torch.from_numpy(cases.bf16_round(x)).cuda().to(torch.bfloat16)
+
+
+@pytest.mark.parametrize("m,n,k", [(128, 256, 64), (128, 256, 256), (8, 10, 512), (64, 512, 784), (200, 1000, 328),
+                                   (1000, 72, 4096), (256, 4096, 4096), (129, 257, 72), (3000, 520, 136)])
+def test_fc_bf16_against_oracle(be, oracle, m, n, k):
+    r = np.random.default_rng(m * 7 + n * 3 + k)
+    a = cases.bf16_round(r.standard_normal((m, k)).astype(np.float32))
+    w = cases.bf16_round((r.standard_normal((k, n)) / np.sqrt(k)).astype(np.float32))
+    bias = (r.standard_normal(n) * 0.1).astype(np.float32)
+    want = oracle.batchedadd_f(oracle.matrixMatrixMul_f(a, w), bias)
+    wp = be.pack_weight_bf16(torch.from_numpy(w).cuda())
+    assert torch.equal(wp.float().cpu(), torch.from_numpy(w).t())  # packing is exact for bf16-representable weights
+    got = be.fc_bf16(_bf16(a), wp, torch.from_numpy(bias).cuda(), swc.ACT_NONE, torch.float32)
+    be.sync()
+    err = np.abs(got.cpu().numpy() - want).max()
+    assert err <= 2e-3, err  # fp32 accumulation of exact products: far inside the 2e-2 bar
+    # fused ReLU + bf16 store
+    got2 = be.fc_bf16(_bf16(a), wp, torch.from_numpy(bias).cuda(), swc.ACT_RELU, torch.bfloat16)
+    be.sync()
+    want2 = cases.bf16_round(np.maximum(want, 0))
+    assert np.abs(got2.float().cpu().numpy() - want2).max() <= 2e-2
+
+
+def test_fc_bf16_rows_are_independent_of_tile_position(be):
+    """Identical input rows placed in different tiles (and so different CTAs, pipeline stages and
+    accumulator buffers) must give identical output rows."""
+    r = np.random.default_rng(3)
+    m, n, k = 128 * 40, 1024, 512
+    base = cases.bf16_round(r.standard_normal((16, k)).astype(np.float32))
+    a = np.tile(base, (m // 16, 1))
+    w = cases.bf16_round((r.standard_normal((k, n)) / np.sqrt(k)).astype(np.float32))
+    wp = be.pack_weight_bf16(torch.from_numpy(w).cuda())
+    got = be.fc_bf16(_bf16(a), wp, None, swc.ACT_NONE, torch.float32)
+    be.sync()
+    g = got.view(m // 16, 16, n)
+    assert torch.equal(g, g[0:1].expand_as(g))
+
+
+def test_matrixMatrixMul_f_in_tensor_core_mode(be, oracle):
+    """The fp32 drop-in entry point with the context in TC_BF16 mode: operands rounded to bf16 on the fly."""
+    r = np.random.default_rng(4)
+    a = r.standard_normal((300, 700)).astype(np.float32)
+    w = (r.standard_normal((700, 260)) / np.sqrt(700)).astype(np.float32)
+    want = oracle.matrixMatrixMul_f(cases.bf16_round(a), cases.bf16_round(w))
+    got = be.matrixMatrixMul_f(torch.from_numpy(a).cuda(), torch.from_numpy(w).cuda())
+    be.sync()
+    assert np.abs(got.cpu().numpy() - want).max() <= 2e-3
+
+
+def test_config3_slice_logits_and_argmax(be, oracle):
+    """256 rows of the wide MLP at full width (4096 -> 4096 x4 -> 1000)."""
+    c = cases.config3_wide_mlp(batch=256)
+    want_logits = cases.wide_mlp_forward(oracle, c, softmax=False)
+    h = _bf16(c["x"])
+    last = len(c["w"]) - 1
+    for i, (w, b) in enumerate(zip(c["w"], c["b"])):
+        wp = be.pack_weight_bf16(torch.from_numpy(w).cuda())
+        bias = torch.from_numpy(b).cuda()
+        if i < last:
+            h = be.fc_bf16(h, wp, bias, swc.ACT_RELU, torch.bfloat16)
+        else:
+            h = be.fc_bf16(h, wp, bias, swc.ACT_NONE, torch.float32)
+    probs = be.matrixSoftmax_f(h)
+    top = be.argMax_i(probs, 1)
+    be.sync()
+    logits = h.cpu().numpy()
+    assert np.abs(logits - want_logits).max() <= 2e-2
+    agree = np.mean(top.cpu().numpy()[:, 0] == oracle.argMax_i(oracle.matrixSoftmax_f(want_logits), 1)[:, 0])
+    assert agree >= 0.999, agree
+
+
+def test_fc_bf16_at_full_config3_size_sampled_rows(be, oracle):
+    """One 65536 x 4096 x 4096 layer; 96 sampled rows are checked against the oracle run on those rows alone."""
+    g = torch.Generator(device="cuda").manual_seed(7)
+    m, n, k = 65536, 4096, 4096
+    a = torch.randn((m, k), generator=g, device="cuda").to(torch.bfloat16)
+    w = (torch.randn((k, n), generator=g, device="cuda") / 64).to(torch.bfloat16).float()
+    bias = torch.randn(n, generator=g, device="cuda") * 0.01
+    wp = be.pack_weight_bf16(w)
+    out = be.fc_bf16(a, wp, bias, swc.ACT_RELU, torch.bfloat16)
+    be.sync()
+    rows = torch.randint(0, m, (96,), generator=torch.Generator().manual_seed(1))
+    rows[0], rows[1] = 0, m - 1
+    a_s = a[rows.cuda()].float().cpu().numpy()
+    want = np.maximum(oracle.batchedadd_f(oracle.matrixMatrixMul_f(a_s, w.cpu().numpy()), bias.cpu().numpy()), 0)
+    got = out[rows.cuda()].float().cpu().numpy()
+    assert np.abs(got - cases.bf16_round(want)).max() <= 2e-2
