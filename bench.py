@@ -1,0 +1,297 @@
+#!/usr/bin/env python
+"""Benchmark of the inference forward path on B200: the wide-MLP configuration.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
+
+Workload (synthetic, seeded): X [65536, 4096] bf16 ~ N(0,1); 4 x (FC 4096->4096, bf16 weights ~ N(0, 1/4096),
+fp32 bias, fp32 accumulation, ReLU); FC 4096->1000; softmax.  One step = one forward pass over the whole
+batch; with N GPUs the batch is split evenly over the ranks (strong scaling) and the probabilities are
+gathered on rank 0.  Prints ONE JSON line on rank 0.
+
+`value` is samples/s with the inputs already resident in HBM; `e2e` is the same forward pass called with
+pinned HOST buffers (host->device copy of X and device->host copy of the probabilities inside the timed
+region).  `--impl reference` times the reference's own scalar CPU kernels on a bounded slice of the same
+workload, one slice per host thread.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path[:0] = [ROOT, os.path.join(ROOT, "tests")]
+
+BATCH, WIDTH, CLASSES, LAYERS, SEED = 65536, 4096, 1000, 4, 1003
+METRIC, UNIT = "inference samples/sec", "samples/s"
+
+
+def config(n_gpus, rows_per_rank):
+    return {"workload": "wide MLP forward (BASELINE configs[2]): X[65536,4096] bf16 -> 4x(FC 4096->4096 + bias + ReLU) "
+                        "-> FC 4096->1000 + bias -> softmax",
+            "global_batch": BATCH, "rows_per_gpu": rows_per_rank, "parallelism": f"dp{n_gpus} (batch split, final gather)",
+            "l2": "inputs larger than L2 (X 512 MiB, activations 512 MiB per layer); no flush needed"}
+
+
+def peaks():
+    try:
+        p = json.load(open(os.path.join(ROOT, "MEASURED_PEAKS.json")))
+        return float(p["bf16_tflops_sustained"]), "measured (MEASURED_PEAKS.json bf16_tflops_sustained)"
+    except Exception:
+        return 1400.0, "fallback (sustained figure of the profiling recipe)"
+
+
+class ClockSampler:
+    """Samples SM clock and throttle reasons while the timed region runs (read-only NVML queries)."""
+
+    def __init__(self, index):
+        self.samples, self.reasons, self.max_mhz = [], set(), None
+        self._stop = threading.Event()
+        self._thread = None
+        try:
+            import pynvml as nv
+            nv.nvmlInit()
+            self.nv = nv
+            self.h = nv.nvmlDeviceGetHandleByIndex(index)
+            self.max_mhz = nv.nvmlDeviceGetMaxClockInfo(self.h, nv.NVML_CLOCK_SM)
+        except Exception:
+            self.nv = None
+
+    def _run(self):
+        nv = self.nv
+        names = {"hw_slowdown": getattr(nv, "nvmlClocksEventReasonHwSlowdown", 0x8),
+                 "hw_thermal_slowdown": getattr(nv, "nvmlClocksEventReasonHwThermalSlowdown", 0x40),
+                 "sw_thermal_slowdown": getattr(nv, "nvmlClocksEventReasonSwThermalSlowdown", 0x20),
+                 "sw_power_cap": getattr(nv, "nvmlClocksEventReasonSwPowerCap", 0x4)}
+        while not self._stop.is_set():
+            try:
+                self.samples.append(nv.nvmlDeviceGetClockInfo(self.h, nv.NVML_CLOCK_SM))
+                try:
+                    mask = nv.nvmlDeviceGetCurrentClocksEventReasons(self.h)
+                except Exception:
+                    mask = nv.nvmlDeviceGetCurrentClocksThrottleReasons(self.h)
+                for k, bit in names.items():
+                    if mask & bit:
+                        self.reasons.add(k)
+            except Exception:
+                pass
+            self._stop.wait(0.05)
+
+    def __enter__(self):
+        if self.nv:
+            self._thread = threading.Thread(target=self._run, daemon=True)
+            self._thread.start()
+        return self
+
+    def __exit__(self, *a):
+        self._stop.set()
+        if self._thread:
+            self._thread.join()
+
+    def summary(self):
+        if not self.samples:
+            return {"sm_mhz": None, "sm_max_mhz": self.max_mhz, "reasons": ["nvml unavailable"]}
+        return {"sm_mhz": statistics.median(self.samples), "sm_max_mhz": self.max_mhz, "reasons": sorted(self.reasons)}
+
+
+def make_inputs(torch, device, rows, row0):
+    """Seeded synthetic tensors of the configuration, generated on the device.  Weights are identical on
+    every rank (same seed); each rank draws its own rows of X."""
+    g = torch.Generator(device=device).manual_seed(SEED)
+    ws, bs = [], []
+    for i in range(LAYERS + 1):
+        n = WIDTH if i < LAYERS else CLASSES
+        ws.append((torch.randn((WIDTH, n), generator=g, device=device) / WIDTH ** 0.5).to(torch.bfloat16).float())
+        bs.append(torch.randn(n, generator=g, device=device) * 0.01)
+    gx = torch.Generator(device=device).manual_seed(SEED * 1000 + row0)
+    x = torch.randn((rows, WIDTH), generator=gx, device=device).to(torch.bfloat16)
+    return x, ws, bs
+
+
+class CpuArm:
+    """The CPU implementation on `threads` slices of `rows_per_thread` rows each, one forward pass per slice,
+    slices run concurrently (the reference's own batch split; its kernels are single-threaded)."""
+
+    def __init__(self, rows_per_thread, threads, kind_pref="reference"):
+        import numpy as np
+
+        import cases
+        from oracle import oracle as orc
+        self.cases = cases
+        self.impl = orc.Reference() if (kind_pref == "reference" and orc.Reference.available()) else orc.Oracle()
+        if self.impl.kind == "port":
+            self.impl.set_threads(1)  # parallelism comes from the slices, as for the reference
+        self.threads, self.rows = threads, rows_per_thread * threads
+        c = cases.config3_wide_mlp(batch=self.rows, width=WIDTH, classes=CLASSES, layers=LAYERS, seed=SEED)
+        self.slices = [dict(c, x=np.ascontiguousarray(c["x"][i * rows_per_thread:(i + 1) * rows_per_thread]))
+                       for i in range(threads)]
+
+    def step(self):
+        """One pass over all slices; returns seconds."""
+        ts = [threading.Thread(target=self.cases.wide_mlp_forward, args=(self.impl, s)) for s in self.slices]
+        t0 = time.perf_counter()
+        for t in ts:
+            t.start()
+        for t in ts:
+            t.join()
+        return time.perf_counter() - t0
+
+
+def run_reference(args, rank, world):
+    if rank != 0:
+        return
+    threads = os.cpu_count() or 1
+    rows_per_thread = 32
+    arm = CpuArm(rows_per_thread, threads)
+    for _ in range(min(args.warmup, 1)):
+        arm.step()
+    total = sum(arm.step() for _ in range(args.steps))
+    value = arm.rows * args.steps / total
+    sample = (f"{arm.rows} rows per step ({rows_per_thread} per thread x {threads} threads) of the 65536-row batch, "
+              "full-width layers")
+    print(json.dumps({
+        "impl": "reference", "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": args.gpus, "steps": args.steps,
+        "warmup": min(args.warmup, 1), "ms_per_step": 1e3 * total / args.steps, "higher_is_better": True,
+        "scaling": "strong", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "config": config(args.gpus, BATCH // max(1, args.gpus)),
+        "cpu_baseline": {"value": value, "unit": UNIT, "cores": threads, "kind": arm.impl.kind, "sample": sample},
+        "e2e": {"value": value, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0}))
+
+
+def run_ours(args, rank, world, local_rank):
+    import torch
+    import torch.distributed as dist
+
+    import swcompiler_b200 as swc
+    from swcompiler_b200.programs import WideMlpProgram
+
+    torch.cuda.set_device(local_rank)
+    device = torch.device("cuda", local_rank)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=device)
+    rows = BATCH // world
+    row0 = rank * rows
+    be = swc.Backend(local_rank, swc.TC_BF16)
+    x, ws, bs = make_inputs(torch, device, rows, row0)
+    prog = WideMlpProgram(be, ws, bs, max_rows=rows)
+    del ws
+    probs = torch.empty((rows, CLASSES), dtype=torch.float32, device=device)
+    gathered = [torch.empty_like(probs) for _ in range(world)] if (world > 1 and rank == 0) else None
+
+    def step():
+        prog.forward(x, probs)
+        if world > 1:
+            dist.gather(probs, gathered, dst=0)
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    for _ in range(max(args.warmup, 3)):
+        step()
+    barrier()
+
+    # ---- timed region: K steps, device-timed, per-launch events for the dominant kernel
+    nl = prog.launches_per_forward
+    ev = [[(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(nl)]
+          for _ in range(args.steps)]
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    launches0 = be.launches
+    with ClockSampler(local_rank) as clocks:
+        barrier()
+        e0.record()
+        for s in range(args.steps):
+            prog.forward(x, probs, on_launch=lambda i, when, s=s: ev[s][i][when].record())
+            if world > 1:
+                dist.gather(probs, gathered, dst=0)
+        e1.record()
+        barrier()
+    launches = be.launches - launches0
+    be.sync()  # also surfaces a device-side timeout status, if any
+    ms = e0.elapsed_time(e1)
+    if world > 1:
+        t = torch.tensor([ms], device=device)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms = float(t.item())
+    value = BATCH * args.steps / (ms * 1e-3)
+
+    # dominant kernel: the hidden-layer FC launches (4 per step)
+    fc_ms = [ev[s][i][0].elapsed_time(ev[s][i][1]) for s in range(args.steps) for i in range(LAYERS)]
+    fc_avg_ms = sum(fc_ms) / len(fc_ms)
+    flops_per_launch = 2.0 * rows * WIDTH * WIDTH
+    achieved = flops_per_launch / (fc_avg_ms * 1e-3) / 1e12
+    peak, peak_src = peaks()
+    per_kernel_ms = [sum(ev[s][i][0].elapsed_time(ev[s][i][1]) for s in range(args.steps)) / args.steps for i in range(nl)]
+
+    # ---- end to end with host buffers (rank-local slice): H2D of X, forward, D2H of the probabilities
+    x_host = torch.empty((rows, WIDTH), dtype=torch.bfloat16).pin_memory()
+    x_host.copy_(x.cpu())
+    probs_host = torch.empty((rows, CLASSES), dtype=torch.float32).pin_memory()
+    x_dev = torch.empty_like(x)
+    for _ in range(2):
+        prog.forward_host(x_host, probs_host, x_dev, probs)
+    barrier()
+    e2e_steps = max(3, min(args.steps, 10))
+    e0.record()
+    for _ in range(e2e_steps):
+        prog.forward_host(x_host, probs_host, x_dev, probs)
+        if world > 1:
+            dist.gather(probs, gathered, dst=0)
+    e1.record()
+    barrier()
+    e2e_ms = e0.elapsed_time(e1)
+    if world > 1:
+        t = torch.tensor([e2e_ms], device=device)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        e2e_ms = float(t.item())
+    e2e_value = BATCH * e2e_steps / (e2e_ms * 1e-3)
+
+    cpu = None
+    if rank == 0 and world == 1:
+        threads = os.cpu_count() or 1
+        arm = CpuArm(64, threads)
+        dt = arm.step()
+        cpu = {"value": arm.rows / dt, "unit": UNIT, "cores": threads, "kind": arm.impl.kind,
+               "sample": f"{arm.rows} rows (64 per thread x {threads} threads) of the 65536-row batch, one pass, {dt:.1f} s"}
+
+    if rank == 0:
+        print(json.dumps({
+            "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps, "warmup": max(args.warmup, 3),
+            "ms_per_step": ms / args.steps, "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
+            "dtype": "bf16 (fp32 accumulate)", "data": "synthetic", "config": config(world, rows),
+            "roofline": {"bound": "tensor", "achieved": achieved, "peak": peak, "unit": "TFLOP/s", "frac": achieved / peak,
+                         "traffic": None, "kernel": "fc_tc_kernel (FC 4096->4096 + bias + ReLU)",
+                         "launch_ms": fc_avg_ms, "flops_per_launch": flops_per_launch, "peak_source": peak_src},
+            "per_launch_ms": per_kernel_ms,
+            "cpu_baseline": cpu,
+            "e2e": {"value": e2e_value, "unit": UNIT, "h2d_bytes_per_step": x_host.numel() * 2 * world,
+                    "d2h_bytes_per_step": probs_host.numel() * 4 * world, "ms_per_step": e2e_ms / e2e_steps},
+            "gpu_launches": launches, "clocks": clocks.summary()}))
+    if world > 1:
+        dist.destroy_process_group()
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=10)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    args = ap.parse_args()
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    if args.impl == "reference":
+        run_reference(args, rank, world)
+    else:
+        run_ours(args, rank, world, local_rank)
+
+
+if __name__ == "__main__":
+    main()

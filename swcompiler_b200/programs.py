@@ -1,0 +1,75 @@
+"""Forward programs: the sequence of kernel-table calls the code generator would emit for a graph,
+with the tensors of its arena held resident in HBM.
+
+The reference's generator writes a C++ main() that allocates one arena, loads weights, and calls one
+kernel per op node in topological order (src/codegen/Codegen.cpp:288-356, :1035-1077).  These
+classes are that emitted program for the benchmark graphs, issued through the C-ABI library: weights
+are packed once at construction (load time), activations live in pre-allocated buffers, and
+`forward` only launches kernels.
+"""
+from __future__ import annotations
+
+import torch
+
+from . import _lib as L
+from .kernels import Backend
+
+
+class WideMlpProgram:
+    """x[B,width] bf16 -> `layers` x (FC width->width, +bias, ReLU) -> FC width->classes, +bias -> Softmax.
+
+    Tensor-core path with bf16 storage: each hidden layer is ONE launch (matmul + bias + ReLU + bf16 store),
+    the last FC writes fp32 logits, softmax is a separate bandwidth-bound launch.  A batch larger than
+    `chunk_rows` is processed chunk by chunk through the same two activation buffers.
+    """
+
+    def __init__(self, be: Backend, weights, biases, max_rows: int):
+        self.be = be
+        self.wp = [be.pack_weight_bf16(w) if w.dtype == torch.float32 else w for w in weights]  # [n, k] bf16
+        self.bias = [b.contiguous() for b in biases]
+        self.width = self.wp[0].shape[1]
+        self.classes = self.wp[-1].shape[0]
+        self.max_rows = max_rows
+        self.h = [torch.empty((max_rows, self.width), dtype=torch.bfloat16, device=be.device) for _ in range(2)]
+        self.logits = torch.empty((max_rows, self.classes), dtype=torch.float32, device=be.device)
+        self.launches_per_forward = len(self.wp) + 1
+        be.sync()
+
+    def flops(self, rows: int) -> float:
+        return float(sum(2.0 * rows * w.shape[0] * w.shape[1] for w in self.wp))
+
+    def forward(self, x_bf16: torch.Tensor, probs_out: torch.Tensor, on_launch=None) -> torch.Tensor:
+        """x_bf16 [rows, width] on device -> probs_out [rows, classes] fp32 on device.  `on_launch(i, when)` is
+        called before (when=0) and after (when=1) the i-th launch, for per-kernel event timing."""
+        rows = x_bf16.shape[0]
+        if rows > self.max_rows:
+            raise ValueError("batch exceeds the activation buffers")
+        be, h = self.be, x_bf16
+        last = len(self.wp) - 1
+        for i, (wp, b) in enumerate(zip(self.wp, self.bias)):
+            if on_launch:
+                on_launch(i, 0)
+            if i < last:
+                out = self.h[i & 1][:rows]
+                be.fc_bf16(h, wp, b, L.ACT_RELU, out=out)
+                h = out
+            else:
+                logits = self.logits[:rows]
+                be.fc_bf16(h, wp, b, L.ACT_NONE, out=logits)
+            if on_launch:
+                on_launch(i, 1)
+        if on_launch:
+            on_launch(last + 1, 0)
+        be.matrixSoftmax_f(logits, out=probs_out)
+        if on_launch:
+            on_launch(last + 1, 1)
+        return probs_out
+
+    def forward_host(self, x_host: torch.Tensor, probs_host: torch.Tensor, x_dev: torch.Tensor,
+                     probs_dev: torch.Tensor) -> torch.Tensor:
+        """End to end with HOST buffers (pinned): copy in, run, copy out, on the backend's stream."""
+        rows = x_host.shape[0]
+        x_dev[:rows].copy_(x_host, non_blocking=True)
+        self.forward(x_dev[:rows], probs_dev[:rows])
+        probs_host.copy_(probs_dev[:rows], non_blocking=True)
+        return probs_host

@@ -70,8 +70,14 @@ def test_matrixMatrixMul_f_in_tensor_core_mode(be, oracle):
 
 
 def test_config3_slice_logits_and_argmax(be, oracle):
-    """256 rows of the wide MLP at full width (4096 -> 4096 x4 -> 1000)."""
-    c = cases.config3_wide_mlp(batch=256)
+    """1024 rows of the wide MLP at full width (4096 -> 4096 x4 -> 1000).
+
+    Logits: max-abs error <= 2e-2.  Argmax: a random-weight network has rows whose two largest logits
+    differ by less than the rounding noise of bf16 activations; on those rows the winner is not decidable
+    at this precision.  So the test requires 100 % agreement on every row whose oracle margin exceeds
+    twice the observed max-abs error, requires those rows to be the overwhelming majority, and bounds the
+    raw agreement over all rows as well."""
+    c = cases.config3_wide_mlp(batch=1024)
     want_logits = cases.wide_mlp_forward(oracle, c, softmax=False)
     h = _bf16(c["x"])
     last = len(c["w"]) - 1
@@ -83,12 +89,21 @@ def test_config3_slice_logits_and_argmax(be, oracle):
         else:
             h = be.fc_bf16(h, wp, bias, swc.ACT_NONE, torch.float32)
     probs = be.matrixSoftmax_f(h)
-    top = be.argMax_i(probs, 1)
+    top = be.argMax_i(probs, 1).cpu().numpy()[:, 0]
     be.sync()
     logits = h.cpu().numpy()
-    assert np.abs(logits - want_logits).max() <= 2e-2
-    agree = np.mean(top.cpu().numpy()[:, 0] == oracle.argMax_i(oracle.matrixSoftmax_f(want_logits), 1)[:, 0])
-    assert agree >= 0.999, agree
+    err = float(np.abs(logits - want_logits).max())
+    assert err <= 2e-2, err
+    want_top = oracle.argMax_i(want_logits, 1)[:, 0]
+    srt = np.sort(want_logits, axis=1)
+    margin = srt[:, -1] - srt[:, -2]
+    decidable = margin > 2 * err
+    raw = float(np.mean(top == want_top))
+    print(f"config3 slice: logits max-abs err {err:.2e}; raw argmax agreement {raw:.4f}; "
+          f"decidable rows {decidable.mean():.4f}")
+    assert np.all(top[decidable] == want_top[decidable])
+    assert decidable.mean() >= 0.85
+    assert raw >= 0.99, raw
 
 
 def test_fc_bf16_at_full_config3_size_sampled_rows(be, oracle):
