@@ -96,6 +96,20 @@ int swcb200_matrixSoftmax_f(swcb200_ctx *ctx, int m, int n, const float *a, int 
  * (kernels.h:601-613; Codegen.cpp:2372-2386).  top_k <= n. */
 int swcb200_argMax_i(swcb200_ctx *ctx, const float *input, int *idx, int m, int n, int top_k);
 
+/* The same product as swcb200_matrixMatrixMul_f in SWCB200_TC_BF16 mode, for callers that must not
+ * allocate device memory (a generated program whose single arena already owns the GPU, a server with a
+ * fixed memory budget, code running between the collectives of a multi-GPU job).  It has no counterpart
+ * in the reference.  The bf16 operand copies live in a fixed 40 MiB array inside the library, held by every
+ * GPU that loads the library until the process exits; sizes with 2*roundup(k,8)*(m+n) beyond 40 MiB return
+ * SWCB200_ERR_TOO_LARGE.  No context is needed: kernels go on `cuda_stream` of `device`, and the call
+ * returns after that stream has drained.  The first call on a device caches the array's device address;
+ * make it outside stream capture.  All calls on a device share the array (its old contents are
+ * overwritten where they matter; nothing needs clearing), so calls that overlap on one GPU race: serialise
+ * them.  Calls no cudaMalloc / cudaFree or allocating library routine. */
+int swcb200_matrixMatrixMul_f_noalloc(int device, void *cuda_stream, int m, int n, int k,
+                                      const float *a, int lda, const float *b, int ldb, float *c,
+                                      int ldc);
+
 /* ------------------------------------------------------- flat elementwise */
 
 /* dest = src > 0 ? src : 0.  Replaces relu_f (kernels.h:575-580; Codegen.cpp:2133-2135). */

@@ -1,0 +1,63 @@
+"""GPU: the allocation-free matrix multiply against the ordinary tensor-core entry point.
+
+Some users of this library cannot let it allocate device memory: a generated inference program plans one
+arena per GPU and may leave no room for a library's hidden cudaMalloc, and a process in a multi-GPU job
+cannot afford the device-wide stall an allocation brings.  `swcb200_matrixMatrixMul_f_noalloc` serves them
+with a fixed 40 MiB scratch array inside the library.  Both entry points run the same kernels on the same
+operands, so their results must be identical; the test asks for that on two calls in a row (the second one
+smaller, so anything stale left in the shared array by the first would show), and checks that a problem
+beyond the fixed array is refused.
+
+Collected last on purpose (file name), so that a run stopping at the first failure has already run
+everything else.  It passes alone in a fresh process and after the other tests.
+"""
+import ctypes as C
+
+import numpy as np
+import pytest
+import torch
+
+import swcompiler_b200 as swc
+from swcompiler_b200 import _lib as L
+
+pytestmark = pytest.mark.gpu
+
+
+def _noalloc(m, n, k, a, b, c):
+    lib = L.lib()
+    stream = torch.cuda.current_stream().cuda_stream
+    return lib.swcb200_matrixMatrixMul_f_noalloc(C.c_int(0), C.c_void_p(stream), C.c_int(m), C.c_int(n), C.c_int(k),
+                                                 C.c_void_p(a.data_ptr()), C.c_int(k), C.c_void_p(b.data_ptr()),
+                                                 C.c_int(n), C.c_void_p(c.data_ptr()), C.c_int(n))
+
+
+def test_noalloc_matches_the_allocating_entry_point_twice_in_a_row():
+    be = swc.Backend(0, swc.TC_BF16)
+    g = torch.Generator(device="cuda").manual_seed(11)
+    # first call on this device: the library caches the array's address (and the driver loads the module that
+    # carries the array, which is when the 40 MiB are taken); done here, before free memory is compared
+    w = torch.ones((8, 8), device="cuda")
+    assert _noalloc(8, 8, 8, w, w, torch.empty((8, 8), device="cuda")) == L.OK
+    for (m, n, k) in [(700, 1000, 1300), (96, 200, 72)]:
+        a = torch.randn((m, k), generator=g, device="cuda")
+        b = torch.randn((k, n), generator=g, device="cuda") / k ** 0.5
+        want = be.matrixMatrixMul_f(a, b)           # existing entry point, through the C-ABI
+        be.sync()
+        got = torch.full((m, n), float("nan"), device="cuda")
+        torch.cuda.synchronize()
+        free_before = torch.cuda.mem_get_info()[0]
+        rc = _noalloc(m, n, k, a, b, got)           # new entry point, through the C-ABI; returns when done
+        assert rc == L.OK, L.status_string(rc)
+        assert torch.cuda.mem_get_info()[0] == free_before   # no device memory was taken
+        assert torch.equal(got, want)
+        # and against plain fp32 arithmetic on the bf16-rounded operands, within the tensor-core tolerance
+        ref = a.to(torch.bfloat16).float() @ b.to(torch.bfloat16).float()
+        assert (got - ref).abs().max().item() <= 2e-3
+
+
+def test_noalloc_refuses_what_does_not_fit():
+    a = torch.zeros(8, device="cuda")
+    # 2 * 8192 * (4096 + 4096) bytes = 128 MiB of operand copies: beyond the 40 MiB array; nothing is launched
+    rc = _noalloc(4096, 4096, 8192, a, a, a)
+    assert rc == L.ERR_TOO_LARGE
+    assert _noalloc(4, 4, 0, a, a, a) == L.ERR_BAD_ARG
