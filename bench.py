@@ -229,7 +229,42 @@ def run_ours(args, rank, world, local_rank):
     peak, peak_src = peaks()
     per_kernel_ms = [sum(ev[s][i][0].elapsed_time(ev[s][i][1]) for s in range(args.steps)) / args.steps for i in range(nl)]
 
-    # ---- end to end with host buffers (rank-local slice): H2D of X, forward, D2H of the probabilities
+    e2e_value = e2e_ms = None
+    e2e_steps = max(3, min(args.steps, 10))
+    x_host = probs_host = None
+    if not args.skip_e2e:
+        e2e_value, e2e_ms, x_host, probs_host = run_e2e(torch, dist, prog, x, probs, gathered, world, device, rows,
+                                                        e2e_steps, barrier)
+
+    cpu = None
+    if rank == 0 and world == 1 and not args.skip_cpu_baseline:
+        threads = os.cpu_count() or 1
+        arm = CpuArm(64, threads)
+        dt = arm.step()
+        cpu = {"value": arm.rows / dt, "unit": UNIT, "cores": threads, "kind": arm.impl.kind,
+               "sample": f"{arm.rows} rows (64 per thread x {threads} threads) of the 65536-row batch, one pass, {dt:.1f} s"}
+
+    if rank == 0:
+        e2e = None if e2e_value is None else {
+            "value": e2e_value, "unit": UNIT, "h2d_bytes_per_step": x_host.numel() * 2 * world,
+            "d2h_bytes_per_step": probs_host.numel() * 4 * world, "ms_per_step": e2e_ms / e2e_steps}
+        print(json.dumps({
+            "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps, "warmup": max(args.warmup, 3),
+            "ms_per_step": ms / args.steps, "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
+            "dtype": "bf16 (fp32 accumulate)", "data": "synthetic", "config": config(world, rows),
+            "roofline": {"bound": "tensor", "achieved": achieved, "peak": peak, "unit": "TFLOP/s", "frac": achieved / peak,
+                         "traffic": None, "kernel": "fc_tc_kernel (FC 4096->4096 + bias + ReLU)",
+                         "launch_ms": fc_avg_ms, "flops_per_launch": flops_per_launch, "peak_source": peak_src},
+            "per_launch_ms": per_kernel_ms,
+            "cpu_baseline": cpu, "e2e": e2e,
+            "gpu_launches": launches, "clocks": clocks.summary()}))
+    if world > 1:
+        dist.destroy_process_group()
+
+
+def run_e2e(torch, dist, prog, x, probs, gathered, world, device, rows, e2e_steps, barrier):
+    """End to end with host buffers (rank-local slice): H2D of X, forward, D2H of the probabilities."""
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     x_host = torch.empty((rows, WIDTH), dtype=torch.bfloat16).pin_memory()
     x_host.copy_(x.cpu())
     probs_host = torch.empty((rows, CLASSES), dtype=torch.float32).pin_memory()
@@ -237,7 +272,6 @@ def run_ours(args, rank, world, local_rank):
     for _ in range(2):
         prog.forward_host(x_host, probs_host, x_dev, probs)
     barrier()
-    e2e_steps = max(3, min(args.steps, 10))
     e0.record()
     for _ in range(e2e_steps):
         prog.forward_host(x_host, probs_host, x_dev, probs)
@@ -251,39 +285,21 @@ def run_ours(args, rank, world, local_rank):
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         e2e_ms = float(t.item())
     e2e_value = BATCH * e2e_steps / (e2e_ms * 1e-3)
-
-    cpu = None
-    if rank == 0 and world == 1:
-        threads = os.cpu_count() or 1
-        arm = CpuArm(64, threads)
-        dt = arm.step()
-        cpu = {"value": arm.rows / dt, "unit": UNIT, "cores": threads, "kind": arm.impl.kind,
-               "sample": f"{arm.rows} rows (64 per thread x {threads} threads) of the 65536-row batch, one pass, {dt:.1f} s"}
-
-    if rank == 0:
-        print(json.dumps({
-            "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps, "warmup": max(args.warmup, 3),
-            "ms_per_step": ms / args.steps, "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
-            "dtype": "bf16 (fp32 accumulate)", "data": "synthetic", "config": config(world, rows),
-            "roofline": {"bound": "tensor", "achieved": achieved, "peak": peak, "unit": "TFLOP/s", "frac": achieved / peak,
-                         "traffic": None, "kernel": "fc_tc_kernel (FC 4096->4096 + bias + ReLU)",
-                         "launch_ms": fc_avg_ms, "flops_per_launch": flops_per_launch, "peak_source": peak_src},
-            "per_launch_ms": per_kernel_ms,
-            "cpu_baseline": cpu,
-            "e2e": {"value": e2e_value, "unit": UNIT, "h2d_bytes_per_step": x_host.numel() * 2 * world,
-                    "d2h_bytes_per_step": probs_host.numel() * 4 * world, "ms_per_step": e2e_ms / e2e_steps},
-            "gpu_launches": launches, "clocks": clocks.summary()}))
-    if world > 1:
-        dist.destroy_process_group()
+    return e2e_value, e2e_ms, x_host, probs_host
 
 
 def main():
+    global BATCH
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=10)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--batch", type=int, default=BATCH, help="rows in the whole job (smaller only for profiler captures)")
+    ap.add_argument("--skip-cpu-baseline", action="store_true", help="leave the CPU sample out (profiler captures)")
+    ap.add_argument("--skip-e2e", action="store_true", help="leave the host-buffer pass out (profiler captures)")
     args = ap.parse_args()
+    BATCH = args.batch
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))

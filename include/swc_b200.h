@@ -171,6 +171,43 @@ int swcb200_maxpool_bf16(swcb200_ctx *ctx, const void *input, void *output, cons
                          const size_t *odims, const size_t *kernels, const size_t *strides,
                          const size_t *pads);
 
+/* ---------------------------------------------------- partitioned graphs
+ * NCCL over NVLink in place of the MPI text ParallelCodegen prints
+ * (src/codegen/ParallelCodegen.cpp:457-896).  One process per GPU.  `axis` follows the
+ * reference's tiling labels (src/parallel/TilingLabel.h): >= 0 splits that axis evenly over
+ * the ranks, -1 replicates.  Root is rank 0 in the reference (master/worker); it is a
+ * parameter here. */
+
+#define SWCB200_UNIQUE_ID_BYTES 128
+/* Path of libnccl.so.2 to dlopen (NULL: the loader's default search). Call before comm_init. */
+int swcb200_comm_load(const char *libnccl_path);
+int swcb200_comm_unique_id(void *id_out /* SWCB200_UNIQUE_ID_BYTES */);
+/* Replaces MPI_Init/Comm_size/Comm_rank (ParallelCodegen.cpp:94-112). */
+int swcb200_comm_init(swcb200_ctx *ctx, const void *unique_id, int nranks, int rank);
+int swcb200_comm_destroy(swcb200_ctx *ctx);
+int swcb200_comm_rank(swcb200_ctx *ctx, int *rank, int *nranks);
+/* Scatter node (ParallelCodegen.cpp:457-575): axis -1 = MPI_Bcast; axis >= 0 = each rank gets
+ * its slice of `src` (read on root only) packed contiguously into `dst`. */
+int swcb200_scatter(swcb200_ctx *ctx, const void *src, void *dst, const size_t *dims, int ndim,
+                    int axis, int dtype, int root);
+/* Gather node (:576-682): inverse of scatter; `dst` is written on root only. */
+int swcb200_gather(swcb200_ctx *ctx, const void *src, void *dst, const size_t *dims, int ndim,
+                   int axis, int dtype, int root);
+/* Reduce node (:873-896): dst(root) = sum over ranks of src. */
+int swcb200_reduce_sum(swcb200_ctx *ctx, const void *src, void *dst, size_t count, int dtype,
+                       int root);
+/* Same sum, result on every rank (what the row-split FC pair needs before its next layer). */
+int swcb200_allreduce_sum(swcb200_ctx *ctx, const void *src, void *dst, size_t count, int dtype);
+/* Gather along axis 0 with the result on every rank. */
+int swcb200_allgather(swcb200_ctx *ctx, const void *src, void *dst, size_t count_per_rank,
+                      int dtype);
+/* Transform node (:685-871): re-tile a 2-D tensor [R, C] from pre_axis to post_axis.  Axes: 0 / 1 =
+ * split along rows / columns (shards packed), -1 = whole tensor on every rank, -2 (pre only) = a
+ * full-size partial sum on every rank.  i -> j is an all-to-all, -2 -> j a reduce(-scatter), -1 -> j a
+ * local slice, j -> -1 an all-gather. */
+int swcb200_transform(swcb200_ctx *ctx, const void *src, void *dst, const size_t *dims, int ndim,
+                      int pre_axis, int post_axis, int dtype);
+
 #ifdef __cplusplus
 }
 #endif

@@ -1,0 +1,423 @@
+// Partitioned graphs: the reference's Scatter / Gather / Reduce / Transform nodes over NCCL.
+//
+// ParallelCodegen prints MPI text for these nodes (src/codegen/ParallelCodegen.cpp:457-896):
+// MPI_Bcast or MPI_Type_vector + MPI_Send/Recv for Scatter, the mirror image for Gather, MPI_Reduce for
+// Reduce, a ring of MPI_Sendrecv for Transform.  Here each becomes NCCL calls on the context's stream,
+// one process per GPU.  NCCL is loaded with dlopen, so the library has no link-time dependency on it
+// and a single-GPU user never needs it.
+//
+// Tiling convention (src/parallel/TilingLabel.h, src/codegen/ParallelCodegen.cpp:503-521): splitting a
+// tensor of shape dims[] along `axis` over p ranks views it as `outer` rows of `inner` elements,
+// outer = prod(dims[<axis]), inner = prod(dims[>=axis]); rank r owns, of every row, the block
+// [r*inner/p, (r+1)*inner/p), and stores its shard packed ([outer, inner/p], leading dimension
+// inner/p).  axis 0 shards are contiguous in the full tensor; other axes are strided and go through a
+// staging block (the context's scratch) packed and unpacked with strided device copies.
+#include <dlfcn.h>
+
+#include <mutex>
+
+#include "common.cuh"
+
+namespace {
+
+typedef void *ncclComm_t;
+struct ncclUniqueId {
+    char internal[SWCB200_UNIQUE_ID_BYTES];
+};
+enum { ncclSuccess = 0, ncclInProgress = 7 };
+enum { ncclSum = 0 };
+enum { ncclInt32 = 2, ncclFloat32 = 7, ncclBfloat16 = 9 };
+
+struct NcclApi {
+    void *handle = nullptr;
+    int (*GetUniqueId)(ncclUniqueId *) = nullptr;
+    int (*CommInitRank)(ncclComm_t *, int, ncclUniqueId, int) = nullptr;
+    int (*CommDestroy)(ncclComm_t) = nullptr;
+    int (*CommAbort)(ncclComm_t) = nullptr;
+    int (*CommGetAsyncError)(ncclComm_t, int *) = nullptr;
+    const char *(*GetErrorString)(int) = nullptr;
+    int (*Broadcast)(const void *, void *, size_t, int, int, ncclComm_t, cudaStream_t) = nullptr;
+    int (*AllReduce)(const void *, void *, size_t, int, int, ncclComm_t, cudaStream_t) = nullptr;
+    int (*Reduce)(const void *, void *, size_t, int, int, int, ncclComm_t, cudaStream_t) = nullptr;
+    int (*ReduceScatter)(const void *, void *, size_t, int, int, ncclComm_t, cudaStream_t) = nullptr;
+    int (*AllGather)(const void *, void *, size_t, int, ncclComm_t, cudaStream_t) = nullptr;
+    int (*Send)(const void *, size_t, int, int, ncclComm_t, cudaStream_t) = nullptr;
+    int (*Recv)(void *, size_t, int, int, ncclComm_t, cudaStream_t) = nullptr;
+    int (*GroupStart)() = nullptr;
+    int (*GroupEnd)() = nullptr;
+};
+NcclApi g_nccl;
+std::mutex g_nccl_mutex;
+
+int load_nccl(const char *path) {
+    std::lock_guard<std::mutex> lock(g_nccl_mutex);
+    if (g_nccl.handle) return SWCB200_OK;
+    void *h = dlopen(path ? path : "libnccl.so.2", RTLD_NOW | RTLD_GLOBAL);
+    if (!h && !path) h = dlopen("libnccl.so", RTLD_NOW | RTLD_GLOBAL);
+    if (!h) return SWCB200_ERR_NCCL;
+#define SWC_SYM(field, name)                                        \
+    *(void **)(&g_nccl.field) = dlsym(h, name);                     \
+    if (!g_nccl.field) {                                            \
+        dlclose(h);                                                 \
+        return SWCB200_ERR_NCCL;                                    \
+    }
+    SWC_SYM(GetUniqueId, "ncclGetUniqueId")
+    SWC_SYM(CommInitRank, "ncclCommInitRank")
+    SWC_SYM(CommDestroy, "ncclCommDestroy")
+    SWC_SYM(CommAbort, "ncclCommAbort")
+    SWC_SYM(CommGetAsyncError, "ncclCommGetAsyncError")
+    SWC_SYM(GetErrorString, "ncclGetErrorString")
+    SWC_SYM(Broadcast, "ncclBroadcast")
+    SWC_SYM(AllReduce, "ncclAllReduce")
+    SWC_SYM(Reduce, "ncclReduce")
+    SWC_SYM(ReduceScatter, "ncclReduceScatter")
+    SWC_SYM(AllGather, "ncclAllGather")
+    SWC_SYM(Send, "ncclSend")
+    SWC_SYM(Recv, "ncclRecv")
+    SWC_SYM(GroupStart, "ncclGroupStart")
+    SWC_SYM(GroupEnd, "ncclGroupEnd")
+#undef SWC_SYM
+    g_nccl.handle = h;
+    return SWCB200_OK;
+}
+
+}  // namespace
+
+struct swcb200_comm {
+    ncclComm_t comm = nullptr;
+    int rank = 0, nranks = 1;
+};
+
+namespace {
+
+#define SWC_NCCL(ctx, call)                                                                              \
+    do {                                                                                                 \
+        int r__ = (call);                                                                                \
+        if (r__ != ncclSuccess)                                                                          \
+            return swc_fail((ctx), SWCB200_ERR_NCCL, "%s: %s", #call, g_nccl.GetErrorString(r__));       \
+    } while (0)
+
+int nccl_type(int dtype, size_t *elem) {
+    switch (dtype) {
+        case SWCB200_F32: *elem = 4; return ncclFloat32;
+        case SWCB200_BF16: *elem = 2; return ncclBfloat16;
+        case SWCB200_I32: *elem = 4; return ncclInt32;
+        default: *elem = 0; return -1;
+    }
+}
+
+struct Tiling {
+    size_t outer, inner, blk, elem;
+    int type;
+};
+
+int make_tiling(swcb200_ctx *ctx, const char *what, const size_t *dims, int ndim, int axis, int dtype, Tiling *t) {
+    SWC_REQUIRE(ctx, ctx->comm != nullptr, SWCB200_ERR_NCCL, "%s: no communicator (call swcb200_comm_init)", what);
+    SWC_REQUIRE(ctx, dims && ndim >= 1 && ndim <= 8, SWCB200_ERR_BAD_ARG, "%s: bad dims", what);
+    SWC_REQUIRE(ctx, axis >= -1 && axis < ndim, SWCB200_ERR_BAD_ARG, "%s: axis %d outside [-1, %d)", what, axis, ndim);
+    t->type = nccl_type(dtype, &t->elem);
+    SWC_REQUIRE(ctx, t->type >= 0, SWCB200_ERR_BAD_ARG, "%s: unknown dtype %d", what, dtype);
+    t->outer = 1;
+    t->inner = 1;
+    for (int d = 0; d < ndim; d++) {
+        if (axis >= 0 && d < axis)
+            t->outer *= dims[d];
+        else
+            t->inner *= dims[d];
+    }
+    const size_t p = (size_t)ctx->comm->nranks;
+    if (axis >= 0) {
+        // the tiling pass only picks strategies with dim % p == 0 (src/pass/ParallelLabelingPass.h:95-135)
+        SWC_REQUIRE(ctx, dims[axis] % p == 0, SWCB200_ERR_BAD_SHAPE, "%s: dims[%d] = %zu not divisible by %zu ranks", what,
+                    axis, dims[axis], p);
+        t->blk = t->inner / p;
+    } else {
+        t->blk = t->inner;
+    }
+    return SWCB200_OK;
+}
+
+// strided [outer x blk] window of a row-major [outer x inner] matrix <-> packed [outer x blk]
+int copy_window(swcb200_ctx *ctx, void *dst, size_t dst_pitch_elems, const void *src, size_t src_pitch_elems, size_t blk,
+                size_t outer, size_t elem) {
+    SWC_CUDA(ctx, cudaMemcpy2DAsync(dst, dst_pitch_elems * elem, src, src_pitch_elems * elem, blk * elem, outer,
+                                    cudaMemcpyDeviceToDevice, ctx->stream));
+    return SWCB200_OK;
+}
+
+}  // namespace
+
+SWC_EXPORT int swcb200_comm_load(const char *libnccl_path) { return load_nccl(libnccl_path); }
+
+SWC_EXPORT int swcb200_comm_unique_id(void *id_out) {
+    if (!id_out) return SWCB200_ERR_BAD_ARG;
+    int rc = load_nccl(nullptr);
+    if (rc) return rc;
+    ncclUniqueId id;
+    if (g_nccl.GetUniqueId(&id) != ncclSuccess) return SWCB200_ERR_NCCL;
+    memcpy(id_out, &id, sizeof(id));
+    return SWCB200_OK;
+}
+
+SWC_EXPORT int swcb200_comm_init(swcb200_ctx *ctx, const void *unique_id, int nranks, int rank) {
+    SWC_CTX(ctx);
+    SWC_REQUIRE(ctx, unique_id && nranks >= 1 && rank >= 0 && rank < nranks, SWCB200_ERR_BAD_ARG, "comm_init: bad argument");
+    SWC_REQUIRE(ctx, ctx->comm == nullptr, SWCB200_ERR_BAD_ARG, "comm_init: context already has a communicator");
+    int rc = load_nccl(nullptr);
+    SWC_REQUIRE(ctx, rc == SWCB200_OK, SWCB200_ERR_NCCL, "comm_init: libnccl.so.2 could not be loaded (%s)", dlerror());
+    ncclUniqueId id;
+    memcpy(&id, unique_id, sizeof(id));
+    swcb200_comm *c = new swcb200_comm();
+    c->rank = rank;
+    c->nranks = nranks;
+    int r = g_nccl.CommInitRank(&c->comm, nranks, id, rank);
+    if (r != ncclSuccess) {
+        delete c;
+        return swc_fail(ctx, SWCB200_ERR_NCCL, "ncclCommInitRank: %s", g_nccl.GetErrorString(r));
+    }
+    ctx->comm = c;
+    return SWCB200_OK;
+}
+
+SWC_EXPORT int swcb200_comm_destroy(swcb200_ctx *ctx) {
+    if (!ctx) return SWCB200_ERR_BAD_ARG;
+    if (!ctx->comm) return SWCB200_OK;
+    cudaSetDevice(ctx->device);
+    cudaStreamSynchronize(ctx->stream);
+    int r = g_nccl.CommDestroy(ctx->comm->comm);
+    delete ctx->comm;
+    ctx->comm = nullptr;
+    return r == ncclSuccess ? SWCB200_OK : SWCB200_ERR_NCCL;
+}
+
+SWC_EXPORT int swcb200_comm_rank(swcb200_ctx *ctx, int *rank, int *nranks) {
+    if (!ctx || !ctx->comm) return SWCB200_ERR_BAD_ARG;
+    if (rank) *rank = ctx->comm->rank;
+    if (nranks) *nranks = ctx->comm->nranks;
+    return SWCB200_OK;
+}
+
+SWC_EXPORT int swcb200_scatter(swcb200_ctx *ctx, const void *src, void *dst, const size_t *dims, int ndim, int axis,
+                               int dtype, int root) {
+    SWC_CTX(ctx);
+    Tiling t;
+    int rc = make_tiling(ctx, "scatter", dims, ndim, axis, dtype, &t);
+    if (rc) return rc;
+    swcb200_comm *c = ctx->comm;
+    SWC_REQUIRE(ctx, root >= 0 && root < c->nranks, SWCB200_ERR_BAD_ARG, "scatter: bad root");
+    SWC_REQUIRE(ctx, dst && (c->rank != root || src), SWCB200_ERR_BAD_ARG, "scatter: null tensor");
+    const size_t shard = t.outer * t.blk;
+    if (shard == 0) return SWCB200_OK;
+    if (axis < 0) {  // replicate: MPI_Bcast in the reference (ParallelCodegen.cpp:488-495)
+        SWC_NCCL(ctx, g_nccl.Broadcast(c->rank == root ? src : dst, dst, shard, t.type, root, c->comm, ctx->stream));
+        return SWCB200_OK;
+    }
+    const uint8_t *send_base = (const uint8_t *)src;
+    if (c->rank == root && t.outer > 1) {
+        // strided shards: pack every peer's window into the staging block first
+        void *stage = nullptr;
+        rc = swc_scratch(ctx, shard * t.elem * c->nranks, &stage);
+        if (rc) return rc;
+        for (int r = 0; r < c->nranks; r++) {
+            if (r == root) continue;
+            rc = copy_window(ctx, (uint8_t *)stage + (size_t)r * shard * t.elem, t.blk,
+                             (const uint8_t *)src + (size_t)r * t.blk * t.elem, t.inner, t.blk, t.outer, t.elem);
+            if (rc) return rc;
+        }
+        send_base = (const uint8_t *)stage;
+    }
+    SWC_NCCL(ctx, g_nccl.GroupStart());
+    if (c->rank == root) {
+        for (int r = 0; r < c->nranks; r++)
+            if (r != root)
+                SWC_NCCL(ctx, g_nccl.Send(send_base + (size_t)r * shard * t.elem, shard, t.type, r, c->comm, ctx->stream));
+    } else {
+        SWC_NCCL(ctx, g_nccl.Recv(dst, shard, t.type, root, c->comm, ctx->stream));
+    }
+    SWC_NCCL(ctx, g_nccl.GroupEnd());
+    if (c->rank == root)  // root's own shard: a local copy
+        return copy_window(ctx, dst, t.blk, (const uint8_t *)src + (size_t)root * t.blk * t.elem, t.inner, t.blk, t.outer,
+                           t.elem);
+    return SWCB200_OK;
+}
+
+SWC_EXPORT int swcb200_gather(swcb200_ctx *ctx, const void *src, void *dst, const size_t *dims, int ndim, int axis,
+                              int dtype, int root) {
+    SWC_CTX(ctx);
+    Tiling t;
+    int rc = make_tiling(ctx, "gather", dims, ndim, axis, dtype, &t);
+    if (rc) return rc;
+    swcb200_comm *c = ctx->comm;
+    SWC_REQUIRE(ctx, root >= 0 && root < c->nranks, SWCB200_ERR_BAD_ARG, "gather: bad root");
+    SWC_REQUIRE(ctx, src && (c->rank != root || dst), SWCB200_ERR_BAD_ARG, "gather: null tensor");
+    const size_t shard = t.outer * t.blk;
+    if (shard == 0) return SWCB200_OK;
+    if (axis < 0) {  // a replicated tensor: root already has it
+        if (c->rank == root && dst != src)
+            SWC_CUDA(ctx, cudaMemcpyAsync(dst, src, shard * t.elem, cudaMemcpyDeviceToDevice, ctx->stream));
+        return SWCB200_OK;
+    }
+    uint8_t *recv_base = (uint8_t *)dst;
+    const bool staged = c->rank == root && t.outer > 1;
+    if (staged) {
+        void *stage = nullptr;
+        rc = swc_scratch(ctx, shard * t.elem * c->nranks, &stage);
+        if (rc) return rc;
+        recv_base = (uint8_t *)stage;
+    }
+    SWC_NCCL(ctx, g_nccl.GroupStart());
+    if (c->rank == root) {
+        for (int r = 0; r < c->nranks; r++)
+            if (r != root)
+                SWC_NCCL(ctx, g_nccl.Recv(recv_base + (size_t)r * shard * t.elem, shard, t.type, r, c->comm, ctx->stream));
+    } else {
+        SWC_NCCL(ctx, g_nccl.Send(src, shard, t.type, root, c->comm, ctx->stream));
+    }
+    SWC_NCCL(ctx, g_nccl.GroupEnd());
+    if (c->rank == root) {
+        rc = copy_window(ctx, (uint8_t *)dst + (size_t)root * t.blk * t.elem, t.inner, src, t.blk, t.blk, t.outer, t.elem);
+        if (rc) return rc;
+        if (staged)
+            for (int r = 0; r < c->nranks; r++) {
+                if (r == root) continue;
+                rc = copy_window(ctx, (uint8_t *)dst + (size_t)r * t.blk * t.elem, t.inner,
+                                 recv_base + (size_t)r * shard * t.elem, t.blk, t.blk, t.outer, t.elem);
+                if (rc) return rc;
+            }
+    }
+    return SWCB200_OK;
+}
+
+SWC_EXPORT int swcb200_reduce_sum(swcb200_ctx *ctx, const void *src, void *dst, size_t count, int dtype, int root) {
+    SWC_CTX(ctx);
+    SWC_REQUIRE(ctx, ctx->comm != nullptr, SWCB200_ERR_NCCL, "reduce_sum: no communicator");
+    size_t elem;
+    int type = nccl_type(dtype, &elem);
+    SWC_REQUIRE(ctx, type >= 0, SWCB200_ERR_BAD_ARG, "reduce_sum: unknown dtype");
+    SWC_REQUIRE(ctx, root >= 0 && root < ctx->comm->nranks, SWCB200_ERR_BAD_ARG, "reduce_sum: bad root");
+    if (count == 0) return SWCB200_OK;
+    SWC_REQUIRE(ctx, src && (ctx->comm->rank != root || dst), SWCB200_ERR_BAD_ARG, "reduce_sum: null tensor");
+    SWC_NCCL(ctx, g_nccl.Reduce(src, dst, count, type, ncclSum, root, ctx->comm->comm, ctx->stream));
+    return SWCB200_OK;
+}
+
+SWC_EXPORT int swcb200_allreduce_sum(swcb200_ctx *ctx, const void *src, void *dst, size_t count, int dtype) {
+    SWC_CTX(ctx);
+    SWC_REQUIRE(ctx, ctx->comm != nullptr, SWCB200_ERR_NCCL, "allreduce_sum: no communicator");
+    size_t elem;
+    int type = nccl_type(dtype, &elem);
+    SWC_REQUIRE(ctx, type >= 0, SWCB200_ERR_BAD_ARG, "allreduce_sum: unknown dtype");
+    if (count == 0) return SWCB200_OK;
+    SWC_REQUIRE(ctx, src && dst, SWCB200_ERR_BAD_ARG, "allreduce_sum: null tensor");
+    SWC_NCCL(ctx, g_nccl.AllReduce(src, dst, count, type, ncclSum, ctx->comm->comm, ctx->stream));
+    return SWCB200_OK;
+}
+
+SWC_EXPORT int swcb200_allgather(swcb200_ctx *ctx, const void *src, void *dst, size_t count_per_rank, int dtype) {
+    SWC_CTX(ctx);
+    SWC_REQUIRE(ctx, ctx->comm != nullptr, SWCB200_ERR_NCCL, "allgather: no communicator");
+    size_t elem;
+    int type = nccl_type(dtype, &elem);
+    SWC_REQUIRE(ctx, type >= 0, SWCB200_ERR_BAD_ARG, "allgather: unknown dtype");
+    if (count_per_rank == 0) return SWCB200_OK;
+    SWC_REQUIRE(ctx, src && dst, SWCB200_ERR_BAD_ARG, "allgather: null tensor");
+    SWC_NCCL(ctx, g_nccl.AllGather(src, dst, count_per_rank, type, ctx->comm->comm, ctx->stream));
+    return SWCB200_OK;
+}
+
+// Re-tiling of a 2-D tensor [R, C].  Shards are packed: split along 0 -> [R/p, C]; along 1 -> [R, C/p];
+// -1 -> the whole tensor on every rank; -2 -> a full-size partial sum on every rank.
+SWC_EXPORT int swcb200_transform(swcb200_ctx *ctx, const void *src, void *dst, const size_t *dims, int ndim, int pre_axis,
+                                 int post_axis, int dtype) {
+    SWC_CTX(ctx);
+    SWC_REQUIRE(ctx, ctx->comm != nullptr, SWCB200_ERR_NCCL, "transform: no communicator");
+    SWC_REQUIRE(ctx, dims && ndim == 2, SWCB200_ERR_UNSUPPORTED, "transform: only 2-D tensors are re-tiled");
+    SWC_REQUIRE(ctx, pre_axis >= -2 && pre_axis <= 1 && post_axis >= -1 && post_axis <= 1, SWCB200_ERR_BAD_ARG,
+                "transform: axes must be in {-2,-1,0,1} -> {-1,0,1}");
+    size_t elem;
+    int type = nccl_type(dtype, &elem);
+    SWC_REQUIRE(ctx, type >= 0, SWCB200_ERR_BAD_ARG, "transform: unknown dtype");
+    swcb200_comm *c = ctx->comm;
+    const size_t p = (size_t)c->nranks, R = dims[0], C = dims[1];
+    if (R * C == 0) return SWCB200_OK;
+    SWC_REQUIRE(ctx, src && dst, SWCB200_ERR_BAD_ARG, "transform: null tensor");
+    SWC_REQUIRE(ctx, (pre_axis != 0 && post_axis != 0) || R % p == 0, SWCB200_ERR_BAD_SHAPE, "transform: rows not divisible");
+    SWC_REQUIRE(ctx, (pre_axis != 1 && post_axis != 1) || C % p == 0, SWCB200_ERR_BAD_SHAPE, "transform: columns not divisible");
+    const size_t Rp = R / p, Cp = C / p;
+    const uint8_t *s = (const uint8_t *)src;
+    uint8_t *d = (uint8_t *)dst;
+    int rc;
+    if (pre_axis == post_axis) {
+        size_t n = pre_axis == 0 ? Rp * C : pre_axis == 1 ? R * Cp : R * C;
+        if (dst != src) SWC_CUDA(ctx, cudaMemcpyAsync(dst, src, n * elem, cudaMemcpyDeviceToDevice, ctx->stream));
+        return SWCB200_OK;
+    }
+    if (pre_axis == -1) {  // replicated -> split: take the local slice, no communication (ParallelCodegen.cpp:864-867)
+        if (post_axis == 0) return copy_window(ctx, d, C, s + (size_t)c->rank * Rp * C * elem, C, C, Rp, elem);
+        return copy_window(ctx, d, Cp, s + (size_t)c->rank * Cp * elem, C, Cp, R, elem);
+    }
+    if (pre_axis == -2) {  // partial sums -> reduce (+ scatter): MPI_Reduce + master scatter in the reference (:798-862)
+        if (post_axis == 0) {
+            SWC_NCCL(ctx, g_nccl.ReduceScatter(src, dst, Rp * C, type, ncclSum, c->comm, ctx->stream));
+            return SWCB200_OK;
+        }
+        void *stage = nullptr;
+        if (post_axis == -1) {
+            SWC_NCCL(ctx, g_nccl.AllReduce(src, dst, R * C, type, ncclSum, c->comm, ctx->stream));
+            return SWCB200_OK;
+        }
+        rc = swc_scratch(ctx, R * C * elem, &stage);
+        if (rc) return rc;
+        SWC_NCCL(ctx, g_nccl.AllReduce(src, stage, R * C, type, ncclSum, c->comm, ctx->stream));
+        return copy_window(ctx, d, Cp, (uint8_t *)stage + (size_t)c->rank * Cp * elem, C, Cp, R, elem);
+    }
+    if (post_axis == -1) {  // split -> replicated: all-gather
+        if (pre_axis == 0) {
+            SWC_NCCL(ctx, g_nccl.AllGather(src, dst, Rp * C, type, c->comm, ctx->stream));
+            return SWCB200_OK;
+        }
+        void *stage = nullptr;
+        rc = swc_scratch(ctx, R * C * elem, &stage);
+        if (rc) return rc;
+        SWC_NCCL(ctx, g_nccl.AllGather(src, stage, R * Cp, type, c->comm, ctx->stream));
+        for (size_t q = 0; q < p; q++) {
+            rc = copy_window(ctx, d + q * Cp * elem, C, (uint8_t *)stage + q * R * Cp * elem, Cp, Cp, R, elem);
+            if (rc) return rc;
+        }
+        return SWCB200_OK;
+    }
+    // split i -> split j: all-to-all of [R/p, C/p] blocks (ring of MPI_Sendrecv in the reference, :714-797)
+    const size_t blk = Rp * Cp;
+    void *stage = nullptr;
+    rc = swc_scratch(ctx, blk * p * elem, &stage);
+    if (rc) return rc;
+    uint8_t *st = (uint8_t *)stage;
+    if (pre_axis == 0) {
+        // local [R/p, C]: block for rank q is columns [q*Cp, (q+1)*Cp) -> pack; received block from q is rows
+        // [q*Rp, (q+1)*Rp) of the result [R, C/p], which is contiguous
+        for (size_t q = 0; q < p; q++) {
+            rc = copy_window(ctx, st + q * blk * elem, Cp, s + q * Cp * elem, C, Cp, Rp, elem);
+            if (rc) return rc;
+        }
+        SWC_NCCL(ctx, g_nccl.GroupStart());
+        for (size_t q = 0; q < p; q++) {
+            SWC_NCCL(ctx, g_nccl.Send(st + q * blk * elem, blk, type, (int)q, c->comm, ctx->stream));
+            SWC_NCCL(ctx, g_nccl.Recv(d + q * blk * elem, blk, type, (int)q, c->comm, ctx->stream));
+        }
+        SWC_NCCL(ctx, g_nccl.GroupEnd());
+        return SWCB200_OK;
+    }
+    // pre 1 -> post 0: local [R, C/p]: block for rank q is rows [q*Rp, (q+1)*Rp), contiguous; the block received
+    // from q becomes columns [q*Cp, (q+1)*Cp) of the result [R/p, C] -> unpack
+    SWC_NCCL(ctx, g_nccl.GroupStart());
+    for (size_t q = 0; q < p; q++) {
+        SWC_NCCL(ctx, g_nccl.Send(s + q * blk * elem, blk, type, (int)q, c->comm, ctx->stream));
+        SWC_NCCL(ctx, g_nccl.Recv(st + q * blk * elem, blk, type, (int)q, c->comm, ctx->stream));
+    }
+    SWC_NCCL(ctx, g_nccl.GroupEnd());
+    for (size_t q = 0; q < p; q++) {
+        rc = copy_window(ctx, d + q * Cp * elem, C, st + q * blk * elem, Cp, Cp, Rp, elem);
+        if (rc) return rc;
+    }
+    return SWCB200_OK;
+}

@@ -89,6 +89,7 @@ SWC_EXPORT int swcb200_init_on_stream(int device, int precision, void *cuda_stre
 SWC_EXPORT int swcb200_destroy(swcb200_ctx *ctx) {
     if (!ctx) return SWCB200_ERR_BAD_ARG;
     int rc = SWCB200_OK;
+    if (ctx->comm) swcb200_comm_destroy(ctx);
     cudaSetDevice(ctx->device);
     if (cudaStreamSynchronize(ctx->stream) != cudaSuccess) rc = SWCB200_ERR_CUDA;
     if (ctx->scratch) cudaFree(ctx->scratch);

@@ -30,9 +30,36 @@ __global__ void __launch_bounds__(256) batchnorm_kernel(float *__restrict__ out,
     __syncthreads();
     const int cg = C / kVec;
     const size_t total = pixels * cg;
-    for (size_t t = (size_t)blockIdx.x * blockDim.x + threadIdx.x; t < total; t += (size_t)gridDim.x * blockDim.x) {
-        const int c = (int)(t % cg) * kVec;
-        const size_t off = (t / cg) * C + c;
+    const size_t nthreads = (size_t)gridDim.x * blockDim.x;
+    // When the thread stride is a multiple of the channel-group count (always for power-of-two channel
+    // counts up to 1024), a thread meets the same channels at every step: their parameters move into
+    // registers and the loop has no division.
+    const bool fixed_c = (nthreads % cg) == 0;
+    size_t t = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    int c = (int)(t % cg) * kVec;
+    // scale and bias are widened to double once per thread, not once per element: float<->double
+    // conversions run at a fraction of the FP64 rate and would otherwise set the pace of the kernel
+    double r_[kVec], s_[kVec], b_[kVec];
+    float m_[kVec];
+#pragma unroll
+    for (int i = 0; i < kVec; i++) {
+        r_[i] = rstd[c + i];
+        m_[i] = s_mean[c + i];
+        s_[i] = (double)s_scale[c + i];
+        b_[i] = (double)s_bias[c + i];
+    }
+    for (; t < total; t += nthreads) {
+        if (!fixed_c) {
+            c = (int)(t % cg) * kVec;
+#pragma unroll
+            for (int i = 0; i < kVec; i++) {
+                r_[i] = rstd[c + i];
+                m_[i] = s_mean[c + i];
+                s_[i] = (double)s_scale[c + i];
+                b_[i] = (double)s_bias[c + i];
+            }
+        }
+        const size_t off = t * kVec;  // (t / cg) * C + c, since C = cg * kVec
         float x[kVec], y[kVec];
         if (kVec == 4) {
             float4 v = __ldcs(reinterpret_cast<const float4 *>(in + off));
@@ -45,10 +72,10 @@ __global__ void __launch_bounds__(256) batchnorm_kernel(float *__restrict__ out,
         }
 #pragma unroll
         for (int i = 0; i < kVec; i++) {
-            double d = (double)__fsub_rn(x[i], s_mean[c + i]);
-            d = __dmul_rn(d, rstd[c + i]);
-            d = __dmul_rn(d, (double)s_scale[c + i]);
-            d = __dadd_rn(d, (double)s_bias[c + i]);
+            double d = (double)__fsub_rn(x[i], m_[i]);
+            d = __dmul_rn(d, r_[i]);
+            d = __dmul_rn(d, s_[i]);
+            d = __dadd_rn(d, b_[i]);
             y[i] = (float)d;
         }
         if (kVec == 4)

@@ -26,18 +26,22 @@ struct MaxAcc {
     }
 };
 
+// Thread mapping shared by the pooling kernels: blockIdx.x walks output rows (n, oh), the threads of
+// a CTA (and blockIdx.y) walk the ow x channel-group positions of that row, channel group fastest.
+// All index arithmetic is 32-bit; the only divisions are by the channel-group count.
+#define SWC_POOL_COORDS(kVec)                                                   \
+    const int cg = g.C / (kVec);                                                \
+    const int rowlen = g.OW * cg;                                               \
+    const int pos = blockIdx.y * blockDim.x + threadIdx.x;                      \
+    if (pos >= rowlen) return;                                                  \
+    const int ow = pos / cg, c = (pos - ow * cg) * (kVec);
+
 template <int kVec>  // 4: float4 over channels, 1: scalar
 __global__ void __launch_bounds__(256) maxpool_f32_kernel(const float *__restrict__ in, float *__restrict__ out,
                                                           PoolGeom g) {
-    const int cg = g.C / kVec;
-    const size_t total = (size_t)g.N * g.OH * g.OW * cg;
-    for (size_t t = (size_t)blockIdx.x * blockDim.x + threadIdx.x; t < total; t += (size_t)gridDim.x * blockDim.x) {
-        int c = (int)(t % cg) * kVec;
-        size_t p = t / cg;
-        int ow = (int)(p % g.OW);
-        p /= g.OW;
-        int oh = (int)(p % g.OH);
-        int n = (int)(p / g.OH);
+    SWC_POOL_COORDS(kVec)
+    for (int row = blockIdx.x; row < g.N * g.OH; row += gridDim.x) {
+        const int n = row / g.OH, oh = row - n * g.OH;
         MaxAcc acc[kVec];
         for (int kx = 0; kx < g.kh; kx++) {
             int ih = oh * g.sh - g.pt + kx;
@@ -68,15 +72,9 @@ __global__ void __launch_bounds__(256) maxpool_f32_kernel(const float *__restric
 template <int kVec>  // 8: uint4 (8 bf16) over channels, 1: scalar
 __global__ void __launch_bounds__(256) maxpool_bf16_kernel(const __nv_bfloat16 *__restrict__ in,
                                                            __nv_bfloat16 *__restrict__ out, PoolGeom g) {
-    const int cg = g.C / kVec;
-    const size_t total = (size_t)g.N * g.OH * g.OW * cg;
-    for (size_t t = (size_t)blockIdx.x * blockDim.x + threadIdx.x; t < total; t += (size_t)gridDim.x * blockDim.x) {
-        int c = (int)(t % cg) * kVec;
-        size_t p = t / cg;
-        int ow = (int)(p % g.OW);
-        p /= g.OW;
-        int oh = (int)(p % g.OH);
-        int n = (int)(p / g.OH);
+    SWC_POOL_COORDS(kVec)
+    for (int row = blockIdx.x; row < g.N * g.OH; row += gridDim.x) {
+        const int n = row / g.OH, oh = row - n * g.OH;
         MaxAcc acc[kVec];
         for (int kx = 0; kx < g.kh; kx++) {
             int ih = oh * g.sh - g.pt + kx;
@@ -87,9 +85,12 @@ __global__ void __launch_bounds__(256) maxpool_bf16_kernel(const __nv_bfloat16 *
                 const __nv_bfloat16 *src = in + (((size_t)n * g.H + ih) * g.W + iw) * g.C + c;
                 if (kVec == 8) {
                     uint4 x = __ldcs(reinterpret_cast<const uint4 *>(src));
-                    const __nv_bfloat16 *e = reinterpret_cast<const __nv_bfloat16 *>(&x);
+                    const uint32_t w[4] = {x.x, x.y, x.z, x.w};
 #pragma unroll
-                    for (int i = 0; i < kVec; i++) acc[i].tap(__bfloat162float(e[i]));
+                    for (int i = 0; i < 4; i++) {  // bf16 -> fp32 is a 16-bit shift
+                        acc[(2 * i) % kVec].tap(__uint_as_float(w[i] << 16));
+                        acc[(2 * i + 1) % kVec].tap(__uint_as_float(w[i] & 0xffff0000u));
+                    }
                 } else {
                     acc[0].tap(__bfloat162float(*src));
                 }
@@ -97,10 +98,11 @@ __global__ void __launch_bounds__(256) maxpool_bf16_kernel(const __nv_bfloat16 *
         }
         __nv_bfloat16 *dst = out + (((size_t)n * g.OH + oh) * g.OW + ow) * g.C + c;
         if (kVec == 8) {
-            uint4 o;
-            __nv_bfloat16 *e = reinterpret_cast<__nv_bfloat16 *>(&o);
-#pragma unroll
-            for (int i = 0; i < kVec; i++) e[i] = __float2bfloat16_rn(acc[i].v);  // exact: the value came from bf16
+            uint4 o;  // the maxima are bf16 values already: the upper halves are the exact results
+            o.x = (__float_as_uint(acc[0].v) >> 16) | (__float_as_uint(acc[1 % kVec].v) & 0xffff0000u);
+            o.y = (__float_as_uint(acc[2 % kVec].v) >> 16) | (__float_as_uint(acc[3 % kVec].v) & 0xffff0000u);
+            o.z = (__float_as_uint(acc[4 % kVec].v) >> 16) | (__float_as_uint(acc[5 % kVec].v) & 0xffff0000u);
+            o.w = (__float_as_uint(acc[6 % kVec].v) >> 16) | (__float_as_uint(acc[7 % kVec].v) & 0xffff0000u);
             __stcs(reinterpret_cast<uint4 *>(dst), o);
         } else {
             *dst = __float2bfloat16_rn(acc[0].v);
@@ -148,6 +150,22 @@ int make_geom(swcb200_ctx *ctx, const char *what, const size_t *idims, const siz
     return SWCB200_OK;
 }
 
+// rows of the output on grid.x (capped at a few waves), positions within a row on threads x grid.y
+int pool_launch_geom(swcb200_ctx *ctx, const PoolGeom &g, int vec, dim3 *grid, dim3 *block) {
+    const long long rowlen = (long long)g.OW * (g.C / vec);
+    SWC_REQUIRE(ctx, rowlen <= 0x7fffffffLL && (long long)g.N * g.OH <= 0x7fffffffLL, SWCB200_ERR_TOO_LARGE,
+                "pooling: output row or row count beyond 2^31");
+    int threads = rowlen >= 256 ? 256 : (int)((rowlen + 31) / 32 * 32);
+    const long long by = (rowlen + threads - 1) / threads;
+    SWC_REQUIRE(ctx, by <= 65535, SWCB200_ERR_TOO_LARGE, "pooling: output row too long");
+    const long long rows = (long long)g.N * g.OH;
+    const long long cap = (long long)ctx->sm_count * 16;
+    long long gx = rows < cap ? rows : cap;
+    *grid = dim3((unsigned)gx, (unsigned)by);
+    *block = dim3((unsigned)threads);
+    return SWCB200_OK;
+}
+
 }  // namespace
 
 SWC_EXPORT int swcb200_maxpool_f(swcb200_ctx *ctx, const float *input, float *output, const size_t *idims,
@@ -161,13 +179,13 @@ SWC_EXPORT int swcb200_maxpool_f(swcb200_ctx *ctx, const float *input, float *ou
     if (total == 0) return SWCB200_OK;
     SWC_REQUIRE(ctx, input && output, SWCB200_ERR_BAD_ARG, "maxpool_f: null tensor");
     bool vec = (g.C % 4 == 0) && swc_aligned16(input) && swc_aligned16(output);
-    if (vec) {
-        unsigned grid = swc_grid(ctx, total / 4, 256, 8);
-        maxpool_f32_kernel<4><<<grid, 256, 0, ctx->stream>>>(input, output, g);
-    } else {
-        unsigned grid = swc_grid(ctx, total, 256, 8);
-        maxpool_f32_kernel<1><<<grid, 256, 0, ctx->stream>>>(input, output, g);
-    }
+    dim3 grid, block;
+    rc = pool_launch_geom(ctx, g, vec ? 4 : 1, &grid, &block);
+    if (rc) return rc;
+    if (vec)
+        maxpool_f32_kernel<4><<<grid, block, 0, ctx->stream>>>(input, output, g);
+    else
+        maxpool_f32_kernel<1><<<grid, block, 0, ctx->stream>>>(input, output, g);
     return swc_check_launch(ctx, "maxpool_f");
 }
 
@@ -182,13 +200,13 @@ SWC_EXPORT int swcb200_maxpool_bf16(swcb200_ctx *ctx, const void *input, void *o
     if (total == 0) return SWCB200_OK;
     SWC_REQUIRE(ctx, input && output, SWCB200_ERR_BAD_ARG, "maxpool_bf16: null tensor");
     bool vec = (g.C % 8 == 0) && swc_aligned16(input) && swc_aligned16(output);
-    if (vec) {
-        unsigned grid = swc_grid(ctx, total / 8, 256, 8);
-        maxpool_bf16_kernel<8><<<grid, 256, 0, ctx->stream>>>((const __nv_bfloat16 *)input, (__nv_bfloat16 *)output, g);
-    } else {
-        unsigned grid = swc_grid(ctx, total, 256, 8);
-        maxpool_bf16_kernel<1><<<grid, 256, 0, ctx->stream>>>((const __nv_bfloat16 *)input, (__nv_bfloat16 *)output, g);
-    }
+    dim3 grid, block;
+    rc = pool_launch_geom(ctx, g, vec ? 8 : 1, &grid, &block);
+    if (rc) return rc;
+    if (vec)
+        maxpool_bf16_kernel<8><<<grid, block, 0, ctx->stream>>>((const __nv_bfloat16 *)input, (__nv_bfloat16 *)output, g);
+    else
+        maxpool_bf16_kernel<1><<<grid, block, 0, ctx->stream>>>((const __nv_bfloat16 *)input, (__nv_bfloat16 *)output, g);
     return swc_check_launch(ctx, "maxpool_bf16");
 }
 

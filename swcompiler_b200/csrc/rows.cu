@@ -20,8 +20,62 @@ __device__ __forceinline__ float warp_sum(float v) {
 
 template <bool kStrict>
 __device__ __forceinline__ float exp_of(float x) {
-    // kStrict: exponential in double, rounded once (see TanhOp in eltwise.cu)
-    return kStrict ? (float)exp((double)x) : expf(x);
+    // kStrict: exponential in double, rounded once (see TanhOp in eltwise.cu).  Otherwise the hardware
+    // exp2 approximation: relative error about 2^-22 plus |x| * 2^-24 from the scaling, far inside 1e-5
+    // for every x whose exponential is not already negligible against the row maximum's 1.0.
+    return kStrict ? (float)exp((double)x) : __expf(x);
+}
+
+// 128-bit variant of softmax_warp_kernel: lane l owns float4 groups l, l+32, ...; needs n % 4 == 0 and
+// 16-byte aligned rows.  In the fast mode each element is multiplied by the reciprocal of the row sum
+// (one division per row) instead of being divided by it.
+template <int kVecPerLane, bool kStrict>
+__global__ void __launch_bounds__(256) softmax_warp_vec_kernel(const float *__restrict__ a, int lda,
+                                                               float *__restrict__ b, int ldb, int m, int n) {
+    const int lane = threadIdx.x & 31;
+    const int warps_per_cta = blockDim.x >> 5;
+    const int n4 = n >> 2;
+    for (long long row = (long long)blockIdx.x * warps_per_cta + (threadIdx.x >> 5); row < m;
+         row += (long long)gridDim.x * warps_per_cta) {
+        const float4 *ar = reinterpret_cast<const float4 *>(a + (size_t)row * lda);
+        float4 *br = reinterpret_cast<float4 *>(b + (size_t)row * ldb);
+        float4 v[kVecPerLane];
+        float mx = -INFINITY;
+#pragma unroll
+        for (int i = 0; i < kVecPerLane; i++) {
+            int j = lane + 32 * i;
+            v[i] = (j < n4) ? __ldcs(ar + j) : make_float4(-INFINITY, -INFINITY, -INFINITY, -INFINITY);
+            mx = fmaxf(fmaxf(mx, fmaxf(v[i].x, v[i].y)), fmaxf(v[i].z, v[i].w));
+        }
+        mx = warp_max(mx);
+        float s = 0.f;
+#pragma unroll
+        for (int i = 0; i < kVecPerLane; i++) {
+            int j = lane + 32 * i;
+            if (j < n4) {
+                v[i].x = exp_of<kStrict>(__fsub_rn(v[i].x, mx));
+                v[i].y = exp_of<kStrict>(__fsub_rn(v[i].y, mx));
+                v[i].z = exp_of<kStrict>(__fsub_rn(v[i].z, mx));
+                v[i].w = exp_of<kStrict>(__fsub_rn(v[i].w, mx));
+                s = __fadd_rn(s, __fadd_rn(__fadd_rn(v[i].x, v[i].y), __fadd_rn(v[i].z, v[i].w)));
+            }
+        }
+        s = warp_sum(s);
+        const float inv = __fdiv_rn(1.0f, s);
+#pragma unroll
+        for (int i = 0; i < kVecPerLane; i++) {
+            int j = lane + 32 * i;
+            if (j < n4) {
+                float4 o;
+                if (kStrict) {
+                    o = make_float4(__fdiv_rn(v[i].x, s), __fdiv_rn(v[i].y, s), __fdiv_rn(v[i].z, s), __fdiv_rn(v[i].w, s));
+                } else {
+                    o = make_float4(v[i].x * inv, v[i].y * inv, v[i].z * inv, v[i].w * inv);
+                }
+                __stcs(br + j, o);
+            }
+        }
+    }
 }
 
 // One warp per row, the row held in registers: lane l owns columns l, l+32, ...  Each load
@@ -125,12 +179,23 @@ __global__ void __launch_bounds__(256) argmax_kernel(const float *__restrict__ i
         for (int t = 0; t < top_k; t++) {
             float bv = 0.f;
             int bi = -1;
-            for (int j = lane; j < n; j += 32) {
-                float v = r[j];
-                if (pi >= 0 && !beats(pv, pi, v, j)) continue;  // already emitted (or not below the last winner)
-                if (bi < 0 || beats(v, j, bv, bi)) {
-                    bv = v;
-                    bi = j;
+            // eight independent loads in flight per lane, then the comparisons in index order
+            for (int j0 = lane; j0 < n; j0 += 32 * 8) {
+                float v[8];
+#pragma unroll
+                for (int u = 0; u < 8; u++) {
+                    int j = j0 + 32 * u;
+                    v[u] = (j < n) ? __ldg(r + j) : 0.f;
+                }
+#pragma unroll
+                for (int u = 0; u < 8; u++) {
+                    int j = j0 + 32 * u;
+                    if (j >= n) continue;
+                    if (pi >= 0 && !beats(pv, pi, v[u], j)) continue;  // emitted already, or not below the last winner
+                    if (bi < 0 || beats(v[u], j, bv, bi)) {
+                        bv = v[u];
+                        bi = j;
+                    }
                 }
             }
 #pragma unroll
@@ -153,6 +218,18 @@ template <bool kStrict>
 int launch_softmax(swcb200_ctx *ctx, int m, int n, const float *a, int lda, float *b, int ldb) {
     const int warps = 8;
     unsigned grid = swc_grid(ctx, (size_t)m, warps, 8);
+    if (n % 4 == 0 && lda % 4 == 0 && ldb % 4 == 0 && swc_aligned16(a) && swc_aligned16(b) && n >= 128) {
+#define SWC_SMV_CASE(P)                                                                                     \
+    if (n <= 128 * (P)) {                                                                                   \
+        softmax_warp_vec_kernel<P, kStrict><<<grid, 32 * warps, 0, ctx->stream>>>(a, lda, b, ldb, m, n);    \
+        return swc_check_launch(ctx, "matrixSoftmax_f");                                                   \
+    }
+        SWC_SMV_CASE(1)
+        SWC_SMV_CASE(2)
+        SWC_SMV_CASE(4)
+        SWC_SMV_CASE(8)
+#undef SWC_SMV_CASE
+    }
 #define SWC_SM_CASE(P)                                                                                   \
     if (n <= 32 * (P)) {                                                                                 \
         softmax_warp_kernel<P, kStrict><<<grid, 32 * warps, 0, ctx->stream>>>(a, lda, b, ldb, m, n);    \

@@ -37,19 +37,23 @@ def pool_out_dims(idims, kernels, strides, pads):
 
 
 class Backend:
-    def __init__(self, device: int | torch.device = 0, precision: int = L.STRICT_F32, own_stream: bool = False):
+    def __init__(self, device: int | torch.device = 0, precision: int = L.STRICT_F32, own_stream: bool = False,
+                 stream: "torch.cuda.Stream | None" = None):
+        """Work is issued on `stream` if given, else on torch's current stream of the device (own_stream=True:
+        on a stream the library creates, which torch knows nothing about -- synchronise with `sync()`)."""
         if not torch.cuda.is_available():
             raise RuntimeError("swcompiler_b200 needs a CUDA device; there is no CPU path")
         self.lib = L.lib()
         self.device = torch.device("cuda", device if isinstance(device, int) else device.index or 0)
         self._ctx = C.c_void_p()
+        self.torch_stream = None
         with torch.cuda.device(self.device):
             if own_stream:
                 rc = self.lib.swcb200_init(C.c_int(self.device.index), C.c_int(precision), C.byref(self._ctx))
             else:
-                s = torch.cuda.current_stream(self.device).cuda_stream
-                rc = self.lib.swcb200_init_on_stream(C.c_int(self.device.index), C.c_int(precision), C.c_void_p(s),
-                                                     C.byref(self._ctx))
+                self.torch_stream = stream if stream is not None else torch.cuda.current_stream(self.device)
+                rc = self.lib.swcb200_init_on_stream(C.c_int(self.device.index), C.c_int(precision),
+                                                     C.c_void_p(self.torch_stream.cuda_stream), C.byref(self._ctx))
         if rc != L.OK:
             raise L.SwcError(rc, "swcb200_init")
         self.precision = precision

@@ -1,0 +1,115 @@
+"""Per-kernel roofline measurements on one GPU:  python -m swcompiler_b200.opbench [--only NAME] [--iters N]
+
+Times every kernel of the table at the sizes the benchmark configurations give it (config 5 stage
+[256,56,56,64], config 3 activations [65536,4096] and logits [65536,1000]), with CUDA events on the
+launching stream after warm-up, inputs larger than L2, and prints one JSON line per kernel:
+achieved GB/s (algorithmic bytes / time) or TFLOP/s, and the fraction of the measured peak.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+
+import torch
+
+import swcompiler_b200 as swc
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def _peaks():
+    try:
+        p = json.load(open(os.path.join(ROOT, "MEASURED_PEAKS.json")))
+        return float(p["hbm_gbs"]), float(p["bf16_tflops"]), "measured"
+    except Exception:
+        return 6650.0, 1590.0, "fallback"
+
+
+def _time(fn, iters):
+    for _ in range(3):
+        fn()
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(iters):
+        fn()
+    e1.record()
+    torch.cuda.synchronize()
+    return e0.elapsed_time(e1) / iters * 1e-3
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--only", default=None)
+    ap.add_argument("--iters", type=int, default=20)
+    args = ap.parse_args()
+    hbm, tflops, src = _peaks()
+    be = swc.Backend(0, swc.STRICT_F32)
+    dev = be.device
+    g = torch.Generator(device=dev).manual_seed(0)
+    stage = (256, 56, 56, 64)
+    x = torch.randn(stage, generator=g, device=dev)
+    y = torch.randn(stage, generator=g, device=dev)
+    out = torch.empty_like(x)
+    E = x.numel()
+    C = stage[3]
+    vec = [torch.rand(C, generator=g, device=dev) + 0.5 for _ in range(4)]
+    pooled = torch.empty((256, 28, 28, 64), device=dev)
+    logits = torch.randn((65536, 1000), generator=g, device=dev)
+    probs = torch.empty_like(logits)
+    act = torch.randn((32768, 4096), generator=g, device=dev)  # 512 MiB fp32
+    act_out = torch.empty_like(act)
+    bias = torch.randn(4096, generator=g, device=dev)
+    xb = x.to(torch.bfloat16)
+    pooled_b = torch.empty((256, 28, 28, 64), device=dev, dtype=torch.bfloat16)
+
+    mem_ops = [
+        ("relu_f", 8 * E, lambda: be.relu_f(x, out=out)),
+        ("vecAdd_f", 12 * E, lambda: be.vecAdd_f(x, y, out=out)),
+        ("batchnormalization_f", 8 * E + 16 * C, lambda: be.batchnormalization_f(x, vec[0], vec[1], vec[2], vec[3], 1e-5, out=out)),
+        ("maxpool_f 2x2/2", 5 * E, lambda: be.maxpool_f(x, (2, 2), (2, 2), (0, 0, 0, 0), out=pooled)),
+        ("maxpool_bf16 2x2/2", 2.5 * E, lambda: be.maxpool_bf16(xb, (2, 2), (2, 2), (0, 0, 0, 0), out=pooled_b)),
+        ("batchedadd_f [32768,4096]", 8 * act.numel() + 4 * 4096, lambda: be.batchedadd_f(act, bias, out=act_out)),
+        ("matrixTanh_f strict [32768,4096]", 8 * act.numel(), lambda: be.matrixTanh_f(act, out=act_out)),
+        ("matrixSoftmax_f strict [65536,1000]", 8 * logits.numel(), lambda: be.matrixSoftmax_f(logits, out=probs)),
+        ("argMax_i top1 [65536,1000]", 4 * logits.numel(), lambda: be.argMax_i(logits, 1)),
+        ("cast_f32_to_bf16", 6 * E, lambda: be.cast_f32_to_bf16(x, out=xb)),
+    ]
+    for name, nbytes, fn in mem_ops:
+        if args.only and args.only not in name:
+            continue
+        t = _time(fn, args.iters)
+        print(json.dumps({"kernel": name, "bound": "hbm", "us": t * 1e6, "achieved": nbytes / t / 1e9, "unit": "GB/s",
+                          "peak": hbm, "frac": nbytes / t / 1e9 / hbm, "peak_source": src, "bytes": nbytes}))
+    be.set_precision(swc.TC_BF16)
+    for name, nbytes, fn in [
+        ("matrixTanh_f fast [32768,4096]", 8 * act.numel(), lambda: be.matrixTanh_f(act, out=act_out)),
+        ("matrixSoftmax_f fast [65536,1000]", 8 * logits.numel(), lambda: be.matrixSoftmax_f(logits, out=probs)),
+    ]:
+        if args.only and args.only not in name:
+            continue
+        t = _time(fn, args.iters)
+        print(json.dumps({"kernel": name, "bound": "hbm", "us": t * 1e6, "achieved": nbytes / t / 1e9, "unit": "GB/s",
+                          "peak": hbm, "frac": nbytes / t / 1e9 / hbm, "peak_source": src, "bytes": nbytes}))
+    del act, act_out, logits, probs
+
+    # tensor-core FC shapes (bf16, fp32 accumulate): config 3 hidden layer and last layer, config 4 per-GPU shards at p = 8
+    for (m, n, k) in [(65536, 4096, 4096), (65536, 1000, 4096), (8192, 4096, 8192), (8192, 8192, 4096)]:
+        name = f"fc_bf16 {m}x{n}x{k}"
+        if args.only and args.only not in name:
+            continue
+        a = torch.randn((m, k), generator=g, device=dev).to(torch.bfloat16)
+        wp = (torch.randn((n, k), generator=g, device=dev) / k ** 0.5).to(torch.bfloat16)
+        b = torch.randn(n, generator=g, device=dev)
+        o = torch.empty((m, n), device=dev, dtype=torch.bfloat16)
+        t = _time(lambda: be.fc_bf16(a, wp, b, swc.ACT_RELU, out=o), args.iters)
+        fl = 2.0 * m * n * k
+        print(json.dumps({"kernel": name, "bound": "tensor", "us": t * 1e6, "achieved": fl / t / 1e12, "unit": "TFLOP/s",
+                          "peak": tflops, "frac": fl / t / 1e12 / tflops, "peak_source": src + " (burst)", "flops": fl}))
+        del a, wp, o
+    be.sync()
+
+
+if __name__ == "__main__":
+    main()

@@ -73,3 +73,59 @@ class WideMlpProgram:
         self.forward(x_dev[:rows], probs_dev[:rows])
         probs_host.copy_(probs_dev[:rows], non_blocking=True)
         return probs_host
+
+
+class FcPairProgram:
+    """Model-parallel FC -> ReLU -> FC on p GPUs (the strategy of `parallel.strategy_fc_pair`).
+
+    FC1's weight is split by output columns, so each rank computes a column shard of the hidden activation
+    and applies ReLU locally; FC2's weight is split by input rows, so each rank's product is a full-size
+    partial sum, joined by a sum over ranks (the reference's Reduce node, an NCCL all-reduce here).  X is
+    replicated.  With `chunks` > 1 the rows are processed in chunks: the all-reduce of chunk i runs on the
+    communication context's stream while the tensor cores work on chunk i+1.
+    """
+
+    def __init__(self, be: Backend, comm, w1_full, w2_full, max_rows: int):
+        from . import parallel as par
+        self.be, self.comm = be, comm
+        p, r = comm.nranks, comm.rank
+        w1s = par.take_shard(w1_full, 1, r, p)      # [k, n1/p]
+        w2s = par.take_shard(w2_full, 0, r, p)      # [n1/p, n2]
+        self.wp1 = be.pack_weight_bf16(w1s)         # [n1/p, k]
+        self.wp2 = be.pack_weight_bf16(w2s)         # [n2, n1/p]
+        self.k, self.n1s, self.n2 = w1_full.shape[0], w1s.shape[1], w2_full.shape[1]
+        self.h = torch.empty((max_rows, self.n1s), dtype=torch.bfloat16, device=be.device)
+        self.y_part = torch.empty((max_rows, self.n2), dtype=torch.float32, device=be.device)
+        self.y = torch.empty((max_rows, self.n2), dtype=torch.float32, device=be.device)
+        self.max_rows = max_rows
+        be.sync()
+
+    def flops(self, rows: int) -> float:
+        """Per rank."""
+        return 2.0 * rows * self.n1s * (self.k + self.n2)
+
+    def forward(self, x_bf16: torch.Tensor, chunks: int = 1) -> torch.Tensor:
+        rows = x_bf16.shape[0]
+        be = self.be
+        chunks = max(1, chunks)
+        step = (rows + chunks - 1) // chunks
+        ms, cs = be.torch_stream, self.comm.be.torch_stream
+        overlap = ms is not None and cs is not None and cs != ms
+        if overlap:
+            start = torch.cuda.Event()
+            start.record(ms)
+            cs.wait_event(start)  # y of an earlier forward may still be read on the main stream
+        for r0 in range(0, rows, step):
+            r1 = min(rows, r0 + step)
+            be.fc_bf16(x_bf16[r0:r1], self.wp1, None, L.ACT_RELU, out=self.h[r0:r1])
+            be.fc_bf16(self.h[r0:r1], self.wp2, None, L.ACT_NONE, out=self.y_part[r0:r1])
+            if overlap:
+                ready = torch.cuda.Event()
+                ready.record(ms)
+                cs.wait_event(ready)
+            self.comm.allreduce_sum(self.y_part[r0:r1], out=self.y[r0:r1])
+        if overlap:
+            done = torch.cuda.Event()
+            done.record(cs)
+            ms.wait_event(done)
+        return self.y[:rows]

@@ -1,0 +1,118 @@
+"""CPU, world_size 2 over gloo: the host-side tiling logic of partitioned graphs (Scatter / Gather / Reduce /
+Transform semantics, batch split, the model-parallel FC pair) against the un-partitioned computation."""
+import os
+import socket
+
+import numpy as np
+import pytest
+import torch
+import torch.distributed as dist
+import torch.multiprocessing as mp
+
+from swcompiler_b200 import parallel as par
+
+
+def _free_port():
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        return s.getsockname()[1]
+
+
+def _worker(rank, world, port, fn, ret):
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        fn(rank, world)
+        ret[rank] = "ok"
+    except Exception as e:  # surfaced to the parent
+        import traceback
+        ret[rank] = traceback.format_exc()
+    finally:
+        dist.destroy_process_group()
+
+
+def run_ranks(fn, world=2):
+    mgr = mp.get_context("spawn").Manager()
+    ret = mgr.dict()
+    mp.spawn(_worker, args=(world, _free_port(), fn, ret), nprocs=world, join=True)
+    assert all(ret.get(r) == "ok" for r in range(world)), dict(ret)
+
+
+def _scatter_gather(rank, world):
+    comm = par.TorchComm()
+    g = torch.Generator().manual_seed(1)
+    full = torch.randn((4, 6, 8), generator=g)
+    for axis in (0, 1, 2, -1):
+        local = comm.scatter(full if rank == 0 else None, full.shape, axis)
+        assert torch.equal(local, par.take_shard(full, axis, rank, world))
+        back = comm.gather(local, full.shape, axis)
+        if rank == 0:
+            assert torch.equal(back, full)
+        else:
+            assert back is None
+
+
+def _transform(rank, world):
+    comm = par.TorchComm()
+    full = torch.arange(8 * 12, dtype=torch.float32).reshape(8, 12)
+    for pre in (0, 1, -1):
+        for post in (0, 1, -1):
+            local = par.take_shard(full, pre, rank, world)
+            out = comm.transform(local, full.shape, pre, post)
+            assert torch.equal(out, par.take_shard(full, post, rank, world)), (pre, post)
+    # partial sums: every rank holds a full-size addend
+    part = full * (rank + 1)
+    total = full * sum(range(1, world + 1))
+    for post in (0, 1, -1):
+        assert torch.equal(comm.transform(part, full.shape, par.PARTIAL, post), par.take_shard(total, post, rank, world))
+    r = comm.reduce_sum(part)
+    assert (rank != 0 and r is None) or torch.equal(r, total)
+    assert torch.equal(comm.allgather(par.take_shard(full, 0, rank, world)), full)
+
+
+def _fc_pair(rank, world):
+    """FC1 by output columns -> ReLU -> FC2 by input rows -> Reduce equals the un-partitioned chain (up to the
+    order of the final sum)."""
+    comm = par.TorchComm()
+    g = torch.Generator().manual_seed(2)
+    x = torch.randn((16, 32), generator=g, dtype=torch.float64)
+    w1 = torch.randn((32, 48), generator=g, dtype=torch.float64)
+    w2 = torch.randn((48, 24), generator=g, dtype=torch.float64)
+    st = par.strategy_fc_pair(world)
+    assert st["fc1"] == (-1, 1, 1) and st["fc2"] == (1, 0, -2)
+    xs = comm.scatter(x if rank == 0 else None, x.shape, st["fc1"][0], dtype=torch.float64)
+    w1s = comm.scatter(w1 if rank == 0 else None, w1.shape, st["fc1"][1], dtype=torch.float64)
+    w2s = comm.scatter(w2 if rank == 0 else None, w2.shape, st["fc2"][1], dtype=torch.float64)
+    h = torch.relu(xs @ w1s)                      # column shard [16, 48/p]
+    y_part = h @ w2s                               # full-size partial sum
+    y = comm.allreduce_sum(y_part)
+    assert torch.allclose(y, torch.relu(x @ w1) @ w2, rtol=1e-12, atol=1e-12)
+
+
+def _batch_split(rank, world):
+    """Data-parallel: each rank runs the whole chain on its rows; gathering axis 0 gives the full result."""
+    comm = par.TorchComm()
+    g = torch.Generator().manual_seed(3)
+    x = torch.randn((8, 5), generator=g)
+    w = torch.randn((5, 7), generator=g)
+    r0, n = par.split_rows(x.shape[0], world, rank)
+    xs = comm.scatter(x if rank == 0 else None, x.shape, 0)
+    assert torch.equal(xs, x[r0:r0 + n])
+    ws = comm.scatter(w if rank == 0 else None, w.shape, -1)
+    y = comm.gather(torch.softmax(xs @ ws, dim=1), (8, 7), 0)
+    if rank == 0:
+        assert torch.equal(y, torch.softmax(x @ w, dim=1))
+
+
+@pytest.mark.parametrize("fn", [_scatter_gather, _transform, _fc_pair, _batch_split])
+def test_two_ranks_gloo(fn):
+    run_ranks(fn, 2)
+
+
+def test_shapes_and_costs():
+    assert par.shard_dims((8, 12), 1, 4) == (8, 3) and par.shard_dims((8, 12), -1, 4) == (8, 12)
+    with pytest.raises(ValueError):
+        par.shard_dims((8, 10), 1, 4)
+    assert par.split_rows(65536, 8, 3) == (3 * 8192, 8192)
+    assert par.allreduce_wire_bytes(1 << 20, 4, 8) == 2 * 7 / 8 * 4 * (1 << 20)
+    assert par.comm_cost_bytes((8, 8), -1, 0, 2) == 0 and par.comm_cost_bytes((8, 8), 0, 1, 2) == 128
