@@ -16,6 +16,7 @@ workload, one slice per host thread.
 from __future__ import annotations
 
 import argparse
+import ctypes as C
 import json
 import os
 import statistics
@@ -33,7 +34,7 @@ METRIC, UNIT = "inference samples/sec", "samples/s"
 def config(n_gpus, rows_per_rank):
     return {"workload": "wide MLP forward (BASELINE configs[2]): X[65536,4096] bf16 -> 4x(FC 4096->4096 + bias + ReLU) "
                         "-> FC 4096->1000 + bias -> softmax",
-            "global_batch": BATCH, "rows_per_gpu": rows_per_rank, "parallelism": f"dp{n_gpus} (batch split, final gather)",
+            "global_batch": BATCH, "rows_per_gpu": rows_per_rank, "parallelism": f"dp{n_gpus} (batch split; Gather to rank 0 over NCCL, overlapped with the next step)",
             "l2": "inputs larger than L2 (X 512 MiB, activations 512 MiB per layer); no flush needed"}
 
 
@@ -180,13 +181,48 @@ def run_ours(args, rank, world, local_rank):
     x, ws, bs = make_inputs(torch, device, rows, row0)
     prog = WideMlpProgram(be, ws, bs, max_rows=rows)
     del ws
-    probs = torch.empty((rows, CLASSES), dtype=torch.float32, device=device)
-    gathered = [torch.empty_like(probs) for _ in range(world)] if (world > 1 and rank == 0) else None
+    # Two output buffers: with more than one GPU the Gather of step s (NCCL, on its own stream, through the
+    # library's swcb200_gather) runs while the tensor cores work on step s+1.
+    probs2 = [torch.empty((rows, CLASSES), dtype=torch.float32, device=device) for _ in range(2 if world > 1 else 1)]
+    probs = probs2[0]
+    comm = gathered = None
+    if world > 1:
+        from swcompiler_b200 import parallel as par
 
-    def step():
-        prog.forward(x, probs)
+        def exchange(uid):
+            box = [uid]
+            dist.broadcast_object_list(box, src=0)
+            return box[0]
+
+        comm_stream = torch.cuda.Stream(device)
+        comm = par.NcclComm(swc.Backend(local_rank, swc.TC_BF16, stream=comm_stream), rank, world, exchange)
+        if rank == 0:
+            gathered = torch.empty((BATCH, CLASSES), dtype=torch.float32, device=device)
+    main_stream = torch.cuda.current_stream(device)
+    gather_done = [None, None]
+    counter = [0]
+
+    def step(on_launch=None):
+        s = counter[0]
+        counter[0] += 1
+        out = probs2[s % len(probs2)]
+        if gather_done[s % 2] is not None:
+            main_stream.wait_event(gather_done[s % 2])  # the buffer's previous Gather has read it
+        prog.forward(x, out, on_launch=on_launch)
         if world > 1:
-            dist.gather(probs, gathered, dst=0)
+            ready = torch.cuda.Event()
+            ready.record(main_stream)
+            comm.be.torch_stream.wait_event(ready)
+            dst = C.c_void_p(gathered.data_ptr()) if rank == 0 else C.c_void_p(0)
+            comm.be._call("gather", C.c_void_p(out.data_ptr()), dst, (C.c_size_t * 2)(BATCH, CLASSES), C.c_int(2),
+                          C.c_int(0), C.c_int(swc.F32), C.c_int(0))
+            done = torch.cuda.Event()
+            done.record(comm.be.torch_stream)
+            gather_done[s % 2] = done
+
+    def drain():
+        if world > 1:
+            main_stream.wait_stream(comm.be.torch_stream)
 
     def barrier():
         if world > 1:
@@ -207,12 +243,11 @@ def run_ours(args, rank, world, local_rank):
         barrier()
         e0.record()
         for s in range(args.steps):
-            prog.forward(x, probs, on_launch=lambda i, when, s=s: ev[s][i][when].record())
-            if world > 1:
-                dist.gather(probs, gathered, dst=0)
+            step(on_launch=lambda i, when, s=s: ev[s][i][when].record())
+        drain()
         e1.record()
         barrier()
-    launches = be.launches - launches0
+    launches = be.launches - launches0 + (args.steps if world > 1 else 0)  # + one NCCL gather per step
     be.sync()  # also surfaces a device-side timeout status, if any
     ms = e0.elapsed_time(e1)
     if world > 1:
@@ -233,8 +268,8 @@ def run_ours(args, rank, world, local_rank):
     e2e_steps = max(3, min(args.steps, 10))
     x_host = probs_host = None
     if not args.skip_e2e:
-        e2e_value, e2e_ms, x_host, probs_host = run_e2e(torch, dist, prog, x, probs, gathered, world, device, rows,
-                                                        e2e_steps, barrier)
+        e2e_value, e2e_ms, x_host, probs_host = run_e2e(torch, dist, prog, x, probs, world, device, rows, e2e_steps,
+                                                        barrier)
 
     cpu = None
     if rank == 0 and world == 1 and not args.skip_cpu_baseline:
@@ -259,10 +294,12 @@ def run_ours(args, rank, world, local_rank):
             "cpu_baseline": cpu, "e2e": e2e,
             "gpu_launches": launches, "clocks": clocks.summary()}))
     if world > 1:
+        barrier()
+        comm.close()
         dist.destroy_process_group()
 
 
-def run_e2e(torch, dist, prog, x, probs, gathered, world, device, rows, e2e_steps, barrier):
+def run_e2e(torch, dist, prog, x, probs, world, device, rows, e2e_steps, barrier):
     """End to end with host buffers (rank-local slice): H2D of X, forward, D2H of the probabilities."""
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     x_host = torch.empty((rows, WIDTH), dtype=torch.bfloat16).pin_memory()
@@ -274,9 +311,7 @@ def run_e2e(torch, dist, prog, x, probs, gathered, world, device, rows, e2e_step
     barrier()
     e0.record()
     for _ in range(e2e_steps):
-        prog.forward_host(x_host, probs_host, x_dev, probs)
-        if world > 1:
-            dist.gather(probs, gathered, dst=0)
+        prog.forward_host(x_host, probs_host, x_dev, probs)  # every rank returns its rows to its own host buffer
     e1.record()
     barrier()
     e2e_ms = e0.elapsed_time(e1)

@@ -166,7 +166,29 @@ int swcb200_fc_bf16(swcb200_ctx *ctx, int m, int n, int k, const void *a_bf16, i
                     const void *wp_bf16, int ldw, const float *bias, int act, void *c,
                     int c_dtype, int ldc);
 
-/* MaxPool / ReLU / add on bf16 NHWC storage (same semantics as the fp32 entry points). */
+/* filter fp32 [oC,kh,kw,iC] -> bf16, same index order (K-major for the implicit GEMM). */
+int swcb200_pack_filter_bf16(swcb200_ctx *ctx, const float *filter, const size_t *fdims,
+                             void *fp_bf16);
+
+/* Epilogue applied to a convolution's accumulator, in this order, each step optional:
+ * + conv bias; inference batch-norm as an affine map (computed in fp32); + residual;
+ * ReLU.  Covers Conv->BN->ReLU and Conv->BN->ElementAdd->ReLU chains. */
+typedef struct swcb200_conv_epilogue {
+    const float *bn_scale, *bn_bias, *bn_mean, *bn_var; /* all four or none */
+    float bn_eps;
+    const void *residual; /* same shape and dtype as the output, or NULL */
+    int relu;
+} swcb200_conv_epilogue;
+/* NHWC implicit-GEMM convolution on tensor cores (replaces the chain conv2d_f -> batchnormalization_f ->
+ * vecAdd_f -> relu_f, kernels.h:177-243, :496-517, :592-596, :575-580, in one launch).  input, filter
+ * (swcb200_pack_filter_bf16), output and residual bf16; bias and batch-norm vectors fp32.  stride 1,
+ * group 1, iC a multiple of 64, oC a multiple of 32 and <= 256, filter at most 96 KiB in bf16; other
+ * shapes return SWCB200_ERR_UNSUPPORTED.  pads[0] (top) and pads[1] (left) are read, as in conv2d_f. */
+int swcb200_conv2d_bf16(swcb200_ctx *ctx, void *output, const void *input, const void *fp_bf16,
+                        const float *bias, const size_t *odims, const size_t *idims,
+                        const size_t *fdims, const size_t *kernels, const size_t *strides,
+                        const size_t *pads, const swcb200_conv_epilogue *ep);
+/* MaxPool on bf16 NHWC storage (same semantics as maxpool_f). */
 int swcb200_maxpool_bf16(swcb200_ctx *ctx, const void *input, void *output, const size_t *idims,
                          const size_t *odims, const size_t *kernels, const size_t *strides,
                          const size_t *pads);

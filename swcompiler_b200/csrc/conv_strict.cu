@@ -64,6 +64,10 @@ __global__ void __launch_bounds__(256) conv_strict_kernel(float *__restrict__ ou
 
 }  // namespace
 
+int swc_conv_tc_from_f32(swcb200_ctx *ctx, float *output, const float *input, const float *filter, const float *bias,
+                         const size_t *odims, const size_t *idims, const size_t *fdims, const size_t *kernels,
+                         const size_t *strides, const size_t *pads);
+
 SWC_EXPORT int swcb200_conv2d_f(swcb200_ctx *ctx, float *output, const float *input, const float *filter,
                                 const float *bias, const size_t *odims, const size_t *idims, const size_t *fdims,
                                 const size_t *bdims, const size_t *kernels, const size_t *strides, const size_t *pads,
@@ -86,6 +90,10 @@ SWC_EXPORT int swcb200_conv2d_f(swcb200_ctx *ctx, float *output, const float *in
     const size_t npix = (size_t)g.N * g.OH * g.OW;
     if (npix * g.OC == 0) return SWCB200_OK;
     SWC_REQUIRE(ctx, output && input && filter && bias, SWCB200_ERR_BAD_ARG, "conv2d_f: null tensor");
+    if (ctx->precision == SWCB200_TC_BF16) {
+        int rc = swc_conv_tc_from_f32(ctx, output, input, filter, bias, odims, idims, fdims, kernels, strides, pads);
+        if (rc != SWCB200_ERR_UNSUPPORTED) return rc;  // shapes the tensor-core kernel does not take run strict
+    }
     dim3 grid((unsigned)((npix + kPix - 1) / kPix), (g.OC + kCo - 1) / kCo);
     SWC_REQUIRE(ctx, grid.y <= 65535, SWCB200_ERR_TOO_LARGE, "conv2d_f: too many output channels");
     conv_strict_kernel<<<grid, 256, 0, ctx->stream>>>(output, input, filter, bias, g);

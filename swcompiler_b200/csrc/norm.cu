@@ -48,6 +48,35 @@ __global__ void __launch_bounds__(256) batchnorm_kernel(float *__restrict__ out,
         s_[i] = (double)s_scale[c + i];
         b_[i] = (double)s_bias[c + i];
     }
+    if (fixed_c && kVec == 4) {
+        // main path: kU independent 128-bit loads in flight per thread
+        constexpr int kU = 4;
+        for (size_t base = t; base < total; base += nthreads * kU) {
+            float4 v[kU];
+#pragma unroll
+            for (int u = 0; u < kU; u++) {
+                size_t tt = base + (size_t)u * nthreads;
+                if (tt < total) v[u] = __ldcs(reinterpret_cast<const float4 *>(in + tt * 4));
+            }
+#pragma unroll
+            for (int u = 0; u < kU; u++) {
+                size_t tt = base + (size_t)u * nthreads;
+                if (tt >= total) continue;
+                const float x[4] = {v[u].x, v[u].y, v[u].z, v[u].w};
+                float y[4];
+#pragma unroll
+                for (int i = 0; i < 4; i++) {
+                    double d = (double)__fsub_rn(x[i], m_[i % kVec]);
+                    d = __dmul_rn(d, r_[i % kVec]);
+                    d = __dmul_rn(d, s_[i % kVec]);
+                    d = __dadd_rn(d, b_[i % kVec]);
+                    y[i] = (float)d;
+                }
+                __stcs(reinterpret_cast<float4 *>(out + tt * 4), make_float4(y[0], y[1], y[2], y[3]));
+            }
+        }
+        return;
+    }
     for (; t < total; t += nthreads) {
         if (!fixed_c) {
             c = (int)(t % cg) * kVec;

@@ -237,6 +237,33 @@ class Backend:
                    C.c_int(act), _p(out), C.c_int(L.BF16 if out.dtype == torch.bfloat16 else L.F32), C.c_int(n))
         return out
 
+    def pack_filter_bf16(self, filt):
+        """fp32 filter [oC, kh, kw, iC] -> bf16, same layout."""
+        self._f32(filt)
+        fp = self._new(filt.shape, torch.bfloat16)
+        self._call("pack_filter_bf16", _p(filt), _dims(filt.shape), _p(fp))
+        return fp
+
+    def conv2d_bf16(self, x, fp, bias, kernels, strides, pads, bn=None, residual=None, relu=False, out=None):
+        """Conv2d [-> BatchNormalization] [-> ElementAdd(residual)] [-> Relu] in one tensor-core launch.
+        x, fp (packed filter), residual, out: bf16 NHWC.  bn = (scale, bias, mean, var, eps) or None."""
+        odims = conv_out_dims(x.shape, fp.shape, kernels, strides, pads)
+        out = out if out is not None else self._new(odims, torch.bfloat16)
+
+        class Ep(C.Structure):
+            _fields_ = [("bn_scale", C.c_void_p), ("bn_bias", C.c_void_p), ("bn_mean", C.c_void_p),
+                        ("bn_var", C.c_void_p), ("bn_eps", C.c_float), ("residual", C.c_void_p), ("relu", C.c_int)]
+
+        ep = Ep()
+        if bn is not None:
+            ep.bn_scale, ep.bn_bias, ep.bn_mean, ep.bn_var = (t.data_ptr() for t in bn[:4])
+            ep.bn_eps = float(bn[4])
+        ep.residual = residual.data_ptr() if residual is not None else None
+        ep.relu = 1 if relu else 0
+        self._call("conv2d_bf16", _p(out), _p(x), _p(fp), _p(bias), _dims(odims), _dims(x.shape), _dims(fp.shape),
+                   _dims(kernels), _dims(strides), _dims(pads), C.byref(ep))
+        return out
+
     def maxpool_bf16(self, x, kernels, strides, pads, out=None):
         odims = pool_out_dims(x.shape, kernels, strides, pads)
         out = out if out is not None else self._new(odims, torch.bfloat16)

@@ -129,3 +129,54 @@ class FcPairProgram:
             done.record(cs)
             ms.wait_event(done)
         return self.y[:rows]
+
+
+class ResStageProgram:
+    """ResNet-style stage, NHWC bf16 storage: `blocks` x (Conv3x3-BN-ReLU-Conv3x3-BN-Add(skip)-ReLU), MaxPool 2x2/2.
+
+    Each Conv -> BatchNormalization [-> ElementAdd] -> Relu chain of the graph is ONE tensor-core launch (the
+    batch-norm becomes a per-channel affine map in the epilogue, the skip tensor is added there too); the
+    pool is one bandwidth-bound launch.  2 * blocks + 1 launches per forward instead of 7 * blocks + 1.
+    """
+
+    def __init__(self, be: Backend, convs, bns, max_batch: int, hw: int, ch: int):
+        self.be = be
+        self.fp = [be.pack_filter_bf16(c["w"]) for c in convs]
+        self.cb = [c["b"].contiguous() for c in convs]
+        self.bn = [(b["scale"], b["bias"], b["mean"], b["var"], float(b["eps"])) for b in bns]
+        shape = (max_batch, hw, hw, ch)
+        self.buf = [torch.empty(shape, dtype=torch.bfloat16, device=be.device) for _ in range(3)]
+        self.pooled = torch.empty((max_batch, hw // 2, hw // 2, ch), dtype=torch.bfloat16, device=be.device)
+        self.launches_per_forward = len(self.fp) + 1
+        self.hw, self.ch = hw, ch
+        be.sync()
+
+    def flops(self, batch: int) -> float:
+        return float(len(self.fp)) * 2.0 * batch * self.hw * self.hw * self.ch * 9 * self.ch
+
+    def forward(self, x_bf16: torch.Tensor, on_launch=None) -> torch.Tensor:
+        n = x_bf16.shape[0]
+        k3, s1, p1 = (3, 3), (1, 1), (1, 1, 1, 1)
+        be, cur = self.be, x_bf16
+        free = [b[:n] for b in self.buf]
+        li = 0
+        for blk in range(len(self.fp) // 2):
+            t, o = [b for b in free if b.data_ptr() != cur.data_ptr()][:2]
+            if on_launch:
+                on_launch(li, 0)
+            be.conv2d_bf16(cur, self.fp[2 * blk], self.cb[2 * blk], k3, s1, p1, bn=self.bn[2 * blk], relu=True, out=t)
+            if on_launch:
+                on_launch(li, 1)
+                on_launch(li + 1, 0)
+            be.conv2d_bf16(t, self.fp[2 * blk + 1], self.cb[2 * blk + 1], k3, s1, p1, bn=self.bn[2 * blk + 1],
+                           residual=cur, relu=True, out=o)
+            if on_launch:
+                on_launch(li + 1, 1)
+            li += 2
+            cur = o
+        if on_launch:
+            on_launch(li, 0)
+        out = be.maxpool_bf16(cur, (2, 2), (2, 2), (0, 0, 0, 0), out=self.pooled[:n])
+        if on_launch:
+            on_launch(li, 1)
+        return out

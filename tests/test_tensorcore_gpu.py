@@ -122,3 +122,88 @@ def test_fc_bf16_at_full_config3_size_sampled_rows(be, oracle):
     want = np.maximum(oracle.batchedadd_f(oracle.matrixMatrixMul_f(a_s, w.cpu().numpy()), bias.cpu().numpy()), 0)
     got = out[rows.cuda()].float().cpu().numpy()
     assert np.abs(got - cases.bf16_round(want)).max() <= 2e-2
+
+
+def _conv_case(r, n, h, w, c, oc, k, pads):
+    x = cases.bf16_round(r.standard_normal((n, h, w, c)).astype(np.float32))
+    f = cases.bf16_round((r.standard_normal((oc, k[0], k[1], c)) * np.sqrt(2.0 / (k[0] * k[1] * c))).astype(np.float32))
+    b = (r.standard_normal(oc) * 0.1).astype(np.float32)
+    return x, f, b
+
+
+@pytest.mark.parametrize("n,h,w,c,oc,k,pads", [
+    (1, 8, 8, 64, 64, (3, 3), (1, 1, 1, 1)),       # one 8x8 block, one tile with an empty second half
+    (2, 16, 16, 64, 64, (3, 3), (1, 1, 1, 1)),     # whole tiles
+    (3, 12, 20, 64, 32, (3, 3), (1, 1, 1, 1)),     # ragged blocks in both directions, odd block count, oC 32
+    (2, 9, 7, 128, 96, (1, 1), (0, 0, 0, 0)),      # 1x1, two channel chunks, oC 96
+    (1, 14, 14, 64, 128, (5, 5), (2, 2, 2, 2)),    # 5x5 (25 taps resident: 200 KiB > limit) -> must be refused
+    (2, 10, 10, 64, 64, (3, 3), (0, 0, 0, 0)),     # no padding: output 8x8
+    (1, 11, 13, 64, 64, (3, 2), (2, 0, 2, 0)),     # asymmetric window and padding
+])
+def test_conv2d_bf16_against_oracle(be, oracle, n, h, w, c, oc, k, pads):
+    r = np.random.default_rng(n * 1000 + h * 10 + oc)
+    x, f, b = _conv_case(r, n, h, w, c, oc, k, pads)
+    tx, tb = _bf16(x), torch.from_numpy(b).cuda()
+    fp = be.pack_filter_bf16(torch.from_numpy(f).cuda())
+    if k[0] * k[1] * c * oc * 2 > 96 * 1024:
+        with pytest.raises(swc.SwcError) as e:
+            be.conv2d_bf16(tx, fp, tb, k, (1, 1), pads)
+        assert e.value.status == swc._lib.ERR_UNSUPPORTED
+        return
+    want = oracle.conv2d_f(x, f, b, k, (1, 1), pads)
+    got = be.conv2d_bf16(tx, fp, tb, k, (1, 1), pads)
+    be.sync()
+    assert got.shape == want.shape
+    err = np.abs(got.float().cpu().numpy() - want)
+    assert np.all(err <= 1e-2 * np.abs(want) + 1e-2), err.max()   # bf16 store: 2^-9 relative, plus accumulation order
+    # conv -> batch-norm -> add(skip) -> relu in one launch
+    if want.shape == x.shape:
+        bn = [r.uniform(0.5, 1.5, oc).astype(np.float32), (r.standard_normal(oc) * 0.1).astype(np.float32),
+              (r.standard_normal(oc) * 0.1).astype(np.float32), r.uniform(0.5, 1.5, oc).astype(np.float32)]
+        ref = oracle.batchnormalization_f(want, bn[2], bn[3], bn[0], bn[1], 1e-5)
+        ref = oracle.relu_f(oracle.vecAdd_f(ref.reshape(-1), x.reshape(-1)).reshape(ref.shape))
+        tbn = [torch.from_numpy(v).cuda() for v in bn] + [1e-5]
+        got = be.conv2d_bf16(tx, fp, tb, k, (1, 1), pads, bn=tbn, residual=tx, relu=True)
+        be.sync()
+        err = np.abs(got.float().cpu().numpy() - ref)
+        assert np.all(err <= 1e-2 * np.abs(ref) + 1e-2), err.max()
+
+
+def test_conv2d_f_in_tensor_core_mode(be, oracle):
+    """fp32 drop-in entry point with the context in TC_BF16 mode; and a shape it cannot take falls to the strict kernel."""
+    r = np.random.default_rng(8)
+    x, f, b = _conv_case(r, 2, 12, 12, 64, 64, (3, 3), (1, 1, 1, 1))
+    want = oracle.conv2d_f(x, f, b, (3, 3), (1, 1), (1, 1, 1, 1))
+    got = be.conv2d_f(torch.from_numpy(x).cuda(), torch.from_numpy(f).cuda(), torch.from_numpy(b).cuda(), (3, 3), (1, 1),
+                      (1, 1, 1, 1))
+    be.sync()
+    assert np.abs(got.cpu().numpy() - want).max() <= 2e-3
+    x2, f2, b2 = _conv_case(r, 1, 9, 9, 3, 5, (3, 3), (1, 1, 1, 1))
+    want2 = oracle.conv2d_f(x2, f2, b2, (3, 3), (2, 2), (1, 1, 1, 1))
+    got2 = be.conv2d_f(torch.from_numpy(x2).cuda(), torch.from_numpy(f2).cuda(), torch.from_numpy(b2).cuda(), (3, 3),
+                       (2, 2), (1, 1, 1, 1))
+    be.sync()
+    assert np.array_equal(got2.cpu().numpy(), want2)   # strict kernel: bit-exact
+
+
+def test_config5_stage_slice_tensor_core(be, oracle):
+    """Two images of the [256,56,56,64] stage through the fused tensor-core program against the fp32 oracle chain."""
+    from swcompiler_b200.programs import ResStageProgram
+    c = cases.config5_res_stage(batch=2)
+    c["x"] = cases.bf16_round(c["x"])
+    for cv in c["conv"]:
+        cv["w"] = cases.bf16_round(cv["w"])
+    want = cases.res_stage_forward(oracle, c)
+    t = lambda a: torch.from_numpy(a).cuda()
+    prog = ResStageProgram(be, [dict(w=t(cv["w"]), b=t(cv["b"])) for cv in c["conv"]],
+                           [dict(scale=t(b["scale"]), bias=t(b["bias"]), mean=t(b["mean"]), var=t(b["var"]), eps=b["eps"])
+                            for b in c["bn"]], max_batch=2, hw=56, ch=64)
+    got = prog.forward(_bf16(c["x"]))
+    be.sync()
+    g = got.float().cpu().numpy()
+    assert g.shape == want.shape
+    err = np.abs(g - want)
+    print(f"config5 slice: max-abs err {err.max():.3e}, mean-abs err {err.mean():.3e}, ref max {np.abs(want).max():.2f}")
+    rel = err.max() / np.abs(want).max()
+    print(f"config5 slice: max-abs err over max-abs ref {rel:.3e}")
+    assert rel <= 2e-2 and err.mean() <= 1e-2 * np.abs(want).mean() + 1e-3   # six layers of bf16 storage
