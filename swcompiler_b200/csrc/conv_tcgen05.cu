@@ -55,8 +55,8 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap tmIn, const __grid_constant__
     float *s_alpha = reinterpret_cast<float *>(s_a + (size_t)p.stages * A_STAGE_BYTES);  // [OC]
     float *s_beta = s_alpha + p.OC;                             // [OC]
     uint64_t *full = reinterpret_cast<uint64_t *>(s_beta + p.OC);
-    uint64_t *empty = full + 8;
-    uint64_t *tmem_full = empty + 8;
+    uint64_t *empty = full + 9;
+    uint64_t *tmem_full = empty + 9;
     uint64_t *tmem_empty = tmem_full + 4;
     uint64_t *filter_bar = tmem_empty + 4;
     uint32_t *tmem_holder = reinterpret_cast<uint32_t *>(filter_bar + 1);
@@ -103,77 +103,122 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap tmIn, const __grid_constant__
 
     if (warp == 0) {
         // ------------------------------------------------------------ TMA producer
+        // The whole warp walks the loop and waits on the barriers together; lane 0 alone issues the copies.
+        // (A lone lane looping while its 31 siblings sit at the final barrier makes every instruction of
+        // the loop several times slower.)
         if (lane == 0) {
             // the filter, once: one box [OC x 64] per (tap, channel chunk)
             mbar_expect_tx(filter_bar, (uint32_t)p.filter_bytes);
             for (int t = 0; t < taps; t++)
                 for (int kc = 0; kc < p.kchunks; kc++)
                     tma_load_3d(s_filter + (size_t)(t * p.kchunks + kc) * p.OC * 128, &tmF, filter_bar, kc * BK, t, 0);
-            uint32_t g = 0;
-            bool ok = true;
-            const int bpi = p.blocks_h * p.blocks_w;
-            for (long long tile = blockIdx.x; tile < p.num_tiles && ok; tile += gridDim.x) {
-                int bn[2], bh0[2], bw0[2];
-                for (int h = 0; h < 2; h++) {
-                    long long b = tile * 2 + h;
-                    int n = (int)(b / bpi), r = (int)(b - (long long)n * bpi);
-                    bn[h] = n;  // n >= N for the odd block past the end: every element out of bounds -> zeros
-                    bh0[h] = (r / p.blocks_w) * 8;
-                    bw0[h] = (r % p.blocks_w) * 8;
-                }
-                for (int kx = 0; kx < p.kh && ok; kx++)
-                    for (int ky = 0; ky < p.kw && ok; ky++)
-                        for (int kc = 0; kc < p.kchunks; kc++, g++) {
-                            const int s = g % p.stages;
-                            const uint32_t ph = (g / p.stages) & 1;
-                            if (!mbar_wait(&empty[s], ph ^ 1, p.status, kWaitEmpty)) {
-                                ok = false;
-                                break;
-                            }
-                            mbar_expect_tx(&full[s], A_STAGE_BYTES);
-                            uint8_t *sa = s_a + (size_t)s * A_STAGE_BYTES;
-                            for (int h = 0; h < 2; h++)
-                                tma_load_4d(sa + h * (BLOCK_PIX * 128), &tmIn, &full[s], kc * BK, bw0[h] + ky - p.pl,
-                                            bh0[h] + kx - p.pt, bn[h]);
-                        }
+        }
+        __syncwarp();
+        uint32_t issued = 0, ph = 0;
+        int st = 0;
+        bool ok = true;
+        const int bpi = p.blocks_h * p.blocks_w;
+        for (long long tile = blockIdx.x; tile < p.num_tiles && ok; tile += gridDim.x) {
+            int bn[2], bh0[2], bw0[2];
+            for (int h = 0; h < 2; h++) {
+                long long b = tile * 2 + h;
+                int n = (int)(b / bpi), r = (int)(b - (long long)n * bpi);
+                bn[h] = n;  // n >= N for the odd block past the end: every element out of bounds -> zeros
+                bh0[h] = (r / p.blocks_w) * 8;
+                bw0[h] = (r % p.blocks_w) * 8;
             }
-            const uint32_t issued = g;
+            for (int kx = 0; kx < p.kh && ok; kx++)
+                for (int ky = 0; ky < p.kw && ok; ky++)
+                    for (int kc = 0; kc < p.kchunks; kc++) {
+                        ok = mbar_wait(&empty[st], ph ^ 1, p.status, kWaitEmpty);
+                        ok = __all_sync(0xffffffffu, ok);
+                        if (!ok) break;
+                        if (lane == 0) {
+                            uint8_t *sa = s_a + (size_t)st * A_STAGE_BYTES;
+                            mbar_expect_tx(&full[st], A_STAGE_BYTES);
+                            tma_load_4d(sa, &tmIn, &full[st], kc * BK, bw0[0] + ky - p.pl, bh0[0] + kx - p.pt, bn[0]);
+                            tma_load_4d(sa + BLOCK_PIX * 128, &tmIn, &full[st], kc * BK, bw0[1] + ky - p.pl,
+                                        bh0[1] + kx - p.pt, bn[1]);
+                        }
+                        __syncwarp();
+                        issued++;
+                        if (++st == p.stages) {
+                            st = 0;
+                            ph ^= 1;
+                        }
+                    }
+        }
+        // Drain: do not leave while copies may still be landing in this CTA's shared memory.  Walk back
+        // over the last fills of every stage and wait for each to complete.
+        {
+            int s2 = st;
+            uint32_t ph2 = ph;
             for (uint32_t back = 0; back < (uint32_t)p.stages && back < issued; back++) {
-                const uint32_t gi = issued - 1 - back;
-                if (!mbar_wait(&full[gi % p.stages], (gi / p.stages) & 1, p.status, kWaitDrain)) break;
+                if (s2 == 0) {
+                    s2 = p.stages;
+                    ph2 ^= 1;
+                }
+                s2--;
+                if (!mbar_wait(&full[s2], ph2, p.status, kWaitDrain)) break;
             }
             mbar_wait(filter_bar, 0, p.status, kWaitDrain);
         }
     } else if (warp == 1) {
-        // ------------------------------------------------------------ MMA issuer
-        if (lane == 0) {
-            const uint32_t idesc = idesc_bf16_f32(BM, p.OC);
-            bool ok = mbar_wait(filter_bar, 0, p.status, kWaitFull);
+        // ------------------------------------------------------------ MMA issuer (whole warp walks, lane 0 issues)
+        const uint32_t idesc = idesc_bf16_f32(BM, p.OC);
+        bool ok = mbar_wait(filter_bar, 0, p.status, kWaitFull);
+        ok = __all_sync(0xffffffffu, ok);
+        tc_fence_after();
+        uint32_t it = 0, ph = 0;
+        int st = 0;
+        // descriptors differ from stage to stage and from tap to tap only in the 14-bit address field
+        const uint64_t da0 = smem_desc_sw128(smem_u32(s_a)), db0 = smem_desc_sw128(smem_u32(s_filter));
+        const uint64_t b_step = (uint64_t)((p.OC * 128) >> 4);
+        for (long long tile = blockIdx.x; tile < p.num_tiles && ok; tile += gridDim.x, it++) {
+            const uint32_t buf = it % p.num_acc, aph = (it / p.num_acc) & 1;
+            ok = mbar_wait(&tmem_empty[buf], aph ^ 1, p.status, kWaitTmemEmpty);
+            ok = __all_sync(0xffffffffu, ok);
+            if (!ok) break;
             tc_fence_after();
-            uint32_t g = 0, it = 0;
-            const uint32_t sf = smem_u32(s_filter);
-            for (long long tile = blockIdx.x; tile < p.num_tiles && ok; tile += gridDim.x, it++) {
-                const uint32_t buf = it % p.num_acc, aph = (it / p.num_acc) & 1;
-                if (!mbar_wait(&tmem_empty[buf], aph ^ 1, p.status, kWaitTmemEmpty)) break;
-                tc_fence_after();
-                const uint32_t d_tmem = tmem_base + buf * p.acc_stride;
-                for (int ks = 0; ks < ksteps; ks++, g++) {
-                    const int s = g % p.stages;
-                    const uint32_t ph = (g / p.stages) & 1;
-                    if (!mbar_wait(&full[s], ph, p.status, kWaitFull)) {
-                        ok = false;
-                        break;
+            const uint32_t d_tmem = tmem_base + buf * p.acc_stride;
+            uint64_t db = db0;
+            // One round per filter row: wait for its kw * kchunks stages, issue all their MMAs back to back,
+            // then release the stages.  Batching keeps the per-round cost of the barrier hand-shake from
+            // setting the pace when N = oC is small and each MMA is short.
+            const int per_row = p.kw * p.kchunks;
+            for (int kx = 0; kx < p.kh && ok; kx++) {
+                int s2 = st;
+                uint32_t ph2 = ph;
+                for (int i = 0; i < per_row; i++) {
+                    ok = mbar_wait(&full[s2], ph2, p.status, kWaitFull) && ok;
+                    if (++s2 == p.stages) {
+                        s2 = 0;
+                        ph2 ^= 1;
                     }
-                    tc_fence_after();
-                    const uint64_t da = smem_desc_sw128(smem_u32(s_a + (size_t)s * A_STAGE_BYTES));
-                    const uint64_t db = smem_desc_sw128(sf + (uint32_t)ks * p.OC * 128);
-#pragma unroll
-                    for (int j = 0; j < BK / UMMA_K; j++)
-                        umma_bf16(d_tmem, da + 2 * j, db + 2 * j, idesc, (uint32_t)((ks | j) != 0));
-                    umma_commit(&empty[s]);
                 }
-                if (ok) umma_commit(&tmem_full[buf]);
+                ok = __all_sync(0xffffffffu, ok);
+                if (!ok) break;
+                tc_fence_after();
+                if (lane == 0) {
+                    int s3 = st;
+                    for (int i = 0; i < per_row; i++) {
+                        const uint64_t da = da0 + (uint64_t)s3 * (A_STAGE_BYTES >> 4);
+                        // advancing K by 16 elements = 32 bytes inside the swizzle row: +2 in the >>4 address field
+                        umma_bf16(d_tmem, da, db, idesc, (uint32_t)((kx | i) != 0));
+                        umma_bf16(d_tmem, da + 2, db + 2, idesc, 1u);
+                        umma_bf16(d_tmem, da + 4, db + 4, idesc, 1u);
+                        umma_bf16(d_tmem, da + 6, db + 6, idesc, 1u);
+                        umma_commit(&empty[s3]);  // stage reusable once the MMAs issued so far have read it
+                        db += b_step;
+                        if (++s3 == p.stages) s3 = 0;
+                    }
+                }
+                __syncwarp();
+                st = s2;
+                ph = ph2;
             }
+            if (ok && lane == 0) umma_commit(&tmem_full[buf]);
+            __syncwarp();
         }
     } else {
         // ------------------------------------------------------------ epilogue: one thread per output pixel
@@ -256,10 +301,10 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap tmIn, const __grid_constant__
         }
     }
 
+    __syncwarp();
     tc_fence_before();
     __syncthreads();
     if (warp == 1) {
-        __syncwarp();
         tc_fence_after();
         tmem_dealloc(tmem_base, (uint32_t)p.tmem_cols);
     }
@@ -298,8 +343,9 @@ int swc_conv_tc(swcb200_ctx *ctx, void *output, int out_dtype, const void *input
     p.tmem_cols = p.acc_stride * p.num_acc;
     const int fixed = p.filter_bytes + 2 * p.OC * 4 + 256 + 1024;
     p.stages = (kMaxSmem - fixed) / A_STAGE_BYTES;
-    if (p.stages > 8) p.stages = 8;
-    SWC_REQUIRE(ctx, p.stages >= 2, SWCB200_ERR_UNSUPPORTED, "conv2d_bf16: not enough shared memory for the pipeline");
+    if (p.stages > 9) p.stages = 9;
+    SWC_REQUIRE(ctx, p.stages >= 2 && p.stages >= p.kw * p.kchunks, SWCB200_ERR_UNSUPPORTED,
+                "conv2d_bf16: a filter row (kw * iC/64 = %d stages) does not fit the %d-stage ring", p.kw * p.kchunks, p.stages);
     p.bias = bias;
     if (ep) {
         const int nbn = (ep->bn_scale != nullptr) + (ep->bn_bias != nullptr) + (ep->bn_mean != nullptr) + (ep->bn_var != nullptr);

@@ -16,7 +16,6 @@ namespace tc {
 // ---- device status codes written by kernels (0 = clean)
 enum : int { kWaitFull = 1, kWaitEmpty = 2, kWaitTmemFull = 3, kWaitTmemEmpty = 4, kWaitDrain = 5 };
 
-constexpr unsigned long long kWaitLimitNs = 2000000000ull;  // 2 s
 
 __device__ __forceinline__ uint32_t smem_u32(const void *p) { return (uint32_t)__cvta_generic_to_shared(p); }
 
@@ -61,14 +60,19 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t *bar, uint32_t parity) {
         : "memory");
     return ok != 0;
 }
-// Bounded wait: false (and `code` stored to *status) once kWaitLimitNs has passed.
+// Bounded wait: false (and `code` stored to *status) once the limit has passed.  The limit is counted in
+// SM clock cycles (clock64 is a cheap per-SM counter; the nanosecond %globaltimer is served by a remote
+// unit and costs on the order of a microsecond per read, which would tax every wait that is not
+// satisfied at the first probe).  4e9 cycles is 2 s at 2 GHz and 3 s at the 1.3 GHz a power-capped GEMM
+// settles at.
+constexpr long long kWaitLimitCycles = 4000000000ll;
 __device__ __forceinline__ bool mbar_wait(uint64_t *bar, uint32_t parity, int *status, int code) {
     if (mbar_try_wait(bar, parity)) return true;
-    const unsigned long long t0 = globaltimer_ns();
+    const long long t0 = clock64();
     uint32_t spins = 0;
     while (!mbar_try_wait(bar, parity)) {
-        if ((++spins & 0xff) == 0) {
-            if (globaltimer_ns() - t0 > kWaitLimitNs) {
+        if ((++spins & 0x3f) == 0) {
+            if (clock64() - t0 > kWaitLimitCycles) {
                 atomicCAS(status, 0, code);
                 return false;
             }

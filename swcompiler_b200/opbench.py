@@ -108,6 +108,35 @@ def main():
         print(json.dumps({"kernel": name, "bound": "tensor", "us": t * 1e6, "achieved": fl / t / 1e12, "unit": "TFLOP/s",
                           "peak": tflops, "frac": fl / t / 1e12 / tflops, "peak_source": src + " (burst)", "flops": fl}))
         del a, wp, o
+    # config 5: 3x3 64->64 convolution on [256,56,56,64] with the fused epilogue, and the whole stage
+    if not args.only or "conv" in args.only or "stage" in args.only:
+        from .programs import ResStageProgram
+        n, hw, ch = 256, 56, 64
+        xin = torch.randn((n, hw, hw, ch), generator=g, device=dev).to(torch.bfloat16)
+        convs = [dict(w=torch.randn((ch, 3, 3, ch), generator=g, device=dev) * (2.0 / (9 * ch)) ** 0.5,
+                      b=torch.zeros(ch, device=dev)) for _ in range(6)]
+        bns = [dict(scale=torch.rand(ch, generator=g, device=dev) + 0.5, bias=torch.randn(ch, generator=g, device=dev) * 0.1,
+                    mean=torch.randn(ch, generator=g, device=dev) * 0.1, var=torch.rand(ch, generator=g, device=dev) + 0.5,
+                    eps=1e-5) for _ in range(6)]
+        prog = ResStageProgram(be, convs, bns, max_batch=n, hw=hw, ch=ch)
+        o = torch.empty_like(xin)
+        fl = 2.0 * n * hw * hw * ch * 9 * ch
+        for name, fn in [
+            ("conv2d_bf16 3x3 64->64 [256,56,56,64] +BN+ReLU",
+             lambda: be.conv2d_bf16(xin, prog.fp[0], prog.cb[0], (3, 3), (1, 1), (1, 1, 1, 1), bn=prog.bn[0], relu=True, out=o)),
+            ("conv2d_bf16 3x3 64->64 [256,56,56,64] +BN+Add+ReLU",
+             lambda: be.conv2d_bf16(xin, prog.fp[1], prog.cb[1], (3, 3), (1, 1), (1, 1, 1, 1), bn=prog.bn[1], residual=xin,
+                                    relu=True, out=o)),
+        ]:
+            t = _time(fn, args.iters)
+            print(json.dumps({"kernel": name, "bound": "tensor", "us": t * 1e6, "achieved": fl / t / 1e12, "unit": "TFLOP/s",
+                              "peak": tflops, "frac": fl / t / 1e12 / tflops, "peak_source": src + " (burst)", "flops": fl,
+                              "hbm_GBps": (2 * xin.numel() * 2) / t / 1e9}))
+        t = _time(lambda: prog.forward(xin), args.iters)
+        print(json.dumps({"kernel": "res stage forward (config 5): 6 fused convs + maxpool, batch 256", "bound": "tensor",
+                          "us": t * 1e6, "achieved": prog.flops(n) / t / 1e12, "unit": "TFLOP/s", "peak": tflops,
+                          "frac": prog.flops(n) / t / 1e12 / tflops, "peak_source": src + " (burst)",
+                          "samples_per_s": n / t, "launches": prog.launches_per_forward}))
     be.sync()
 
 
