@@ -12,8 +12,13 @@
 //     channels are exactly one 128-byte swizzle row, which makes the box a K-major UMMA operand as is.
 //   * The whole filter stays resident in shared memory for the life of the (persistent) CTA:
 //     kh*kw*(iC/64) slices of [oC x 64] loaded once by TMA.
-//   * warp 0 produces A stages (ring of up to 8), warp 1 issues tcgen05.mma (4 per stage, M128 x N=oC x K16),
-//     warps 2-5 run the epilogue out of up to four tensor-memory accumulators while the next tiles compute.
+//   * Shared-memory barrier operations cost on the order of 100 cycles each on this part, and one MMA of
+//     this shape (N = oC = 64) lasts well under that, so the pipeline hands over a whole filter ROW at a
+//     time: a stage holds the A operands of the kw taps of one filter row (kw * iC/64 slots of 16 KiB),
+//     filled by two producer warps (warp 0: the first 8x8 block of every slot, warp 6: the second), one
+//     barrier wait and one expect-tx per producer per row.  Warp 1 waits once per row, issues all of its
+//     tcgen05.mma (4 per slot, M128 x N=oC x K16) back to back and releases the row with one commit.
+//     Warps 2-5 run the epilogue out of up to four tensor-memory accumulators while the next tiles compute.
 //   Restrictions: stride 1, group 1, iC a multiple of 64, oC a multiple of 32 and <= 256, filter at most
 //   96 KiB in bf16.  Other shapes return SWCB200_ERR_UNSUPPORTED (the strict kernel takes them).
 #include "tc_common.cuh"
@@ -25,7 +30,7 @@ using namespace tc;
 constexpr int BM = 128, BK = 64, UMMA_K = 16;
 constexpr int BLOCK_PIX = 64;            // 8 x 8 pixels
 constexpr int A_STAGE_BYTES = BM * 128;  // 16 KiB
-constexpr int kThreads = 192;
+constexpr int kThreads = 224;  // producer A, MMA issuer, 4 epilogue warps, producer B
 constexpr int kMaxFilterBytes = 96 * 1024;
 constexpr int kMaxSmem = 227 * 1024;
 
@@ -34,7 +39,7 @@ struct ConvParams {
     int kchunks;            // C / 64
     int blocks_h, blocks_w; // 8x8 blocks per image
     long long num_blocks, num_tiles;
-    int stages, acc_stride, num_acc, tmem_cols;
+    int stages, slots, acc_stride, num_acc, tmem_cols;  // stages = row stages in the ring, slots = 16 KiB slots per row
     int filter_bytes;
     const float *bias;
     const float *bn_scale, *bn_bias, *bn_mean, *bn_var;
@@ -51,30 +56,30 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap tmIn, const __grid_constant__
     extern __shared__ uint8_t smem_raw[];
     uint8_t *smem = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
     uint8_t *s_filter = smem;                                   // [taps*kchunks][OC x 128 B]
-    uint8_t *s_a = smem + p.filter_bytes;                       // stages x 16 KiB
-    float *s_alpha = reinterpret_cast<float *>(s_a + (size_t)p.stages * A_STAGE_BYTES);  // [OC]
+    uint8_t *s_a = smem + p.filter_bytes;                       // stages x slots x 16 KiB
+    const int row_bytes = p.slots * A_STAGE_BYTES;
+    float *s_alpha = reinterpret_cast<float *>(s_a + (size_t)p.stages * row_bytes);  // [OC]
     float *s_beta = s_alpha + p.OC;                             // [OC]
     uint64_t *full = reinterpret_cast<uint64_t *>(s_beta + p.OC);
-    uint64_t *empty = full + 9;
-    uint64_t *tmem_full = empty + 9;
+    uint64_t *empty = full + 8;
+    uint64_t *tmem_full = empty + 8;
     uint64_t *tmem_empty = tmem_full + 4;
     uint64_t *filter_bar = tmem_empty + 4;
     uint32_t *tmem_holder = reinterpret_cast<uint32_t *>(filter_bar + 1);
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int taps = p.kh * p.kw;
-    const int ksteps = taps * p.kchunks;  // stages consumed per tile
 
     if (threadIdx.x == 0) {
         tma_prefetch_desc(&tmIn);
         tma_prefetch_desc(&tmF);
         for (int s = 0; s < p.stages; s++) {
-            mbar_init(&full[s], 1);
-            mbar_init(&empty[s], 1);
+            mbar_init(&full[s], 2);   // one arrive(+expect-tx) from each producer warp
+            mbar_init(&empty[s], 1);  // one tcgen05.commit
         }
         for (int b = 0; b < p.num_acc; b++) {
             mbar_init(&tmem_full[b], 1);
-            mbar_init(&tmem_empty[b], 128);
+            mbar_init(&tmem_empty[b], 4);  // one arrival per epilogue warp
         }
         mbar_init(filter_bar, 1);
         fence_barrier_init();
@@ -101,12 +106,12 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap tmIn, const __grid_constant__
     tc_fence_after();
     const uint32_t tmem_base = *tmem_holder;
 
-    if (warp == 0) {
-        // ------------------------------------------------------------ TMA producer
-        // The whole warp walks the loop and waits on the barriers together; lane 0 alone issues the copies.
-        // (A lone lane looping while its 31 siblings sit at the final barrier makes every instruction of
-        // the loop several times slower.)
-        if (lane == 0) {
+    if (warp == 0 || warp == 6) {
+        // ------------------------------------------------------------ TMA producers
+        // Lane 0 of each producer warp does the work; the other lanes wait at the __syncwarp of each round
+        // (a lone lane looping while its siblings sit at the CTA barrier runs several times slower).
+        const int half = warp == 0 ? 0 : 1;  // which 8x8 block of every slot this warp fills
+        if (warp == 0 && lane == 0) {
             // the filter, once: one box [OC x 64] per (tap, channel chunk)
             mbar_expect_tx(filter_bar, (uint32_t)p.filter_bytes);
             for (int t = 0; t < taps; t++)
@@ -118,39 +123,34 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap tmIn, const __grid_constant__
         int st = 0;
         bool ok = true;
         const int bpi = p.blocks_h * p.blocks_w;
+        const uint32_t tx_bytes = (uint32_t)p.slots * (BLOCK_PIX * 128);
         for (long long tile = blockIdx.x; tile < p.num_tiles && ok; tile += gridDim.x) {
-            int bn[2], bh0[2], bw0[2];
-            for (int h = 0; h < 2; h++) {
-                long long b = tile * 2 + h;
-                int n = (int)(b / bpi), r = (int)(b - (long long)n * bpi);
-                bn[h] = n;  // n >= N for the odd block past the end: every element out of bounds -> zeros
-                bh0[h] = (r / p.blocks_w) * 8;
-                bw0[h] = (r % p.blocks_w) * 8;
-            }
-            for (int kx = 0; kx < p.kh && ok; kx++)
-                for (int ky = 0; ky < p.kw && ok; ky++)
-                    for (int kc = 0; kc < p.kchunks; kc++) {
-                        ok = mbar_wait(&empty[st], ph ^ 1, p.status, kWaitEmpty);
-                        ok = __all_sync(0xffffffffu, ok);
-                        if (!ok) break;
-                        if (lane == 0) {
-                            uint8_t *sa = s_a + (size_t)st * A_STAGE_BYTES;
-                            mbar_expect_tx(&full[st], A_STAGE_BYTES);
-                            tma_load_4d(sa, &tmIn, &full[st], kc * BK, bw0[0] + ky - p.pl, bh0[0] + kx - p.pt, bn[0]);
-                            tma_load_4d(sa + BLOCK_PIX * 128, &tmIn, &full[st], kc * BK, bw0[1] + ky - p.pl,
-                                        bh0[1] + kx - p.pt, bn[1]);
-                        }
-                        __syncwarp();
-                        issued++;
-                        if (++st == p.stages) {
-                            st = 0;
-                            ph ^= 1;
-                        }
+            const long long b = tile * 2 + half;
+            const int bn = (int)(b / bpi), r = (int)(b - (long long)bn * bpi);  // bn >= N past the end: all zeros
+            const int bh0 = (r / p.blocks_w) * 8 - p.pt, bw0 = (r % p.blocks_w) * 8 - p.pl;
+            for (int kx = 0; kx < p.kh; kx++) {
+                if (lane == 0) {
+                    ok = mbar_wait(&empty[st], ph ^ 1, p.status, kWaitEmpty);
+                    if (ok) {
+                        mbar_expect_tx(&full[st], tx_bytes);
+                        uint8_t *dst = s_a + (size_t)st * row_bytes + half * (BLOCK_PIX * 128);
+                        for (int ky = 0; ky < p.kw; ky++)
+                            for (int kc = 0; kc < p.kchunks; kc++, dst += A_STAGE_BYTES)
+                                tma_load_4d(dst, &tmIn, &full[st], kc * BK, bw0 + ky, bh0 + kx, bn);
                     }
+                }
+                ok = __shfl_sync(0xffffffffu, ok, 0);
+                if (!ok) break;
+                issued++;
+                if (++st == p.stages) {
+                    st = 0;
+                    ph ^= 1;
+                }
+            }
         }
         // Drain: do not leave while copies may still be landing in this CTA's shared memory.  Walk back
-        // over the last fills of every stage and wait for each to complete.
-        {
+        // over the last fill of every stage and wait for it to complete.
+        if (lane == 0) {
             int s2 = st;
             uint32_t ph2 = ph;
             for (uint32_t back = 0; back < (uint32_t)p.stages && back < issued; back++) {
@@ -161,64 +161,53 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap tmIn, const __grid_constant__
                 s2--;
                 if (!mbar_wait(&full[s2], ph2, p.status, kWaitDrain)) break;
             }
-            mbar_wait(filter_bar, 0, p.status, kWaitDrain);
+            if (warp == 0) mbar_wait(filter_bar, 0, p.status, kWaitDrain);
         }
+        __syncwarp();
     } else if (warp == 1) {
-        // ------------------------------------------------------------ MMA issuer (whole warp walks, lane 0 issues)
+        // ------------------------------------------------------------ MMA issuer (lane 0 works, the warp re-converges each round)
         const uint32_t idesc = idesc_bf16_f32(BM, p.OC);
-        bool ok = mbar_wait(filter_bar, 0, p.status, kWaitFull);
-        ok = __all_sync(0xffffffffu, ok);
+        bool ok = true;
+        if (lane == 0) ok = mbar_wait(filter_bar, 0, p.status, kWaitFull);
+        ok = __shfl_sync(0xffffffffu, ok, 0);
         tc_fence_after();
         uint32_t it = 0, ph = 0;
         int st = 0;
-        // descriptors differ from stage to stage and from tap to tap only in the 14-bit address field
+        // descriptors differ from slot to slot and from tap to tap only in the 14-bit address field
         const uint64_t da0 = smem_desc_sw128(smem_u32(s_a)), db0 = smem_desc_sw128(smem_u32(s_filter));
         const uint64_t b_step = (uint64_t)((p.OC * 128) >> 4);
         for (long long tile = blockIdx.x; tile < p.num_tiles && ok; tile += gridDim.x, it++) {
             const uint32_t buf = it % p.num_acc, aph = (it / p.num_acc) & 1;
-            ok = mbar_wait(&tmem_empty[buf], aph ^ 1, p.status, kWaitTmemEmpty);
-            ok = __all_sync(0xffffffffu, ok);
-            if (!ok) break;
-            tc_fence_after();
-            const uint32_t d_tmem = tmem_base + buf * p.acc_stride;
-            uint64_t db = db0;
-            // One round per filter row: wait for its kw * kchunks stages, issue all their MMAs back to back,
-            // then release the stages.  Batching keeps the per-round cost of the barrier hand-shake from
-            // setting the pace when N = oC is small and each MMA is short.
-            const int per_row = p.kw * p.kchunks;
-            for (int kx = 0; kx < p.kh && ok; kx++) {
-                int s2 = st;
-                uint32_t ph2 = ph;
-                for (int i = 0; i < per_row; i++) {
-                    ok = mbar_wait(&full[s2], ph2, p.status, kWaitFull) && ok;
-                    if (++s2 == p.stages) {
-                        s2 = 0;
-                        ph2 ^= 1;
-                    }
-                }
-                ok = __all_sync(0xffffffffu, ok);
-                if (!ok) break;
+            if (lane == 0) {
+                ok = mbar_wait(&tmem_empty[buf], aph ^ 1, p.status, kWaitTmemEmpty);
                 tc_fence_after();
-                if (lane == 0) {
-                    int s3 = st;
-                    for (int i = 0; i < per_row; i++) {
-                        const uint64_t da = da0 + (uint64_t)s3 * (A_STAGE_BYTES >> 4);
+                const uint32_t d_tmem = tmem_base + buf * p.acc_stride;
+                uint64_t db = db0;
+                for (int kx = 0; kx < p.kh && ok; kx++) {
+                    ok = mbar_wait(&full[st], ph, p.status, kWaitFull);
+                    if (!ok) break;
+                    tc_fence_after();
+                    uint64_t da = da0 + (uint64_t)st * (uint64_t)(row_bytes >> 4);
+                    for (int i = 0; i < p.slots; i++) {
                         // advancing K by 16 elements = 32 bytes inside the swizzle row: +2 in the >>4 address field
                         umma_bf16(d_tmem, da, db, idesc, (uint32_t)((kx | i) != 0));
                         umma_bf16(d_tmem, da + 2, db + 2, idesc, 1u);
                         umma_bf16(d_tmem, da + 4, db + 4, idesc, 1u);
                         umma_bf16(d_tmem, da + 6, db + 6, idesc, 1u);
-                        umma_commit(&empty[s3]);  // stage reusable once the MMAs issued so far have read it
+                        da += A_STAGE_BYTES >> 4;
                         db += b_step;
-                        if (++s3 == p.stages) s3 = 0;
+                    }
+                    umma_commit(&empty[st]);  // the row's slots are reusable once these MMAs have read them
+                    if (++st == p.stages) {
+                        st = 0;
+                        ph ^= 1;
                     }
                 }
-                __syncwarp();
-                st = s2;
-                ph = ph2;
+                if (ok) umma_commit(&tmem_full[buf]);
             }
-            if (ok && lane == 0) umma_commit(&tmem_full[buf]);
-            __syncwarp();
+            ok = __shfl_sync(0xffffffffu, ok, 0);
+            st = __shfl_sync(0xffffffffu, st, 0);
+            ph = __shfl_sync(0xffffffffu, ph, 0);
         }
     } else {
         // ------------------------------------------------------------ epilogue: one thread per output pixel
@@ -229,8 +218,9 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap tmIn, const __grid_constant__
         uint32_t it = 0;
         for (long long tile = blockIdx.x; tile < p.num_tiles; tile += gridDim.x, it++) {
             const uint32_t buf = it % p.num_acc, aph = (it / p.num_acc) & 1;
-            bool ok = mbar_wait(&tmem_full[buf], aph, p.status, kWaitTmemFull);
-            ok = __all_sync(0xffffffffu, ok);
+            bool ok = true;
+            if (lane == 0) ok = mbar_wait(&tmem_full[buf], aph, p.status, kWaitTmemFull);
+            ok = __shfl_sync(0xffffffffu, ok, 0);
             if (!ok) break;
             tc_fence_after();
             const long long b = tile * 2 + half;
@@ -297,7 +287,8 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap tmIn, const __grid_constant__
                 }
             }
             tc_fence_before();
-            mbar_arrive(&tmem_empty[buf]);
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&tmem_empty[buf]);
         }
     }
 
@@ -342,10 +333,12 @@ int swc_conv_tc(swcb200_ctx *ctx, void *output, int out_dtype, const void *input
     p.num_acc = 512 / p.acc_stride < 4 ? 512 / p.acc_stride : 4;
     p.tmem_cols = p.acc_stride * p.num_acc;
     const int fixed = p.filter_bytes + 2 * p.OC * 4 + 256 + 1024;
-    p.stages = (kMaxSmem - fixed) / A_STAGE_BYTES;
-    if (p.stages > 9) p.stages = 9;
-    SWC_REQUIRE(ctx, p.stages >= 2 && p.stages >= p.kw * p.kchunks, SWCB200_ERR_UNSUPPORTED,
-                "conv2d_bf16: a filter row (kw * iC/64 = %d stages) does not fit the %d-stage ring", p.kw * p.kchunks, p.stages);
+    p.slots = p.kw * p.kchunks;
+    p.stages = (kMaxSmem - fixed) / (p.slots * A_STAGE_BYTES);
+    if (p.stages > 8) p.stages = 8;
+    if (p.stages < 2)
+        return swc_fail(ctx, SWCB200_ERR_UNSUPPORTED, "conv2d_bf16: two filter rows of operands (2 x %d KiB) do not fit beside the filter",
+                        p.slots * A_STAGE_BYTES / 1024);
     p.bias = bias;
     if (ep) {
         const int nbn = (ep->bn_scale != nullptr) + (ep->bn_bias != nullptr) + (ep->bn_mean != nullptr) + (ep->bn_var != nullptr);
@@ -376,7 +369,7 @@ int swc_conv_tc(swcb200_ctx *ctx, void *output, int out_dtype, const void *input
         int rc = tc::make_tmap_bf16(ctx, &tmF, filt, 3, dims, str, box);
         if (rc) return rc;
     }
-    const size_t smem = (size_t)p.filter_bytes + (size_t)p.stages * A_STAGE_BYTES + 2 * p.OC * 4 + 256 + 1024;
+    const size_t smem = (size_t)p.filter_bytes + (size_t)p.stages * p.slots * A_STAGE_BYTES + 2 * p.OC * 4 + 256 + 1024;
     if (!ctx->conv_attr_set) {
         SWC_CUDA(ctx, cudaFuncSetAttribute(conv_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kMaxSmem));
         ctx->conv_attr_set = true;
