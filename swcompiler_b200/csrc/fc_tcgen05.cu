@@ -16,6 +16,8 @@
 //     128-bit global stores.  Two accumulators (2 x 256 columns = all 512 of the SM) alternate, so the
 //     epilogue of tile i overlaps the main loop of tile i+1.
 //   Out-of-range rows/columns/k are zero-filled by TMA on the way in and masked on the way out.
+#include <stdlib.h>
+
 #include <mutex>
 #include <unordered_map>
 
@@ -78,6 +80,7 @@ struct FcParams {
     int m, n, k;
     int bn;  // tile width actually used: 32, 64, 128 or 256
     int tiles_m, tiles_n;
+    int band;  // n tiles per band of the tile order (see tile_coords)
     const float *bias;
     int act;
     void *c;
@@ -87,10 +90,63 @@ struct FcParams {
     int *status;
 };
 
+// Tile order.  Tiles are taken band by band: a band is `band` consecutive n tiles wide and is walked m
+// panel by m panel, n fastest inside the band.  The CTAs running at the same moment therefore share a few A
+// panels and at most `band` Wp tiles, which keeps both in L2 even when Wp as a whole does not fit.  With
+// band = tiles_n this is the plain n-fastest order (each A panel read once, Wp resident).
+__device__ __forceinline__ void tile_coords(const FcParams &p, int t, int &tm, int &tn) {
+    const int per_band = p.band * p.tiles_m;
+    const int b = t / per_band, i = t - b * per_band;
+    const int n0 = b * p.band;
+    const int gw = min(p.band, p.tiles_n - n0);
+    tm = i / gw;
+    tn = n0 + (i - tm * gw);
+}
+
 __device__ __forceinline__ float apply_act(float v, int act) {
     if (act == SWCB200_ACT_RELU) return (v > 0.f) ? v : 0.f;
     if (act == SWCB200_ACT_TANH) return 1.0f - __fdividef(2.0f, __expf(2.0f * v) + 1.0f);
     return v;
+}
+
+// bias + activation + conversion + store of 32 consecutive columns of one output row
+__device__ __forceinline__ void store_row_chunk(const FcParams &p, const uint32_t (&r)[32], int row, int col) {
+    float v[32];
+#pragma unroll
+    for (int j = 0; j < 32; j++) {
+        float x = __uint_as_float(r[j]);
+        if (p.bias != nullptr && col + j < p.n) x += __ldg(p.bias + col + j);
+        v[j] = apply_act(x, p.act);
+    }
+    if (p.c_is_bf16) {
+        __nv_bfloat16 *dst = reinterpret_cast<__nv_bfloat16 *>(p.c) + (size_t)row * p.ldc + col;
+#pragma unroll
+        for (int j = 0; j < 32; j += 8) {
+            if (p.c_vec && col + j + 8 <= p.n) {
+                uint4 o;
+                __nv_bfloat162 *h = reinterpret_cast<__nv_bfloat162 *>(&o);
+                h[0] = __floats2bfloat162_rn(v[j], v[j + 1]);
+                h[1] = __floats2bfloat162_rn(v[j + 2], v[j + 3]);
+                h[2] = __floats2bfloat162_rn(v[j + 4], v[j + 5]);
+                h[3] = __floats2bfloat162_rn(v[j + 6], v[j + 7]);
+                *reinterpret_cast<uint4 *>(dst + j) = o;
+            } else {
+                for (int e = 0; e < 8; e++)
+                    if (col + j + e < p.n) dst[j + e] = __float2bfloat16_rn(v[j + e]);
+            }
+        }
+    } else {
+        float *dst = reinterpret_cast<float *>(p.c) + (size_t)row * p.ldc + col;
+#pragma unroll
+        for (int j = 0; j < 32; j += 4) {
+            if (p.c_vec && col + j + 4 <= p.n) {
+                *reinterpret_cast<float4 *>(dst + j) = make_float4(v[j], v[j + 1], v[j + 2], v[j + 3]);
+            } else {
+                for (int e = 0; e < 4; e++)
+                    if (col + j + e < p.n) dst[j + e] = v[j + e];
+            }
+        }
+    }
 }
 
 __global__ void __launch_bounds__(kThreads, 1)
@@ -137,7 +193,8 @@ fc_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CU
             uint32_t g = 0;  // k blocks issued so far (ring position)
             bool ok = true;
             for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x) {
-                const int tm = t / p.tiles_n, tn = t - tm * p.tiles_n;
+                int tm, tn;
+                tile_coords(p, t, tm, tn);
                 for (int kb = 0; kb < kblocks; kb++, g++) {
                     const int s = g % kStages;
                     const uint32_t ph = (g / kStages) & 1;
@@ -197,7 +254,8 @@ fc_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CU
         uint32_t it = 0;
         for (int t = blockIdx.x; t < num_tiles; t += gridDim.x, it++) {
             const uint32_t buf = it & 1, aph = (it >> 1) & 1;
-            const int tm = t / p.tiles_n, tn = t - tm * p.tiles_n;
+            int tm, tn;
+            tile_coords(p, t, tm, tn);
             bool ok = mbar_wait(&tmem_full[buf], aph, p.status, kWaitTmemFull);
             ok = __all_sync(0xffffffffu, ok);
             if (!ok) break;
@@ -212,42 +270,7 @@ fc_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CU
                 tmem_ld_wait();
                 const int col = col_base + c0;
                 if (!row_ok || col >= p.n) continue;
-                float v[32];
-#pragma unroll
-                for (int j = 0; j < 32; j++) {
-                    float x = __uint_as_float(r[j]);
-                    if (p.bias != nullptr && col + j < p.n) x += __ldg(p.bias + col + j);
-                    v[j] = apply_act(x, p.act);
-                }
-                if (p.c_is_bf16) {
-                    __nv_bfloat16 *dst = reinterpret_cast<__nv_bfloat16 *>(p.c) + (size_t)row * p.ldc + col;
-#pragma unroll
-                    for (int j = 0; j < 32; j += 8) {
-                        if (p.c_vec && col + j + 8 <= p.n) {
-                            uint4 o;
-                            __nv_bfloat162 *h = reinterpret_cast<__nv_bfloat162 *>(&o);
-                            h[0] = __floats2bfloat162_rn(v[j], v[j + 1]);
-                            h[1] = __floats2bfloat162_rn(v[j + 2], v[j + 3]);
-                            h[2] = __floats2bfloat162_rn(v[j + 4], v[j + 5]);
-                            h[3] = __floats2bfloat162_rn(v[j + 6], v[j + 7]);
-                            *reinterpret_cast<uint4 *>(dst + j) = o;
-                        } else {
-                            for (int e = 0; e < 8; e++)
-                                if (col + j + e < p.n) dst[j + e] = __float2bfloat16_rn(v[j + e]);
-                        }
-                    }
-                } else {
-                    float *dst = reinterpret_cast<float *>(p.c) + (size_t)row * p.ldc + col;
-#pragma unroll
-                    for (int j = 0; j < 32; j += 4) {
-                        if (p.c_vec && col + j + 4 <= p.n) {
-                            *reinterpret_cast<float4 *>(dst + j) = make_float4(v[j], v[j + 1], v[j + 2], v[j + 3]);
-                        } else {
-                            for (int e = 0; e < 4; e++)
-                                if (col + j + e < p.n) dst[j + e] = v[j + e];
-                        }
-                    }
-                }
+                store_row_chunk(p, r, row, col);
             }
             tc_fence_before();
             mbar_arrive(&tmem_empty[buf]);
@@ -261,6 +284,178 @@ fc_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CU
         __syncwarp();
         tc_fence_after();
         tmem_dealloc(tmem_base, kTmemCols);
+    }
+}
+
+// ---------------------------------------------------------------------------------------------------
+// CTA-pair variant (cta_group::2): two CTAs of a cluster compute one 256 x BN tile.  Each CTA loads its own
+// 128 rows of A and HALF of the BN rows of Wp per k block (32 KiB instead of 48 KiB), the leader's one
+// thread issues tcgen05.mma with M = 256 that reads both CTAs' shared memory, and each CTA's tensor memory
+// receives its 128 rows of the accumulator.  Per SM that is a third less operand traffic from L2 and a
+// third less shared memory per stage, which buys a 6-deep ring: the 128 x 256 single-CTA kernel is bound
+// by how many bytes it can keep in flight, not by the tensor pipe.
+//   barriers: full[s] lives in the leader and counts the bytes of BOTH CTAs' loads; empty[s] and
+//   tmem_full[b] exist in both CTAs and are signalled together by one tcgen05.commit; tmem_empty[b] lives in
+//   the leader and collects the epilogue warps of both CTAs.
+constexpr int kStages2 = 6;
+constexpr int B2_BYTES = (BN_MAX / 2) * BK * 2;       // 16 KiB: this CTA's half of the Wp tile
+constexpr int STAGE2_BYTES = A_BYTES + B2_BYTES;      // 32 KiB
+constexpr size_t kSmemBytes2 = (size_t)kStages2 * STAGE2_BYTES + 1024 + 256;
+
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads, 1)
+fc_tc_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB, const FcParams p) {
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t *smem = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
+    uint64_t *full = reinterpret_cast<uint64_t *>(smem + (size_t)kStages2 * STAGE2_BYTES);
+    uint64_t *empty = full + kStages2;
+    uint64_t *tmem_full = empty + kStages2;
+    uint64_t *tmem_empty = tmem_full + 2;
+    uint32_t *tmem_holder = reinterpret_cast<uint32_t *>(tmem_empty + 2);
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const uint32_t rank = cluster_ctarank();
+    const bool leader = rank == 0;
+    const int num_tiles = p.tiles_m * p.tiles_n;
+    const int kblocks = (p.k + BK - 1) / BK;
+    const int cluster_id = blockIdx.x >> 1, num_clusters = gridDim.x >> 1;
+    const int half_bn = p.bn >> 1;
+
+    if (threadIdx.x == 0) {
+        tma_prefetch_desc(&tmA);
+        tma_prefetch_desc(&tmB);
+        for (int s = 0; s < kStages2; s++) {
+            mbar_init(&full[s], 1);
+            mbar_init(&empty[s], 1);
+        }
+        for (int b = 0; b < 2; b++) {
+            mbar_init(&tmem_full[b], 1);
+            mbar_init(&tmem_empty[b], 8);  // 4 epilogue warps in each of the two CTAs
+        }
+        fence_barrier_init();
+        fence_proxy_async();
+    }
+    if (warp == 1) {
+        tmem_alloc_pair(tmem_holder, kTmemCols);
+        tmem_relinquish_pair();
+    }
+    tc_fence_before();
+    __syncthreads();
+    cluster_sync();  // the peer's barriers exist before anything is signalled across the pair
+    tc_fence_after();
+    const uint32_t tmem_base = *tmem_holder;
+    bool failed = false;
+
+    if (warp == 0) {
+        // ------------------------------------------------------------ TMA producer (one per CTA)
+        if (lane == 0) {
+            const uint32_t tx_bytes = 2u * (uint32_t)(A_BYTES + half_bn * BK * 2);  // both CTAs' boxes
+            int st = 0;
+            uint32_t ph = 0;
+            for (int t = cluster_id; t < num_tiles && !failed; t += num_clusters) {
+                int tm, tn;
+                tile_coords(p, t, tm, tn);
+                const int row_a = tm * (2 * BM) + (int)rank * BM, row_b = tn * p.bn + (int)rank * half_bn;
+                for (int kb = 0; kb < kblocks; kb++) {
+                    if (!mbar_wait(&empty[st], ph ^ 1, p.status, kWaitEmpty)) {
+                        failed = true;
+                        break;
+                    }
+                    const uint32_t full_leader = map_to_cta(smem_u32(&full[st]), 0);
+                    if (leader) mbar_expect_tx(&full[st], tx_bytes);
+                    uint8_t *sa = smem + (size_t)st * STAGE2_BYTES;
+                    tma_load_2d_pair(sa, &tmA, full_leader, kb * BK, row_a);
+                    tma_load_2d_pair(sa + A_BYTES, &tmB, full_leader, kb * BK, row_b);
+                    if (++st == kStages2) {
+                        st = 0;
+                        ph ^= 1;
+                    }
+                }
+            }
+        }
+    } else if (warp == 1) {
+        // ------------------------------------------------------------ MMA issuer (leader CTA only)
+        if (leader && lane == 0) {
+            const uint32_t idesc = idesc_bf16_f32(2 * BM, p.bn);
+            const uint64_t da0 = smem_desc_sw128(smem_u32(smem)), db0 = smem_desc_sw128(smem_u32(smem + A_BYTES));
+            int st = 0;
+            uint32_t ph = 0, it = 0;
+            for (int t = cluster_id; t < num_tiles && !failed; t += num_clusters, it++) {
+                const uint32_t buf = it & 1, aph = (it >> 1) & 1;
+                if (!mbar_wait(&tmem_empty[buf], aph ^ 1, p.status, kWaitTmemEmpty)) {
+                    failed = true;
+                    break;
+                }
+                tc_fence_after();
+                const uint32_t d_tmem = tmem_base + buf * BN_MAX;
+                for (int kb = 0; kb < kblocks; kb++) {
+                    if (!mbar_wait(&full[st], ph, p.status, kWaitFull)) {
+                        failed = true;
+                        break;
+                    }
+                    tc_fence_after();
+                    const uint64_t off = (uint64_t)st * (STAGE2_BYTES >> 4);
+                    const uint64_t da = da0 + off, db = db0 + off;
+                    umma_bf16_pair(d_tmem, da, db, idesc, (uint32_t)(kb != 0));
+                    umma_bf16_pair(d_tmem, da + 2, db + 2, idesc, 1u);
+                    umma_bf16_pair(d_tmem, da + 4, db + 4, idesc, 1u);
+                    umma_bf16_pair(d_tmem, da + 6, db + 6, idesc, 1u);
+                    umma_commit_pair(&empty[st], 3);  // both CTAs' stage `st` may be refilled once these have read it
+                    if (++st == kStages2) {
+                        st = 0;
+                        ph ^= 1;
+                    }
+                }
+                if (!failed) umma_commit_pair(&tmem_full[buf], 3);
+            }
+        }
+    } else {
+        // ------------------------------------------------------------ epilogue (warps 2..5 of both CTAs)
+        const int quarter = warp & 3;
+        uint32_t it = 0;
+        for (int t = cluster_id; t < num_tiles; t += num_clusters, it++) {
+            const uint32_t buf = it & 1, aph = (it >> 1) & 1;
+            int tm, tn;
+            tile_coords(p, t, tm, tn);
+            bool ok = true;
+            if (lane == 0) ok = mbar_wait(&tmem_full[buf], aph, p.status, kWaitTmemFull);
+            ok = __shfl_sync(0xffffffffu, ok, 0);
+            if (!ok) {
+                failed = true;
+                break;
+            }
+            tc_fence_after();
+            const int row = tm * (2 * BM) + (int)rank * BM + quarter * 32 + lane;
+            const bool row_ok = row < p.m;
+            const int col_base = tn * p.bn;
+            for (int c0 = 0; c0 < p.bn; c0 += 32) {
+                uint32_t r[32];
+                __syncwarp();
+                tmem_ld_32x32(tmem_base + ((uint32_t)(quarter * 32) << 16) + buf * BN_MAX + c0, r);
+                tmem_ld_wait();
+                const int col = col_base + c0;
+                if (!row_ok || col >= p.n) continue;
+                store_row_chunk(p, r, row, col);
+            }
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive_cluster(map_to_cta(smem_u32(&tmem_empty[buf]), 0));
+        }
+    }
+
+    // A wait that gave up leaves copies possibly still in flight towards this CTA's shared memory: give them
+    // a bounded time to land before anyone tears down (the clean path needs none: every load was consumed).
+    if (failed) {
+        const long long t0 = clock64();
+        while (clock64() - t0 < 4000000ll) {
+        }
+    }
+    __syncwarp();
+    tc_fence_before();
+    __syncthreads();
+    cluster_sync();  // neither CTA leaves while the other's MMAs may read its shared memory or signal its barriers
+    if (warp == 1) {
+        tc_fence_after();
+        tmem_dealloc_pair(tmem_base, kTmemCols);
     }
 }
 
@@ -306,6 +501,16 @@ int tmap_2d(swcb200_ctx *ctx, const void *base, uint64_t rows, uint64_t cols, ui
 
 }  // namespace
 
+// SWCB200_FC_SINGLE_CTA=1 in the environment keeps every launch on the single-CTA kernel (for A/B timing).
+static bool swc_fc_force_single() {
+    static int v = -1;
+    if (v < 0) {
+        const char *e = getenv("SWCB200_FC_SINGLE_CTA");
+        v = (e && e[0] == '1') ? 1 : 0;
+    }
+    return v == 1;
+}
+
 int swc_fc_tc(swcb200_ctx *ctx, int m, int n, int k, const void *a, int lda, const void *wp, int ldw, const float *bias,
               int act, void *c, int c_dtype, int ldc) {
     SWC_REQUIRE(ctx, swc_aligned16(a) && swc_aligned16(wp), SWCB200_ERR_MISALIGNED,
@@ -323,6 +528,8 @@ int swc_fc_tc(swcb200_ctx *ctx, int m, int n, int k, const void *a, int lda, con
     p.bn = bn;
     p.tiles_m = (m + BM - 1) / BM;
     p.tiles_n = (n + bn - 1) / bn;
+    // keep the plain order while the packed weight is small enough to live in L2 next to the streams
+    p.band = ((size_t)n * k * 2 <= ((size_t)48 << 20) || p.tiles_n <= 8) ? p.tiles_n : 8;
     p.bias = bias;
     p.act = act;
     p.c = c;
@@ -330,11 +537,25 @@ int swc_fc_tc(swcb200_ctx *ctx, int m, int n, int k, const void *a, int lda, con
     p.ldc = ldc;
     p.c_vec = swc_aligned16(c) && ((size_t)ldc * celem) % 16 == 0;
     p.status = ctx->dev_status;
+    // CTA pairs whenever there is more than one 128-row panel and the tile is wide enough to halve
+    const bool pair = m > BM && bn >= 64 && ctx->sm_count >= 2 && !swc_fc_force_single();
     CUtensorMap tmA, tmB;
     int rc = tmap_2d(ctx, a, (uint64_t)m, (uint64_t)k, (uint64_t)lda, BM, &tmA);
     if (rc) return rc;
-    rc = tmap_2d(ctx, wp, (uint64_t)n, (uint64_t)k, (uint64_t)ldw, (uint32_t)bn, &tmB);
+    rc = tmap_2d(ctx, wp, (uint64_t)n, (uint64_t)k, (uint64_t)ldw, (uint32_t)(pair ? bn / 2 : bn), &tmB);
     if (rc) return rc;
+    if (pair) {
+        p.tiles_m = (m + 2 * BM - 1) / (2 * BM);
+        if (!ctx->fc_pair_attr_set) {
+            SWC_CUDA(ctx, cudaFuncSetAttribute(fc_tc_pair_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSmemBytes2));
+            ctx->fc_pair_attr_set = true;
+        }
+        const long long tiles2 = (long long)p.tiles_m * p.tiles_n;
+        const long long max_clusters = ctx->sm_count / 2;
+        unsigned grid2 = 2u * (unsigned)(tiles2 < max_clusters ? tiles2 : max_clusters);
+        fc_tc_pair_kernel<<<grid2, kThreads, kSmemBytes2, ctx->stream>>>(tmA, tmB, p);
+        return swc_check_launch(ctx, "fc_bf16");
+    }
     if (!ctx->fc_attr_set) {
         SWC_CUDA(ctx, cudaFuncSetAttribute(fc_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSmemBytes));
         ctx->fc_attr_set = true;
