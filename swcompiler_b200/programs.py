@@ -66,12 +66,34 @@ class WideMlpProgram:
         return probs_out
 
     def forward_host(self, x_host: torch.Tensor, probs_host: torch.Tensor, x_dev: torch.Tensor,
-                     probs_dev: torch.Tensor) -> torch.Tensor:
-        """End to end with HOST buffers (pinned): copy in, run, copy out, on the backend's stream."""
+                     probs_dev: torch.Tensor, chunk_rows: int = 8192) -> torch.Tensor:
+        """End to end with pinned HOST buffers.  The batch is cut into row chunks and three streams work as a
+        pipeline: chunk i+1 is copied in and chunk i-1 is copied out (both on copy engines) while the tensor
+        cores work on chunk i.  Every op is per-sample, so chunking the rows changes no result.  On return the
+        backend's stream has been made to wait for the last device->host copy."""
         rows = x_host.shape[0]
-        x_dev[:rows].copy_(x_host, non_blocking=True)
-        self.forward(x_dev[:rows], probs_dev[:rows])
-        probs_host.copy_(probs_dev[:rows], non_blocking=True)
+        main = self.be.torch_stream or torch.cuda.current_stream(self.be.device)
+        if not hasattr(self, "_io_streams"):
+            self._io_streams = (torch.cuda.Stream(self.be.device), torch.cuda.Stream(self.be.device))
+        s_in, s_out = self._io_streams
+        start = torch.cuda.Event()
+        start.record(main)
+        s_in.wait_event(start)   # buffers of an earlier call are free once the main stream got here
+        s_out.wait_event(start)
+        for r0 in range(0, rows, chunk_rows):
+            r1 = min(rows, r0 + chunk_rows)
+            with torch.cuda.stream(s_in):
+                x_dev[r0:r1].copy_(x_host[r0:r1], non_blocking=True)
+                arrived = torch.cuda.Event()
+                arrived.record(s_in)
+            main.wait_event(arrived)
+            self.forward(x_dev[r0:r1], probs_dev[r0:r1])
+            done = torch.cuda.Event()
+            done.record(main)
+            with torch.cuda.stream(s_out):
+                s_out.wait_event(done)
+                probs_host[r0:r1].copy_(probs_dev[r0:r1], non_blocking=True)
+        main.wait_stream(s_out)
         return probs_host
 
 
