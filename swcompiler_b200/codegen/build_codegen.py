@@ -1,0 +1,72 @@
+"""Builds the B200Codegen generator against a reference checkout and emits the sample programs.
+
+    python -m swcompiler_b200.codegen.build_codegen [reference_root]
+
+The reference's own build system (cmake + protobuf) is not used: its library sources under src/ (all but
+the importer, which needs protobuf, and the emitted-program utilities) are compiled in place with g++,
+together with B200Codegen.cpp and gen_driver.cpp.  Objects and the binary go to codegen/build/ (not
+tracked); the emitted programs are written to codegen/emitted/ (tracked: they are what the GPU test
+compiles and runs, since the GPU machine has no reference checkout).
+"""
+from __future__ import annotations
+
+import concurrent.futures as cf
+import glob
+import os
+import subprocess
+import sys
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+ROOT = os.path.dirname(os.path.dirname(HERE))
+BUILD = os.path.join(HERE, "build")
+EMITTED = os.path.join(HERE, "emitted")
+
+
+def reference_sources(ref: str):
+    srcs = []
+    for path in glob.glob(os.path.join(ref, "src", "**", "*.cpp"), recursive=True):
+        rel = os.path.relpath(path, os.path.join(ref, "src"))
+        if rel.startswith("importer") or rel.startswith(os.path.join("codegen", "utils")):
+            continue
+        srcs.append(path)
+    return sorted(srcs)
+
+
+def build(ref: str = "/root/reference", quiet: bool = True) -> str:
+    if not os.path.exists(os.path.join(ref, "include", "SWC.h")):
+        raise FileNotFoundError(f"no reference checkout at {ref}")
+    os.makedirs(BUILD, exist_ok=True)
+    os.makedirs(EMITTED, exist_ok=True)
+    flags = ["-std=c++11", "-O1", "-w", "-I" + os.path.join(ref, "src"), "-I" + os.path.join(ref, "include"), "-I" + HERE]
+    jobs, objs = [], []
+    for s in reference_sources(ref) + [os.path.join(HERE, "B200Codegen.cpp"), os.path.join(HERE, "gen_driver.cpp")]:
+        o = os.path.join(BUILD, os.path.relpath(s, "/").replace(os.sep, "_")[:-4] + ".o")
+        objs.append(o)
+        if not os.path.exists(o) or os.path.getmtime(o) < max(os.path.getmtime(s), os.path.getmtime(os.path.join(HERE, "B200Codegen.h"))):
+            jobs.append(["g++", *flags, "-c", s, "-o", o])
+
+    def run(cmd):
+        r = subprocess.run(cmd, capture_output=True, text=True)
+        if r.returncode:
+            raise RuntimeError(" ".join(cmd) + "\n" + r.stdout + r.stderr)
+
+    with cf.ThreadPoolExecutor(max_workers=8) as ex:
+        list(ex.map(run, jobs))
+    exe = os.path.join(BUILD, "gen_driver")
+    run(["g++", "-o", exe, *objs])
+    return exe
+
+
+def emit(exe: str, out_dir: str = EMITTED):
+    os.makedirs(out_dir, exist_ok=True)
+    for which in ("mlp8", "convnet"):
+        # the generator also drops Graph.cpp / G_Makefile / SW_Makefile and *.dot in its working directory
+        r = subprocess.run([exe, which, out_dir, "$(abspath ../../..)"], cwd=BUILD, capture_output=True, text=True)
+        if r.returncode:
+            raise RuntimeError(r.stdout[-2000:] + r.stderr[-2000:])
+    return out_dir
+
+
+if __name__ == "__main__":
+    exe = build(sys.argv[1] if len(sys.argv) > 1 else "/root/reference", quiet=False)
+    print(emit(exe))
