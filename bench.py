@@ -288,7 +288,7 @@ def run_ours(args, rank, world, local_rank):
             "ms_per_step": ms / args.steps, "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
             "dtype": "bf16 (fp32 accumulate)", "data": "synthetic", "config": config(world, rows),
             "roofline": {"bound": "tensor", "achieved": achieved, "peak": peak, "unit": "TFLOP/s", "frac": achieved / peak,
-                         "traffic": None, "kernel": "fc_tc_pair_kernel (FC 4096->4096 + bias + ReLU, one launch)",
+                         "traffic": 32e6 + 127.6e6 * rows / 8192, "traffic_source": "ncu dram bytes of the 8192-row launch (159.6 MB), row-proportional part scaled; profiles/fc_tc_pair_kernel__config3_layer.md", "kernel": "fc_tc_pair_kernel (FC 4096->4096 + bias + ReLU, one launch)",
                          "launch_ms": fc_avg_ms, "flops_per_launch": flops_per_launch, "peak_source": peak_src},
             "per_launch_ms": per_kernel_ms,
             "cpu_baseline": cpu, "e2e": e2e,
