@@ -34,7 +34,7 @@ METRIC, UNIT = "inference samples/sec", "samples/s"
 def config(n_gpus, rows_per_rank):
     return {"workload": "wide MLP forward (BASELINE configs[2]): X[65536,4096] bf16 -> 4x(FC 4096->4096 + bias + ReLU) "
                         "-> FC 4096->1000 + bias -> softmax",
-            "global_batch": BATCH, "rows_per_gpu": rows_per_rank, "parallelism": f"dp{n_gpus} (batch split; Gather to rank 0 over NCCL, overlapped with the next step)",
+            "global_batch": BATCH, "rows_per_gpu": rows_per_rank, "parallelism": f"dp{n_gpus} (batch split; Gather to rank 0 by peer copies over NVLink, overlapped with the next step)",
             "l2": "inputs larger than L2 (X 512 MiB, activations 512 MiB per layer); no flush needed"}
 
 
@@ -198,6 +198,11 @@ def run_ours(args, rank, world, local_rank):
         comm = par.NcclComm(swc.Backend(local_rank, swc.TC_BF16, stream=comm_stream), rank, world, exchange)
         if rank == 0:
             gathered = torch.empty((BATCH, CLASSES), dtype=torch.float32, device=device)
+        # The Gather: peer copies on the copy engines (swcb200_gather_rows), so that it takes no SM from the
+        # persistent GEMMs of the next step; SWCB200_BENCH_GATHER=nccl selects the send/recv path instead.
+        use_rows = os.environ.get("SWCB200_BENCH_GATHER", "rows") != "nccl"
+        if use_rows:
+            comm.gather_rows_setup(gathered, rows * CLASSES * 4, root=0)
     main_stream = torch.cuda.current_stream(device)
     gather_done = [None, None]
     counter = [0]
@@ -213,9 +218,12 @@ def run_ours(args, rank, world, local_rank):
             ready = torch.cuda.Event()
             ready.record(main_stream)
             comm.be.torch_stream.wait_event(ready)
-            dst = C.c_void_p(gathered.data_ptr()) if rank == 0 else C.c_void_p(0)
-            comm.be._call("gather", C.c_void_p(out.data_ptr()), dst, (C.c_size_t * 2)(BATCH, CLASSES), C.c_int(2),
-                          C.c_int(0), C.c_int(swc.F32), C.c_int(0))
+            if use_rows:
+                comm.gather_rows(out)
+            else:
+                dst = C.c_void_p(gathered.data_ptr()) if rank == 0 else C.c_void_p(0)
+                comm.be._call("gather", C.c_void_p(out.data_ptr()), dst, (C.c_size_t * 2)(BATCH, CLASSES), C.c_int(2),
+                              C.c_int(0), C.c_int(swc.F32), C.c_int(0))
             done = torch.cuda.Event()
             done.record(comm.be.torch_stream)
             gather_done[s % 2] = done
@@ -247,7 +255,7 @@ def run_ours(args, rank, world, local_rank):
         drain()
         e1.record()
         barrier()
-    launches = be.launches - launches0 + (args.steps if world > 1 else 0)  # + one NCCL gather per step
+    launches = be.launches - launches0 # the Gather is a copy-engine transfer, not a launch
     be.sync()  # also surfaces a device-side timeout status, if any
     ms = e0.elapsed_time(e1)
     if world > 1:

@@ -215,6 +215,16 @@ int swcb200_scatter(swcb200_ctx *ctx, const void *src, void *dst, const size_t *
 /* Gather node (:576-682): inverse of scatter; `dst` is written on root only. */
 int swcb200_gather(swcb200_ctx *ctx, const void *src, void *dst, const size_t *dims, int ndim,
                    int axis, int dtype, int root);
+/* Gather along axis 0 without kernels: root exports `dst_on_root` once (CUDA IPC, exchanged through the
+ * communicator), the other ranks map it, and each swcb200_gather_rows is one device-to-device copy of this
+ * rank's `bytes_per_rank` block into its place in root's buffer, done by a copy engine over NVLink on the
+ * context's stream.  No SM is used, so a persistent GEMM running beside it is not disturbed (an NCCL
+ * send/recv kernel is).  Same result as swcb200_gather(axis 0).  The data is in root's buffer once the
+ * SENDER's stream has passed the call: ranks must meet (stream sync, then a host barrier) before root reads
+ * it or before the buffer is written again.  setup/release are collective; dst must come from cudaMalloc. */
+int swcb200_gather_rows_setup(swcb200_ctx *ctx, void *dst_on_root, size_t bytes_per_rank, int root);
+int swcb200_gather_rows(swcb200_ctx *ctx, const void *src);
+int swcb200_gather_rows_release(swcb200_ctx *ctx);
 /* Reduce node (:873-896): dst(root) = sum over ranks of src. */
 int swcb200_reduce_sum(swcb200_ctx *ctx, const void *src, void *dst, size_t count, int dtype,
                        int root);

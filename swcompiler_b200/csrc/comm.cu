@@ -12,6 +12,7 @@
 // [r*inner/p, (r+1)*inner/p), and stores its shard packed ([outer, inner/p], leading dimension
 // inner/p).  axis 0 shards are contiguous in the full tensor; other axes are strided and go through a
 // staging block (the context's scratch) packed and unpacked with strided device copies.
+#include <cuda.h>
 #include <dlfcn.h>
 
 #include <mutex>
@@ -86,6 +87,11 @@ int load_nccl(const char *path) {
 struct swcb200_comm {
     ncclComm_t comm = nullptr;
     int rank = 0, nranks = 1;
+    // peer-copy gather (swcb200_gather_rows_*): root's destination as this rank can address it
+    void *rows_dst = nullptr;      // on root: the caller's buffer; elsewhere: the IPC mapping + offset
+    void *rows_ipc_base = nullptr; // what cudaIpcOpenMemHandle returned (non-root), to close later
+    size_t rows_bytes = 0;
+    int rows_root = -1;
 };
 
 namespace {
@@ -182,6 +188,7 @@ SWC_EXPORT int swcb200_comm_init(swcb200_ctx *ctx, const void *unique_id, int nr
 SWC_EXPORT int swcb200_comm_destroy(swcb200_ctx *ctx) {
     if (!ctx) return SWCB200_ERR_BAD_ARG;
     if (!ctx->comm) return SWCB200_OK;
+    swcb200_gather_rows_release(ctx);
     cudaSetDevice(ctx->device);
     cudaStreamSynchronize(ctx->stream);
     int r = g_nccl.CommDestroy(ctx->comm->comm);
@@ -285,6 +292,93 @@ SWC_EXPORT int swcb200_gather(swcb200_ctx *ctx, const void *src, void *dst, cons
                 if (rc) return rc;
             }
     }
+    return SWCB200_OK;
+}
+
+// ---- Gather along axis 0 by peer-to-peer copies.
+// ncclSend/ncclRecv run as kernels and take SMs for the length of the transfer; a persistent GEMM that
+// wants every SM then waits for them.  A Gather of contiguous row blocks needs no kernel at all: root
+// exports its destination buffer once (CUDA IPC), every other rank maps it, and each Gather is one
+// cudaMemcpyAsync on the sender's stream, carried out by a copy engine over NVLink.
+namespace {
+typedef CUresult (*GetRangeFn)(CUdeviceptr *, size_t *, CUdeviceptr);
+GetRangeFn get_range_fn() {
+    static GetRangeFn fn = nullptr;
+    static std::once_flag once;
+    std::call_once(once, [] {
+        void *p = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        if (cudaGetDriverEntryPoint("cuMemGetAddressRange", &p, cudaEnableDefault, &q) == cudaSuccess &&
+            q == cudaDriverEntryPointSuccess)
+            fn = (GetRangeFn)p;
+    });
+    return fn;
+}
+struct RowsExport {
+    cudaIpcMemHandle_t handle;
+    unsigned long long offset;
+};
+}  // namespace
+
+SWC_EXPORT int swcb200_gather_rows_setup(swcb200_ctx *ctx, void *dst_on_root, size_t bytes_per_rank, int root) {
+    SWC_CTX(ctx);
+    SWC_REQUIRE(ctx, ctx->comm != nullptr, SWCB200_ERR_NCCL, "gather_rows_setup: no communicator");
+    swcb200_comm *c = ctx->comm;
+    SWC_REQUIRE(ctx, root >= 0 && root < c->nranks && bytes_per_rank > 0, SWCB200_ERR_BAD_ARG, "gather_rows_setup: bad argument");
+    SWC_REQUIRE(ctx, c->rank != root || dst_on_root != nullptr, SWCB200_ERR_BAD_ARG, "gather_rows_setup: root needs a destination");
+    SWC_REQUIRE(ctx, c->rows_root < 0, SWCB200_ERR_BAD_ARG, "gather_rows_setup: already set up (release first)");
+    RowsExport ex;
+    memset(&ex, 0, sizeof(ex));
+    if (c->rank == root) {
+        GetRangeFn range = get_range_fn();
+        SWC_REQUIRE(ctx, range != nullptr, SWCB200_ERR_CUDA, "gather_rows_setup: cuMemGetAddressRange not found");
+        CUdeviceptr base = 0;
+        size_t size = 0;
+        SWC_REQUIRE(ctx, range(&base, &size, (CUdeviceptr)dst_on_root) == CUDA_SUCCESS, SWCB200_ERR_CUDA,
+                    "gather_rows_setup: destination is not a device allocation");
+        SWC_CUDA(ctx, cudaIpcGetMemHandle(&ex.handle, (void *)base));
+        ex.offset = (unsigned long long)((CUdeviceptr)dst_on_root - base);
+    }
+    // hand the export to every rank through the communicator (a small device-side broadcast)
+    void *dev = nullptr;
+    int rc = swc_scratch(ctx, sizeof(ex), &dev);
+    if (rc) return rc;
+    SWC_CUDA(ctx, cudaMemcpyAsync(dev, &ex, sizeof(ex), cudaMemcpyHostToDevice, ctx->stream));
+    SWC_NCCL(ctx, g_nccl.Broadcast(dev, dev, sizeof(ex), /*ncclInt8*/ 0, root, c->comm, ctx->stream));
+    SWC_CUDA(ctx, cudaMemcpyAsync(&ex, dev, sizeof(ex), cudaMemcpyDeviceToHost, ctx->stream));
+    SWC_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
+    if (c->rank == root) {
+        c->rows_dst = dst_on_root;
+    } else {
+        void *mapped = nullptr;
+        SWC_CUDA(ctx, cudaIpcOpenMemHandle(&mapped, ex.handle, cudaIpcMemLazyEnablePeerAccess));
+        c->rows_ipc_base = mapped;
+        c->rows_dst = (uint8_t *)mapped + ex.offset;
+    }
+    c->rows_bytes = bytes_per_rank;
+    c->rows_root = root;
+    return SWCB200_OK;
+}
+
+SWC_EXPORT int swcb200_gather_rows(swcb200_ctx *ctx, const void *src) {
+    SWC_CTX(ctx);
+    SWC_REQUIRE(ctx, ctx->comm != nullptr && ctx->comm->rows_root >= 0, SWCB200_ERR_BAD_ARG,
+                "gather_rows: call swcb200_gather_rows_setup first");
+    SWC_REQUIRE(ctx, src != nullptr, SWCB200_ERR_BAD_ARG, "gather_rows: null source");
+    swcb200_comm *c = ctx->comm;
+    SWC_CUDA(ctx, cudaMemcpyAsync((uint8_t *)c->rows_dst + (size_t)c->rank * c->rows_bytes, src, c->rows_bytes,
+                                  cudaMemcpyDeviceToDevice, ctx->stream));
+    return SWCB200_OK;
+}
+
+SWC_EXPORT int swcb200_gather_rows_release(swcb200_ctx *ctx) {
+    if (!ctx) return SWCB200_ERR_BAD_ARG;
+    if (!ctx->comm || ctx->comm->rows_root < 0) return SWCB200_OK;
+    cudaSetDevice(ctx->device);
+    cudaStreamSynchronize(ctx->stream);
+    if (ctx->comm->rows_ipc_base) cudaIpcCloseMemHandle(ctx->comm->rows_ipc_base);
+    ctx->comm->rows_ipc_base = ctx->comm->rows_dst = nullptr;
+    ctx->comm->rows_root = -1;
     return SWCB200_OK;
 }
 

@@ -197,6 +197,20 @@ class NcclComm:
                       C.c_int(_DT[local.dtype]), C.c_int(root))
         return out
 
+    def gather_rows_setup(self, dst_on_root, bytes_per_rank: int, root=0):
+        """Collective.  Prepares the kernel-free Gather along axis 0: root passes its destination tensor (from
+        the ordinary CUDA allocator), the others None."""
+        dst = C.c_void_p(dst_on_root.data_ptr()) if dst_on_root is not None else C.c_void_p(0)
+        self.be._call("gather_rows_setup", dst, C.c_size_t(bytes_per_rank), C.c_int(root))
+
+    def gather_rows(self, local):
+        """One copy-engine transfer of this rank's block into root's buffer, on the backend's stream.  Root may
+        read the result after every rank has synchronised its stream and the ranks have met at a barrier."""
+        self.be._call("gather_rows", C.c_void_p(local.data_ptr()))
+
+    def gather_rows_release(self):
+        self.be._call("gather_rows_release")
+
     def reduce_sum(self, local, root=0):
         out = torch.empty_like(local) if self.rank == root else None
         dst = C.c_void_p(out.data_ptr()) if out is not None else C.c_void_p(0)

@@ -54,6 +54,20 @@ def _collectives(rank, world):
     ag = comm.allgather(par.take_shard(m, 0, rank, world))
     be.sync()
     assert (rank != 0 or torch.equal(r, total)) and torch.equal(a, total) and torch.equal(ag, m)
+    # kernel-free Gather along axis 0 (peer copies into root's buffer)
+    import torch.distributed as dist
+    rows = torch.full((3, 5), float(rank + 1), device=dev)
+    dst = torch.zeros((3 * world, 5), device=dev) if rank == 0 else None
+    comm.gather_rows_setup(dst, rows.numel() * 4, root=0)
+    for _ in range(2):
+        comm.gather_rows(rows)
+    be.sync()
+    dist.barrier()
+    if rank == 0:
+        want = torch.cat([torch.full((3, 5), float(r + 1), device=dev) for r in range(world)])
+        assert torch.equal(dst, want)
+    dist.barrier()
+    comm.gather_rows_release()
     # bf16 and int32 payloads
     b = torch.randn((16, 64), generator=g, device=dev).to(torch.bfloat16)
     lb = comm.scatter(b if rank == 0 else None, b.shape, 1, dtype=torch.bfloat16)
