@@ -307,6 +307,105 @@ def run_ours(args, rank, world, local_rank):
         dist.destroy_process_group()
 
 
+def run_fcpair(args, rank, world, local_rank):
+    """Model-parallel FC pair (BASELINE configs[3]): X[8192,8192] bf16 replicated; FC1 8192->32768 split by output
+    columns -> ReLU; FC2 32768->8192 split by input rows; fp32 partial sums joined by an NCCL all-reduce.  One step =
+    one forward pass over the 8192 rows; the rows go through in `--chunks` chunks so that the all-reduce of one chunk
+    (communication stream) overlaps the tensor-core work of the next."""
+    import torch
+    import torch.distributed as dist
+
+    import swcompiler_b200 as swc
+    from swcompiler_b200 import parallel as par
+    from swcompiler_b200.programs import FcPairProgram
+
+    M, K, N1, N2 = args.fcpair_rows, 8192, 32768, 8192
+    torch.cuda.set_device(local_rank)
+    device = torch.device("cuda", local_rank)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=device)
+    be = swc.Backend(local_rank, swc.TC_BF16)
+
+    def exchange(uid):
+        box = [uid]
+        if world > 1:
+            dist.broadcast_object_list(box, src=0)
+        return box[0]
+
+    comm = par.NcclComm(swc.Backend(local_rank, swc.TC_BF16, stream=torch.cuda.Stream(device)), rank, world, exchange)
+    g = torch.Generator(device=device).manual_seed(1004)
+    x = torch.randn((M, K), generator=g, device=device).to(torch.bfloat16)
+    # the rank's shards are drawn directly (same law as the full matrices; the full 512 MiB + 512 MiB fp32 weights
+    # are never materialised): W1[:, cols of this rank] ~ N(0, 1/K), W2[rows of this rank, :] ~ N(0, 1/N1)
+    gs = torch.Generator(device=device).manual_seed(1004 * 100 + rank)
+    n1s = N1 // world
+
+    w1s = (torch.randn((K, n1s), generator=gs, device=device) / K ** 0.5)
+    w2s = (torch.randn((n1s, N2), generator=gs, device=device) / N1 ** 0.5)
+    prog = FcPairProgram(be, comm, w1s, w2s, max_rows=M, sharded=True)
+    del w1s, w2s
+    chunks = args.chunks
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    for _ in range(max(args.warmup, 3)):
+        prog.forward(x, chunks=chunks)
+    barrier()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    launches0 = be.launches
+    with ClockSampler(local_rank) as clocks:
+        barrier()
+        e0.record()
+        for _ in range(args.steps):
+            prog.forward(x, chunks=chunks)
+        e1.record()
+        barrier()
+    be.sync()
+    comm.be.sync()
+    ms = e0.elapsed_time(e1)
+    # the two GEMMs alone (no all-reduce), for the roofline of the dominant kernel
+    g0, g1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    import swcompiler_b200._lib as L
+    g0.record()
+    for _ in range(args.steps):
+        be.fc_bf16(x, prog.wp1, None, L.ACT_RELU, out=prog.h)
+    g1.record()
+    torch.cuda.synchronize()
+    fc1_ms = g0.elapsed_time(g1) / args.steps
+    if world > 1:
+        t = torch.tensor([ms, fc1_ms], device=device)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms, fc1_ms = float(t[0].item()), float(t[1].item())
+    launches = be.launches - launches0 - args.steps
+    flops_fc1 = 2.0 * M * n1s * K
+    peak, peak_src = peaks()
+    if rank == 0:
+        step_ms = ms / args.steps
+        total_flops = 2.0 * M * N1 * (K + N2)
+        print(json.dumps({
+            "metric": METRIC, "value": M / (step_ms * 1e-3), "unit": UNIT, "n_gpus": world, "steps": args.steps,
+            "warmup": max(args.warmup, 3), "ms_per_step": step_ms, "higher_is_better": True, "scaling": "strong",
+            "vs_baseline": None, "dtype": "bf16 (fp32 accumulate, fp32 all-reduce)", "data": "synthetic",
+            "config": {"workload": "model-parallel FC pair (BASELINE configs[3]): X[8192,8192] bf16 -> FC 8192->32768 "
+                                   "(column split) -> ReLU -> FC 32768->8192 (row split) -> all-reduce(sum)",
+                       "global_batch": M, "parallelism": f"mp{world}", "chunks": chunks,
+                       "l2": "weights (1 GiB / p per rank) larger than L2; no flush needed"},
+            "job_tflops": total_flops / (step_ms * 1e-3) / 1e12,
+            "roofline": {"bound": "tensor", "achieved": flops_fc1 / (fc1_ms * 1e-3) / 1e12, "peak": peak, "unit": "TFLOP/s",
+                         "frac": flops_fc1 / (fc1_ms * 1e-3) / 1e12 / peak, "traffic": None,
+                         "kernel": "fc_tc_pair_kernel (FC1 shard 8192 x 32768/p x 8192 + ReLU, one launch, timed alone)",
+                         "launch_ms": fc1_ms, "flops_per_launch": flops_fc1, "peak_source": peak_src},
+            "allreduce_bytes_per_rank": M * N2 * 4, "cpu_baseline": None, "e2e": None,
+            "gpu_launches": launches, "clocks": clocks.summary()}))
+    barrier()
+    comm.close()
+    if world > 1:
+        dist.destroy_process_group()
+
+
 def run_e2e(torch, dist, prog, x, probs, world, device, rows, e2e_steps, barrier):
     """End to end with host buffers (rank-local slice): H2D of X, forward, D2H of the probabilities."""
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
@@ -341,6 +440,10 @@ def main():
     ap.add_argument("--batch", type=int, default=BATCH, help="rows in the whole job (smaller only for profiler captures)")
     ap.add_argument("--skip-cpu-baseline", action="store_true", help="leave the CPU sample out (profiler captures)")
     ap.add_argument("--skip-e2e", action="store_true", help="leave the host-buffer pass out (profiler captures)")
+    ap.add_argument("--workload", default="widemlp", choices=["widemlp", "fcpair"],
+                    help="widemlp: the data-parallel wide MLP (default, the headline); fcpair: the model-parallel FC pair")
+    ap.add_argument("--chunks", type=int, default=4, help="fcpair: row chunks per forward (all-reduce overlap)")
+    ap.add_argument("--fcpair-rows", type=int, default=8192, help="fcpair: rows of X")
     args = ap.parse_args()
     BATCH = args.batch
     rank = int(os.environ.get("RANK", "0"))
@@ -348,6 +451,8 @@ def main():
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))
     if args.impl == "reference":
         run_reference(args, rank, world)
+    elif args.workload == "fcpair":
+        run_fcpair(args, rank, world, local_rank)
     else:
         run_ours(args, rank, world, local_rank)
 

@@ -5,42 +5,64 @@
 //   out[n, oh, ow, :] = epi( sum over taps (kx, ky) and channels of  in[n, oh+kx-pt, ow+ky-pl, :] . filt[:, kx, ky, :] )
 //
 // GEMM view: M = output pixels, N = oC, K = kh*kw*iC, bf16 operands, fp32 accumulation in tensor memory.
-//   * A tile of 128 output pixels is two 8x8 pixel blocks (so 56x56 images tile with no waste, and a tile
-//     may straddle images).  For one filter tap its A operand is the same two blocks shifted by the tap:
-//     two 4-D TMA boxes {64 ch, 8, 8, 1} of the input; pixels outside the image (the padding) arrive as
-//     zeros from TMA's out-of-bounds fill, so there is no im2col buffer and no halo logic.  A pixel's 64
-//     channels are exactly one 128-byte swizzle row, which makes the box a K-major UMMA operand as is.
-//   * The whole filter stays resident in shared memory for the life of the (persistent) CTA:
-//     kh*kw*(iC/64) slices of [oC x 64] loaded once by TMA.
-//   * Shared-memory barrier operations cost on the order of 100 cycles each on this part, and one MMA of
-//     this shape (N = oC = 64) lasts well under that, so the pipeline hands over a whole filter ROW at a
-//     time: a stage holds the A operands of the kw taps of one filter row (kw * iC/64 slots of 16 KiB),
-//     filled by two producer warps (warp 0: the first 8x8 block of every slot, warp 6: the second), one
-//     barrier wait and one expect-tx per producer per row.  Warp 1 waits once per row, issues all of its
-//     tcgen05.mma (4 per slot, M128 x N=oC x K16) back to back and releases the row with one commit.
-//     Warps 2-5 run the epilogue out of up to four tensor-memory accumulators while the next tiles compute.
-//   Restrictions: stride 1, group 1, iC a multiple of 64, oC a multiple of 32 and <= 256, filter at most
-//   96 KiB in bf16.  Other shapes return SWCB200_ERR_UNSUPPORTED (the strict kernel takes them).
+// A pixel's 64 channels are exactly one 128-byte swizzle row, so a TMA box of pixels is a K-major UMMA
+// operand as it lands; pixels outside the image (the padding) arrive as zeros from TMA's out-of-bounds
+// fill, so there is no im2col buffer.  The whole filter stays resident in shared memory for the life of
+// the (persistent) CTA: kh*kw*(iC/64) slices of [oC x 64] loaded once by TMA.
+//
+// What bounds this kernel.  With N = oC = 64 one tcgen05.mma (128 x 64 x 16) is 32 cycles of math but
+// reads 6 KiB of operands from shared memory, 48 cycles of the SM's 128 B/clk L1/shared data pipe -- and
+// that pipe also carries TMA's writes, the epilogue's shared-memory traffic and every global load/store
+// wavefront (one per 128-byte line touched).  The design therefore minimises data-pipe wavefronts:
+//   * Halo window.  A tile is 2 output rows x 64 columns (kw-1 of the columns are scrap); its input window,
+//     (kh+1) rows x 64 pixels, is loaded ONCE by one 4-D TMA box per 64-channel chunk, dense in shared
+//     memory at 128 bytes per pixel.  The A operand of tap (kx, ky) is the same buffer read from a start
+//     address (kx*64 + ky) pixels further on: the 128-byte swizzle is a function of the absolute
+//     shared-memory address for TMA and for the MMA alike, so a descriptor whose start is shifted by whole
+//     128-byte rows reads rows r+shift of the buffer (checked on the hardware with an identity-matrix
+//     product for shifts 0..17).  Columns whose window runs into the next row compute scrap that is not
+//     stored.  Per tile 32 KiB of TMA writes instead of one 16 KiB operand per tap, and one barrier
+//     hand-over per tile.
+//   * Staged epilogue (bf16 output, oC a multiple of 64).  An epilogue thread owns one pixel, and pixels
+//     are 128 bytes apart in global memory, so direct 16-byte stores touch 32 lines per instruction.
+//     Instead the tile is written to shared memory in the swizzled layout of a TMA box {64 ch, cw, 2, 1}
+//     (4 wavefronts per instruction) and leaves with one TMA store per 64 channels; TMA clips rows and
+//     columns outside the image.  A bf16 residual arrives the same way, by a TMA load issued by the producer.
+//     Other outputs (fp32, oC not a multiple of 64) are stored directly.
+//   * Per-channel epilogue coefficients are read from shared memory as 128-bit broadcasts.
+// Warp roles: warp 0 TMA producer, warp 1 MMA issuer, warps 2-9 epilogue (two warps per tensor-memory
+// lane quarter, 32 channels each per pass).  The producer and issuer loops run warp-uniform with one
+// elected lane executing the asynchronous instructions: a loop run by a lone lane under a divergent
+// branch issues tcgen05.mma at 75 cycles apiece on this part, the uniform form at the 48 cycles the
+// shared-memory reads allow.
+//
+// Restrictions: stride 1, group 1, iC a multiple of 64, oC a multiple of 32 and <= 256, kw <= 9, filter at
+// most 96 KiB in bf16, two windows fitting beside it.  Other shapes return SWCB200_ERR_UNSUPPORTED (the
+// strict kernel takes them).
 #include "tc_common.cuh"
 
 namespace {
 
 using namespace tc;
 
-constexpr int BM = 128, BK = 64, UMMA_K = 16;
-constexpr int BLOCK_PIX = 64;            // 8 x 8 pixels
-constexpr int A_STAGE_BYTES = BM * 128;  // 16 KiB
-constexpr int kThreads = 224;  // producer A, MMA issuer, 4 epilogue warps, producer B
+constexpr int BM = 128, BK = 64;
+constexpr int ROW_PIX = 64;              // pixels per window row in shared memory (8 KiB)
+constexpr int OUT_CHUNK_BYTES = 16384;   // staging slot of one 64-channel chunk of a tile (2 x cw pixels x 128 B, rounded up)
+constexpr int kThreads = 320;            // TMA producer, MMA issuer, 8 epilogue warps
+constexpr int kEpilogueThreads = 256;
 constexpr int kMaxFilterBytes = 96 * 1024;
 constexpr int kMaxSmem = 227 * 1024;
 
 struct ConvParams {
     int N, H, W, C, OH, OW, OC, kh, kw, pt, pl;
     int kchunks;            // C / 64
-    int blocks_h, blocks_w; // 8x8 blocks per image
-    long long num_blocks, num_tiles;
-    int stages, slots, acc_stride, num_acc, tmem_cols;  // stages = row stages in the ring, slots = 16 KiB slots per row
+    long long num_tiles;
+    int stages, acc_stride, num_acc, tmem_cols;
     int filter_bytes;
+    // tile = 2 output rows x 64 columns of which `cw` are stored; window = `hr` input rows x 64 pixels
+    int hr, cw, col_blocks, row_blocks, chunk_bytes, stage_bytes;
+    int out_tma, res_tma;   // staged epilogue / residual brought in by TMA
+    int out_tile_bytes;     // (OC / 64) * OUT_CHUNK_BYTES
     const float *bias;
     const float *bn_scale, *bn_bias, *bn_mean, *bn_var;
     float bn_eps;
@@ -51,35 +73,115 @@ struct ConvParams {
     int *status;
 };
 
+#ifdef SWC_CONV_TIMING
+__device__ long long g_conv_timing[16];
+#define TIMING(x) x
+#else
+#define TIMING(x)
+#endif
+
+// v[j] = acc[j] * alpha[c0+j] + beta[c0+j], coefficients read as 128-bit broadcasts
+__device__ __forceinline__ void apply_affine(const uint32_t (&acc)[32], const float *s_alpha, const float *s_beta, int c0,
+                                             float (&v)[32]) {
+    const float4 *a4 = reinterpret_cast<const float4 *>(s_alpha + c0), *b4 = reinterpret_cast<const float4 *>(s_beta + c0);
+#pragma unroll
+    for (int j = 0; j < 8; j++) {
+        const float4 a = a4[j], b = b4[j];
+        v[4 * j] = fmaf(__uint_as_float(acc[4 * j]), a.x, b.x);
+        v[4 * j + 1] = fmaf(__uint_as_float(acc[4 * j + 1]), a.y, b.y);
+        v[4 * j + 2] = fmaf(__uint_as_float(acc[4 * j + 2]), a.z, b.z);
+        v[4 * j + 3] = fmaf(__uint_as_float(acc[4 * j + 3]), a.w, b.w);
+    }
+}
+__device__ __forceinline__ void add_bf16x8(float *v, const uint4 q) {
+    const uint32_t w[4] = {q.x, q.y, q.z, q.w};
+#pragma unroll
+    for (int e = 0; e < 4; e++) {
+        v[2 * e] += __uint_as_float(w[e] << 16);
+        v[2 * e + 1] += __uint_as_float(w[e] & 0xffff0000u);
+    }
+}
+__device__ __forceinline__ uint4 pack_bf16x8(const float *v) {
+    uint4 o;
+    __nv_bfloat162 *h2 = reinterpret_cast<__nv_bfloat162 *>(&o);
+    h2[0] = __floats2bfloat162_rn(v[0], v[1]);
+    h2[1] = __floats2bfloat162_rn(v[2], v[3]);
+    h2[2] = __floats2bfloat162_rn(v[4], v[5]);
+    h2[3] = __floats2bfloat162_rn(v[6], v[7]);
+    return o;
+}
+// residual of channels [c0, c0+32) of pixel `pix`, read from global memory
+__device__ __forceinline__ void add_residual_global(const ConvParams &p, float (&v)[32], size_t pix, int c0) {
+    if (p.res_is_f32) {
+        const float4 *rp = reinterpret_cast<const float4 *>(reinterpret_cast<const float *>(p.residual) + pix * p.OC + c0);
+#pragma unroll
+        for (int j = 0; j < 8; j++) {
+            const float4 q = __ldg(rp + j);
+            v[4 * j] += q.x;
+            v[4 * j + 1] += q.y;
+            v[4 * j + 2] += q.z;
+            v[4 * j + 3] += q.w;
+        }
+    } else {
+        const uint4 *rp = reinterpret_cast<const uint4 *>(reinterpret_cast<const __nv_bfloat16 *>(p.residual) + pix * p.OC + c0);
+#pragma unroll
+        for (int j = 0; j < 4; j++) add_bf16x8(v + 8 * j, __ldg(rp + j));
+    }
+}
+__device__ __forceinline__ void store_global(const ConvParams &p, const float (&v)[32], size_t pix, int c0) {
+    if (p.out_is_f32) {
+        float4 *op = reinterpret_cast<float4 *>(reinterpret_cast<float *>(p.out) + pix * p.OC + c0);
+#pragma unroll
+        for (int j = 0; j < 8; j++) op[j] = make_float4(v[4 * j], v[4 * j + 1], v[4 * j + 2], v[4 * j + 3]);
+    } else {
+        uint4 *op = reinterpret_cast<uint4 *>(reinterpret_cast<__nv_bfloat16 *>(p.out) + pix * p.OC + c0);
+#pragma unroll
+        for (int j = 0; j < 4; j++) op[j] = pack_bf16x8(v + 8 * j);
+    }
+}
+
 __global__ void __launch_bounds__(kThreads, 1)
-conv_tc_kernel(const __grid_constant__ CUtensorMap tmIn, const __grid_constant__ CUtensorMap tmF, const ConvParams p) {
+conv_tc_kernel(const __grid_constant__ CUtensorMap tmIn, const __grid_constant__ CUtensorMap tmF,
+               const __grid_constant__ CUtensorMap tmOut, const __grid_constant__ CUtensorMap tmRes, const ConvParams p) {
     extern __shared__ uint8_t smem_raw[];
     uint8_t *smem = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
     uint8_t *s_filter = smem;                                   // [taps*kchunks][OC x 128 B]
-    uint8_t *s_a = smem + p.filter_bytes;                       // stages x slots x 16 KiB
-    const int row_bytes = p.slots * A_STAGE_BYTES;
-    float *s_alpha = reinterpret_cast<float *>(s_a + (size_t)p.stages * row_bytes);  // [OC]
+    uint8_t *s_a = smem + p.filter_bytes;                       // stages x kchunks x (hr x 64 pixels x 128 B)
+    // 1 KiB of slack after the last window: the scrap columns of the last tap read kw-1 pixels past it
+    uint8_t *s_out = s_a + (size_t)p.stages * p.stage_bytes + 1024;             // 2 x out_tile_bytes (staged epilogue)
+    uint8_t *s_res = s_out + (p.out_tma ? 2 * p.out_tile_bytes : 0);            // 2 x out_tile_bytes (TMA residual)
+    float *s_alpha = reinterpret_cast<float *>(s_res + (p.res_tma ? 2 * p.out_tile_bytes : 0));  // [OC]
     float *s_beta = s_alpha + p.OC;                             // [OC]
     uint64_t *full = reinterpret_cast<uint64_t *>(s_beta + p.OC);
     uint64_t *empty = full + 8;
     uint64_t *tmem_full = empty + 8;
     uint64_t *tmem_empty = tmem_full + 4;
     uint64_t *filter_bar = tmem_empty + 4;
-    uint32_t *tmem_holder = reinterpret_cast<uint32_t *>(filter_bar + 1);
+    uint64_t *res_full = filter_bar + 1;
+    uint64_t *res_empty = res_full + 2;
+    uint32_t *tmem_holder = reinterpret_cast<uint32_t *>(res_empty + 2);
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int taps = p.kh * p.kw;
+    const int tiles_per_image = p.row_blocks * p.col_blocks;
+    const int ochunks = p.OC >> 6;  // 64-channel chunks of the output (staged epilogue only)
 
     if (threadIdx.x == 0) {
         tma_prefetch_desc(&tmIn);
         tma_prefetch_desc(&tmF);
+        if (p.out_tma) tma_prefetch_desc(&tmOut);
+        if (p.res_tma) tma_prefetch_desc(&tmRes);
         for (int s = 0; s < p.stages; s++) {
-            mbar_init(&full[s], 2);   // one arrive(+expect-tx) from each producer warp
+            mbar_init(&full[s], 1);   // the producer's arrive(+expect-tx)
             mbar_init(&empty[s], 1);  // one tcgen05.commit
         }
         for (int b = 0; b < p.num_acc; b++) {
             mbar_init(&tmem_full[b], 1);
-            mbar_init(&tmem_empty[b], 4);  // one arrival per epilogue warp
+            mbar_init(&tmem_empty[b], 8);  // one arrival per epilogue warp
+        }
+        for (int b = 0; b < 2; b++) {
+            mbar_init(&res_full[b], 1);
+            mbar_init(&res_empty[b], 8);
         }
         mbar_init(filter_bar, 1);
         fence_barrier_init();
@@ -106,12 +208,10 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap tmIn, const __grid_constant__
     tc_fence_after();
     const uint32_t tmem_base = *tmem_holder;
 
-    if (warp == 0 || warp == 6) {
-        // ------------------------------------------------------------ TMA producers
-        // Lane 0 of each producer warp does the work; the other lanes wait at the __syncwarp of each round
-        // (a lone lane looping while its siblings sit at the CTA barrier runs several times slower).
-        const int half = warp == 0 ? 0 : 1;  // which 8x8 block of every slot this warp fills
-        if (warp == 0 && lane == 0) {
+    if (warp == 0) {
+        // ------------------------------------------------------------ TMA producer (warp-uniform loop, one elected lane issues)
+        const bool leader = elect_one();
+        if (leader) {
             // the filter, once: one box [OC x 64] per (tap, channel chunk)
             mbar_expect_tx(filter_bar, (uint32_t)p.filter_bytes);
             for (int t = 0; t < taps; t++)
@@ -121,35 +221,44 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap tmIn, const __grid_constant__
         __syncwarp();
         uint32_t issued = 0, ph = 0;
         int st = 0;
-        bool ok = true;
-        const int bpi = p.blocks_h * p.blocks_w;
-        const uint32_t tx_bytes = (uint32_t)p.slots * (BLOCK_PIX * 128);
-        for (long long tile = blockIdx.x; tile < p.num_tiles && ok; tile += gridDim.x) {
-            const long long b = tile * 2 + half;
-            const int bn = (int)(b / bpi), r = (int)(b - (long long)bn * bpi);  // bn >= N past the end: all zeros
-            const int bh0 = (r / p.blocks_w) * 8 - p.pt, bw0 = (r % p.blocks_w) * 8 - p.pl;
-            for (int kx = 0; kx < p.kh; kx++) {
-                if (lane == 0) {
-                    ok = mbar_wait(&empty[st], ph ^ 1, p.status, kWaitEmpty);
-                    if (ok) {
-                        mbar_expect_tx(&full[st], tx_bytes);
-                        uint8_t *dst = s_a + (size_t)st * row_bytes + half * (BLOCK_PIX * 128);
-                        for (int ky = 0; ky < p.kw; ky++)
-                            for (int kc = 0; kc < p.kchunks; kc++, dst += A_STAGE_BYTES)
-                                tma_load_4d(dst, &tmIn, &full[st], kc * BK, bw0 + ky, bh0 + kx, bn);
-                    }
-                }
-                ok = __shfl_sync(0xffffffffu, ok, 0);
+        const uint32_t res_box_bytes = (uint32_t)(p.cw * 2 * 128);
+        for (long long tile = blockIdx.x; tile < p.num_tiles; tile += gridDim.x) {
+            const int n = (int)(tile / tiles_per_image), r = (int)(tile - (long long)n * tiles_per_image);
+            const int oh0 = (r / p.col_blocks) * 2, ow0 = (r % p.col_blocks) * p.cw;
+            TIMING(const long long tw0 = clock64();)
+            bool ok = mbar_wait(&empty[st], ph ^ 1, p.status, kWaitEmpty);
+            ok = __all_sync(0xffffffffu, ok);
+            TIMING(if (blockIdx.x == 0 && lane == 0) g_conv_timing[0] += clock64() - tw0;)
+            if (!ok) break;
+            if (leader) {
+                mbar_expect_tx(&full[st], (uint32_t)p.stage_bytes);
+                uint8_t *dst = s_a + (size_t)st * p.stage_bytes;
+                for (int kc = 0; kc < p.kchunks; kc++, dst += p.chunk_bytes)
+                    tma_load_4d(dst, &tmIn, &full[st], kc * BK, ow0 - p.pl, oh0 - p.pt, n);  // outside the image: zeros
+            }
+            __syncwarp();
+            if (p.res_tma) {
+                // the tile's residual, in the layout the epilogue stages its output in
+                const uint32_t b = issued & 1, rph = (issued >> 1) & 1;
+                ok = mbar_wait(&res_empty[b], rph ^ 1, p.status, kWaitEmpty);
+                ok = __all_sync(0xffffffffu, ok);
                 if (!ok) break;
-                issued++;
-                if (++st == p.stages) {
-                    st = 0;
-                    ph ^= 1;
+                if (leader) {
+                    mbar_expect_tx(&res_full[b], res_box_bytes * (uint32_t)ochunks);
+                    for (int oc = 0; oc < ochunks; oc++)
+                        tma_load_4d(s_res + (size_t)b * p.out_tile_bytes + (size_t)oc * OUT_CHUNK_BYTES, &tmRes, &res_full[b],
+                                    oc * 64, ow0, oh0, n);
                 }
+                __syncwarp();
+            }
+            issued++;
+            if (++st == p.stages) {
+                st = 0;
+                ph ^= 1;
             }
         }
         // Drain: do not leave while copies may still be landing in this CTA's shared memory.  Walk back
-        // over the last fill of every stage and wait for it to complete.
+        // over the last fill of every stage (and of both residual buffers) and wait for it to complete.
         if (lane == 0) {
             int s2 = st;
             uint32_t ph2 = ph;
@@ -161,135 +270,155 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap tmIn, const __grid_constant__
                 s2--;
                 if (!mbar_wait(&full[s2], ph2, p.status, kWaitDrain)) break;
             }
-            if (warp == 0) mbar_wait(filter_bar, 0, p.status, kWaitDrain);
+            if (p.res_tma)
+                for (uint32_t back = 0; back < 2 && back < issued; back++) {
+                    const uint32_t i = issued - 1 - back;
+                    if (!mbar_wait(&res_full[i & 1], (i >> 1) & 1, p.status, kWaitDrain)) break;
+                }
+            mbar_wait(filter_bar, 0, p.status, kWaitDrain);
         }
         __syncwarp();
     } else if (warp == 1) {
-        // ------------------------------------------------------------ MMA issuer (lane 0 works, the warp re-converges each round)
+        // ------------------------------------------------------------ MMA issuer (warp-uniform loop, one elected lane issues)
+        const bool leader = elect_one();
         const uint32_t idesc = idesc_bf16_f32(BM, p.OC);
-        bool ok = true;
-        if (lane == 0) ok = mbar_wait(filter_bar, 0, p.status, kWaitFull);
-        ok = __shfl_sync(0xffffffffu, ok, 0);
+        bool ok = mbar_wait(filter_bar, 0, p.status, kWaitFull);
+        ok = __all_sync(0xffffffffu, ok);
         tc_fence_after();
         uint32_t it = 0, ph = 0;
         int st = 0;
-        // descriptors differ from slot to slot and from tap to tap only in the 14-bit address field
+        // descriptors differ from window to window and from tap to tap only in the 14-bit address field
         const uint64_t da0 = smem_desc_sw128(smem_u32(s_a)), db0 = smem_desc_sw128(smem_u32(s_filter));
         const uint64_t b_step = (uint64_t)((p.OC * 128) >> 4);
+        const uint64_t chunk_step = (uint64_t)(p.chunk_bytes >> 4), stage_step = (uint64_t)(p.stage_bytes >> 4);
         for (long long tile = blockIdx.x; tile < p.num_tiles && ok; tile += gridDim.x, it++) {
             const uint32_t buf = it % p.num_acc, aph = (it / p.num_acc) & 1;
-            if (lane == 0) {
-                ok = mbar_wait(&tmem_empty[buf], aph ^ 1, p.status, kWaitTmemEmpty);
-                tc_fence_after();
-                const uint32_t d_tmem = tmem_base + buf * p.acc_stride;
-                uint64_t db = db0;
-                for (int kx = 0; kx < p.kh && ok; kx++) {
-                    ok = mbar_wait(&full[st], ph, p.status, kWaitFull);
-                    if (!ok) break;
-                    tc_fence_after();
-                    uint64_t da = da0 + (uint64_t)st * (uint64_t)(row_bytes >> 4);
-                    for (int i = 0; i < p.slots; i++) {
-                        // advancing K by 16 elements = 32 bytes inside the swizzle row: +2 in the >>4 address field
-                        umma_bf16(d_tmem, da, db, idesc, (uint32_t)((kx | i) != 0));
-                        umma_bf16(d_tmem, da + 2, db + 2, idesc, 1u);
-                        umma_bf16(d_tmem, da + 4, db + 4, idesc, 1u);
-                        umma_bf16(d_tmem, da + 6, db + 6, idesc, 1u);
-                        da += A_STAGE_BYTES >> 4;
+            TIMING(const long long tm0 = clock64();)
+            ok = mbar_wait(&tmem_empty[buf], aph ^ 1, p.status, kWaitTmemEmpty);
+            TIMING(const long long tm1 = clock64();)
+            if (ok) ok = mbar_wait(&full[st], ph, p.status, kWaitFull);
+            ok = __all_sync(0xffffffffu, ok);
+            TIMING(const long long tm2 = clock64();)
+            if (!ok) break;
+            tc_fence_after();
+            const uint32_t d_tmem = tmem_base + buf * p.acc_stride;
+            const uint64_t da_stage = da0 + (uint64_t)st * stage_step;
+            uint64_t db = db0;
+            for (int kx = 0; kx < p.kh; kx++) {
+                for (int ky = 0; ky < p.kw; ky++) {
+                    // tap (kx, ky): the window read from (kx*64 + ky) pixels further on; one pixel = 128 B = 8 address units
+                    uint64_t da = da_stage + (uint64_t)((kx * ROW_PIX + ky) * 8);
+                    for (int kc = 0; kc < p.kchunks; kc++) {
+                        if (leader) {
+                            // advancing K by 16 elements = 32 bytes inside the swizzle row: +2 in the >>4 address field
+                            umma_bf16(d_tmem, da, db, idesc, (uint32_t)((kx | ky | kc) != 0));
+                            umma_bf16(d_tmem, da + 2, db + 2, idesc, 1u);
+                            umma_bf16(d_tmem, da + 4, db + 4, idesc, 1u);
+                            umma_bf16(d_tmem, da + 6, db + 6, idesc, 1u);
+                        }
+                        __syncwarp();
+                        da += chunk_step;
                         db += b_step;
                     }
-                    umma_commit(&empty[st]);  // the row's slots are reusable once these MMAs have read them
-                    if (++st == p.stages) {
-                        st = 0;
-                        ph ^= 1;
-                    }
                 }
-                if (ok) umma_commit(&tmem_full[buf]);
             }
-            ok = __shfl_sync(0xffffffffu, ok, 0);
-            st = __shfl_sync(0xffffffffu, st, 0);
-            ph = __shfl_sync(0xffffffffu, ph, 0);
+            if (leader) {
+                umma_commit(&empty[st]);       // the window is reusable once these MMAs have read it
+                umma_commit(&tmem_full[buf]);  // and the accumulator is complete
+            }
+            __syncwarp();
+            TIMING(if (blockIdx.x == 0 && lane == 0) {
+                g_conv_timing[1] += tm1 - tm0; g_conv_timing[2] += tm2 - tm1; g_conv_timing[3] += clock64() - tm2; g_conv_timing[4] += 1;
+            })
+            if (++st == p.stages) {
+                st = 0;
+                ph ^= 1;
+            }
         }
     } else {
-        // ------------------------------------------------------------ epilogue: one thread per output pixel
-        const int quarter = warp & 3;
+        // ------------------------------------------------------------ epilogue: one thread per output pixel and 32-channel pass
+        const int quarter = warp & 3;                 // the tensor-memory lane quarter this warp may read
+        const int chalf = (warp - 2) >> 2;            // warps 2-5 take channels [0,32) of every 64, warps 6-9 [32,64)
         const int row = quarter * 32 + lane;          // row of the tile = TMEM lane
-        const int half = row >> 6, r64 = row & 63;    // which 8x8 block, position inside it
-        const int bpi = p.blocks_h * p.blocks_w;
+        const int trow = row >> 6, tcol = row & 63;   // position inside the 2 x 64 tile
+        const int q = trow * p.cw + tcol;             // pixel's row in the staged tile (box {64 ch, cw, 2, 1})
+        const uint32_t swz = (uint32_t)(q & 7);       // 128-byte swizzle: 16-byte chunk index ^ (row & 7)
+        const bool issuer = warp == 2 && lane == 0;   // issues the tile's TMA stores
+        const int c_first = chalf * 32;
         uint32_t it = 0;
         for (long long tile = blockIdx.x; tile < p.num_tiles; tile += gridDim.x, it++) {
             const uint32_t buf = it % p.num_acc, aph = (it / p.num_acc) & 1;
+            const uint32_t sb = it & 1, sph = (it >> 1) & 1;  // staging buffer of this tile
+            const int n = (int)(tile / tiles_per_image), r = (int)(tile - (long long)n * tiles_per_image);
+            const int oh0 = (r / p.col_blocks) * 2, ow0 = (r % p.col_blocks) * p.cw;
+            const int oh = oh0 + trow, ow = ow0 + tcol;
+            const bool valid = tcol < p.cw && oh < p.OH && ow < p.OW;
+            const size_t pix = ((size_t)n * p.OH + oh) * p.OW + ow;
             bool ok = true;
-            if (lane == 0) ok = mbar_wait(&tmem_full[buf], aph, p.status, kWaitTmemFull);
+            TIMING(const long long te0 = clock64();)
+            if (lane == 0) {
+                ok = mbar_wait(&tmem_full[buf], aph, p.status, kWaitTmemFull);
+                if (ok && p.res_tma) ok = mbar_wait(&res_full[sb], sph, p.status, kWaitFull);
+            }
             ok = __shfl_sync(0xffffffffu, ok, 0);
+            TIMING(const long long te1 = clock64();)
             if (!ok) break;
             tc_fence_after();
-            const long long b = tile * 2 + half;
-            const int n = (int)(b / bpi), r = (int)(b - (long long)n * bpi);
-            const int oh = (r / p.blocks_w) * 8 + (r64 >> 3), ow = (r % p.blocks_w) * 8 + (r64 & 7);
-            const bool valid = n < p.N && oh < p.OH && ow < p.OW;
-            const size_t pix = ((size_t)n * p.OH + oh) * p.OW + ow;
-            for (int c0 = 0; c0 < p.OC; c0 += 32) {
+            for (int c0 = c_first; c0 < p.OC; c0 += 64) {
                 uint32_t acc[32];
                 __syncwarp();
                 tmem_ld_32x32(tmem_base + ((uint32_t)(quarter * 32) << 16) + buf * p.acc_stride + c0, acc);
                 tmem_ld_wait();
-                if (!valid) continue;
+                if (p.out_tma ? tcol >= p.cw : !valid) continue;
                 float v[32];
-#pragma unroll
-                for (int j = 0; j < 32; j++) v[j] = fmaf(__uint_as_float(acc[j]), s_alpha[c0 + j], s_beta[c0 + j]);
+                apply_affine(acc, s_alpha, s_beta, c0, v);
+                // this pass's 64 bytes of the pixel's 128-byte row in a staged 64-channel chunk: 16-byte chunks ch16 .. ch16+3
+                const uint32_t row_off = (uint32_t)(c0 >> 6) * OUT_CHUNK_BYTES + (uint32_t)q * 128u;
+                const uint32_t ch16 = (uint32_t)(c0 & 63) >> 3;
                 if (p.residual) {
-                    if (p.res_is_f32) {
-                        const float4 *rp = reinterpret_cast<const float4 *>(
-                            reinterpret_cast<const float *>(p.residual) + pix * p.OC + c0);
+                    if (p.res_tma) {
+                        const uint8_t *rr = s_res + (size_t)sb * p.out_tile_bytes + row_off;
 #pragma unroll
-                        for (int j = 0; j < 8; j++) {
-                            float4 q = __ldg(rp + j);
-                            v[4 * j] += q.x;
-                            v[4 * j + 1] += q.y;
-                            v[4 * j + 2] += q.z;
-                            v[4 * j + 3] += q.w;
-                        }
-                    } else {
-                        const uint4 *rp = reinterpret_cast<const uint4 *>(
-                            reinterpret_cast<const __nv_bfloat16 *>(p.residual) + pix * p.OC + c0);
-#pragma unroll
-                        for (int j = 0; j < 4; j++) {
-                            uint4 q = __ldg(rp + j);
-                            const uint32_t w[4] = {q.x, q.y, q.z, q.w};
-#pragma unroll
-                            for (int e = 0; e < 4; e++) {
-                                v[8 * j + 2 * e] += __uint_as_float(w[e] << 16);
-                                v[8 * j + 2 * e + 1] += __uint_as_float(w[e] & 0xffff0000u);
-                            }
-                        }
+                        for (int j = 0; j < 4; j++)
+                            add_bf16x8(v + 8 * j, *reinterpret_cast<const uint4 *>(rr + (((ch16 + j) ^ swz) << 4)));
+                    } else if (valid) {
+                        add_residual_global(p, v, pix, c0);
                     }
                 }
                 if (p.relu) {
 #pragma unroll
                     for (int j = 0; j < 32; j++) v[j] = (v[j] > 0.f) ? v[j] : 0.f;
                 }
-                if (p.out_is_f32) {
-                    float4 *op = reinterpret_cast<float4 *>(reinterpret_cast<float *>(p.out) + pix * p.OC + c0);
+                if (p.out_tma) {
+                    uint8_t *so = s_out + (size_t)sb * p.out_tile_bytes + row_off;
 #pragma unroll
-                    for (int j = 0; j < 8; j++) op[j] = make_float4(v[4 * j], v[4 * j + 1], v[4 * j + 2], v[4 * j + 3]);
+                    for (int j = 0; j < 4; j++) *reinterpret_cast<uint4 *>(so + (((ch16 + j) ^ swz) << 4)) = pack_bf16x8(v + 8 * j);
                 } else {
-                    uint4 *op = reinterpret_cast<uint4 *>(reinterpret_cast<__nv_bfloat16 *>(p.out) + pix * p.OC + c0);
-#pragma unroll
-                    for (int j = 0; j < 4; j++) {
-                        uint4 o;
-                        __nv_bfloat162 *h2 = reinterpret_cast<__nv_bfloat162 *>(&o);
-                        h2[0] = __floats2bfloat162_rn(v[8 * j], v[8 * j + 1]);
-                        h2[1] = __floats2bfloat162_rn(v[8 * j + 2], v[8 * j + 3]);
-                        h2[2] = __floats2bfloat162_rn(v[8 * j + 4], v[8 * j + 5]);
-                        h2[3] = __floats2bfloat162_rn(v[8 * j + 6], v[8 * j + 7]);
-                        op[j] = o;
-                    }
+                    store_global(p, v, pix, c0);
                 }
             }
             tc_fence_before();
             __syncwarp();
-            if (lane == 0) mbar_arrive(&tmem_empty[buf]);
+            TIMING(if (blockIdx.x == 0 && lane == 0 && warp == 2) { g_conv_timing[5] += te1 - te0; g_conv_timing[6] += clock64() - te1; })
+            if (lane == 0) {
+                mbar_arrive(&tmem_empty[buf]);
+                if (p.res_tma) mbar_arrive(&res_empty[sb]);
+            }
+            if (p.out_tma) {
+                // The staged tile leaves by TMA.  Before the barrier the issuing thread makes sure that every
+                // earlier store has finished reading shared memory: past the barrier the other staging buffer
+                // (read by the previous tile's store) is free for the next tile.
+                fence_proxy_async();
+                if (issuer) bulk_wait_read_all();
+                named_barrier(1, kEpilogueThreads);
+                if (issuer) {
+                    const uint8_t *so = s_out + (size_t)sb * p.out_tile_bytes;
+                    for (int oc = 0; oc < ochunks; oc++) tma_store_4d(&tmOut, so + (size_t)oc * OUT_CHUNK_BYTES, oc * 64, ow0, oh0, n);
+                    bulk_commit_group();
+                }
+            }
         }
+        if (p.out_tma && issuer) bulk_wait_all();  // shared memory stays valid until the last store has read it
     }
 
     __syncwarp();
@@ -303,6 +432,17 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap tmIn, const __grid_constant__
 
 }  // namespace
 
+#ifdef SWC_CONV_TIMING
+// working builds only: cycle counters of CTA 0 {producer wait, issuer wait accumulator, issuer wait window, issuer
+// issue, tiles, epilogue wait, epilogue work}; reading clears them
+SWC_EXPORT int swcb200_debug_conv_timing(long long *out16) {
+    long long zero[16] = {0};
+    if (cudaMemcpyFromSymbol(out16, g_conv_timing, sizeof(zero)) != cudaSuccess) return SWCB200_ERR_CUDA;
+    if (cudaMemcpyToSymbol(g_conv_timing, zero, sizeof(zero)) != cudaSuccess) return SWCB200_ERR_CUDA;
+    return SWCB200_OK;
+}
+#endif
+
 // input/filter bf16; output and residual bf16 or fp32
 int swc_conv_tc(swcb200_ctx *ctx, void *output, int out_dtype, const void *input, const void *filt, const float *bias,
                 const size_t *odims, const size_t *idims, const size_t *fdims, const size_t *kernels, const size_t *strides,
@@ -315,6 +455,7 @@ int swc_conv_tc(swcb200_ctx *ctx, void *output, int out_dtype, const void *input
     if (strides[0] != 1 || strides[1] != 1) return swc_fail(ctx, SWCB200_ERR_UNSUPPORTED, "conv2d_bf16: stride must be 1");
     if (p.C % 64 != 0 || p.OC % 32 != 0 || p.OC > 256 || p.OC < 32)
         return swc_fail(ctx, SWCB200_ERR_UNSUPPORTED, "conv2d_bf16: needs iC %% 64 == 0 and oC in {32, 64, ..., 256}");
+    if (p.kw > 9) return swc_fail(ctx, SWCB200_ERR_UNSUPPORTED, "conv2d_bf16: filter wider than 9");
     p.kchunks = p.C / 64;
     p.filter_bytes = p.kh * p.kw * p.kchunks * p.OC * 128;
     if (p.filter_bytes > kMaxFilterBytes)
@@ -325,20 +466,9 @@ int swc_conv_tc(swcb200_ctx *ctx, void *output, int out_dtype, const void *input
                 SWCB200_ERR_MISALIGNED, "conv2d_bf16: tensors must be 16-byte aligned");
     // the output a stride-1 convolution of this input can have; rows/columns beyond it would read outside the padding
     SWC_REQUIRE(ctx, p.OH <= p.H + 2 * p.kh && p.OW <= p.W + 2 * p.kw, SWCB200_ERR_BAD_SHAPE, "conv2d_bf16: odims too large");
-    p.blocks_h = (p.OH + 7) / 8;
-    p.blocks_w = (p.OW + 7) / 8;
-    p.num_blocks = (long long)p.N * p.blocks_h * p.blocks_w;
-    p.num_tiles = (p.num_blocks + 1) / 2;
     p.acc_stride = p.OC <= 64 ? 64 : (p.OC <= 128 ? 128 : 256);
     p.num_acc = 512 / p.acc_stride < 4 ? 512 / p.acc_stride : 4;
     p.tmem_cols = p.acc_stride * p.num_acc;
-    const int fixed = p.filter_bytes + 2 * p.OC * 4 + 256 + 1024;
-    p.slots = p.kw * p.kchunks;
-    p.stages = (kMaxSmem - fixed) / (p.slots * A_STAGE_BYTES);
-    if (p.stages > 8) p.stages = 8;
-    if (p.stages < 2)
-        return swc_fail(ctx, SWCB200_ERR_UNSUPPORTED, "conv2d_bf16: two filter rows of operands (2 x %d KiB) do not fit beside the filter",
-                        p.slots * A_STAGE_BYTES / 1024);
     p.bias = bias;
     if (ep) {
         const int nbn = (ep->bn_scale != nullptr) + (ep->bn_bias != nullptr) + (ep->bn_mean != nullptr) + (ep->bn_var != nullptr);
@@ -353,11 +483,34 @@ int swc_conv_tc(swcb200_ctx *ctx, void *output, int out_dtype, const void *input
     p.res_is_f32 = res_dtype == SWCB200_F32;
     p.status = ctx->dev_status;
 
-    CUtensorMap tmIn, tmF;
+    // shared-memory plan: filter | windows | 1 KiB slack | output staging | residual staging | coefficients | barriers
+    p.hr = p.kh + 1;
+    p.cw = ROW_PIX - (p.kw - 1);
+    p.chunk_bytes = p.hr * ROW_PIX * 128;
+    p.stage_bytes = p.chunk_bytes * p.kchunks;
+    p.out_tile_bytes = (p.OC / 64) * OUT_CHUNK_BYTES;
+    const int fixed = p.filter_bytes + 1024 + 2 * p.OC * 4 + 256 + 1024;
+    p.out_tma = !p.out_is_f32 && p.OC % 64 == 0;
+    p.res_tma = p.out_tma && p.residual != nullptr && !p.res_is_f32;
+    auto stages_for = [&](int out_tma, int res_tma) {
+        return (kMaxSmem - fixed - (out_tma ? 2 * p.out_tile_bytes : 0) - (res_tma ? 2 * p.out_tile_bytes : 0)) / p.stage_bytes;
+    };
+    if (stages_for(p.out_tma, p.res_tma) < 2) p.res_tma = 0;
+    if (stages_for(p.out_tma, p.res_tma) < 2) p.out_tma = 0;
+    p.stages = stages_for(p.out_tma, p.res_tma);
+    if (p.stages > 8) p.stages = 8;
+    if (p.stages < 2)
+        return swc_fail(ctx, SWCB200_ERR_UNSUPPORTED, "conv2d_bf16: two input windows (2 x %d KiB) do not fit beside the filter",
+                        p.stage_bytes / 1024);
+    p.row_blocks = (p.OH + 1) / 2;
+    p.col_blocks = (p.OW + p.cw - 1) / p.cw;
+    p.num_tiles = (long long)p.N * p.row_blocks * p.col_blocks;
+
+    CUtensorMap tmIn, tmF, tmOut, tmRes;
     {
         uint64_t dims[4] = {(uint64_t)p.C, (uint64_t)p.W, (uint64_t)p.H, (uint64_t)p.N};
         uint64_t str[4] = {2, (uint64_t)p.C * 2, (uint64_t)p.W * p.C * 2, (uint64_t)p.H * p.W * p.C * 2};
-        uint32_t box[4] = {64, 8, 8, 1};
+        uint32_t box[4] = {64, (uint32_t)ROW_PIX, (uint32_t)p.hr, 1};
         int rc = tc::make_tmap_bf16(ctx, &tmIn, input, 4, dims, str, box);
         if (rc) return rc;
     }
@@ -369,13 +522,28 @@ int swc_conv_tc(swcb200_ctx *ctx, void *output, int out_dtype, const void *input
         int rc = tc::make_tmap_bf16(ctx, &tmF, filt, 3, dims, str, box);
         if (rc) return rc;
     }
-    const size_t smem = (size_t)p.filter_bytes + (size_t)p.stages * p.slots * A_STAGE_BYTES + 2 * p.OC * 4 + 256 + 1024;
+    tmOut = tmIn;
+    tmRes = tmIn;
+    if (p.out_tma) {
+        // output (and residual) seen tile by tile: 64 channels x cw columns x 2 rows
+        uint64_t dims[4] = {(uint64_t)p.OC, (uint64_t)p.OW, (uint64_t)p.OH, (uint64_t)p.N};
+        uint64_t str[4] = {2, (uint64_t)p.OC * 2, (uint64_t)p.OW * p.OC * 2, (uint64_t)p.OH * p.OW * p.OC * 2};
+        uint32_t box[4] = {64, (uint32_t)p.cw, 2, 1};
+        int rc = tc::make_tmap_bf16(ctx, &tmOut, output, 4, dims, str, box);
+        if (rc) return rc;
+        if (p.res_tma) {
+            rc = tc::make_tmap_bf16(ctx, &tmRes, p.residual, 4, dims, str, box);
+            if (rc) return rc;
+        }
+    }
     if (!ctx->conv_attr_set) {
         SWC_CUDA(ctx, cudaFuncSetAttribute(conv_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kMaxSmem));
         ctx->conv_attr_set = true;
     }
+    const size_t smem = (size_t)fixed + (size_t)p.stages * p.stage_bytes + (p.out_tma ? 2 * p.out_tile_bytes : 0) +
+                        (p.res_tma ? 2 * p.out_tile_bytes : 0);
     unsigned grid = (unsigned)(p.num_tiles < ctx->sm_count ? p.num_tiles : ctx->sm_count);
-    conv_tc_kernel<<<grid, kThreads, smem, ctx->stream>>>(tmIn, tmF, p);
+    conv_tc_kernel<<<grid, kThreads, smem, ctx->stream>>>(tmIn, tmF, tmOut, tmRes, p);
     return swc_check_launch(ctx, "conv2d_bf16");
 }
 

@@ -107,15 +107,17 @@ class FcPairProgram:
     communication context's stream while the tensor cores work on chunk i+1.
     """
 
-    def __init__(self, be: Backend, comm, w1_full, w2_full, max_rows: int):
+    def __init__(self, be: Backend, comm, w1, w2, max_rows: int, sharded: bool = False):
+        """`w1` [k, n1] and `w2` [n1, n2] are the full matrices (each rank keeps its shard), or, with
+        `sharded`, already this rank's shards [k, n1/p] and [n1/p, n2] (the full matrices never exist)."""
         from . import parallel as par
         self.be, self.comm = be, comm
         p, r = comm.nranks, comm.rank
-        w1s = par.take_shard(w1_full, 1, r, p)      # [k, n1/p]
-        w2s = par.take_shard(w2_full, 0, r, p)      # [n1/p, n2]
+        w1s = w1 if sharded else par.take_shard(w1, 1, r, p)      # [k, n1/p]
+        w2s = w2 if sharded else par.take_shard(w2, 0, r, p)      # [n1/p, n2]
         self.wp1 = be.pack_weight_bf16(w1s)         # [n1/p, k]
         self.wp2 = be.pack_weight_bf16(w2s)         # [n2, n1/p]
-        self.k, self.n1s, self.n2 = w1_full.shape[0], w1s.shape[1], w2_full.shape[1]
+        self.k, self.n1s, self.n2 = w1s.shape[0], w1s.shape[1], w2s.shape[1]
         self.h = torch.empty((max_rows, self.n1s), dtype=torch.bfloat16, device=be.device)
         self.y_part = torch.empty((max_rows, self.n2), dtype=torch.float32, device=be.device)
         self.y = torch.empty((max_rows, self.n2), dtype=torch.float32, device=be.device)

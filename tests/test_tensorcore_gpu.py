@@ -132,10 +132,14 @@ def _conv_case(r, n, h, w, c, oc, k, pads):
 
 
 @pytest.mark.parametrize("n,h,w,c,oc,k,pads", [
-    (1, 8, 8, 64, 64, (3, 3), (1, 1, 1, 1)),       # one 8x8 block, one tile with an empty second half
-    (2, 16, 16, 64, 64, (3, 3), (1, 1, 1, 1)),     # whole tiles
-    (3, 12, 20, 64, 32, (3, 3), (1, 1, 1, 1)),     # ragged blocks in both directions, odd block count, oC 32
-    (2, 9, 7, 128, 96, (1, 1), (0, 0, 0, 0)),      # 1x1, two channel chunks, oC 96
+    (1, 8, 8, 64, 64, (3, 3), (1, 1, 1, 1)),       # image much narrower than the 64-pixel window
+    (2, 16, 16, 64, 64, (3, 3), (1, 1, 1, 1)),
+    (3, 12, 20, 64, 32, (3, 3), (1, 1, 1, 1)),     # oC 32
+    (2, 9, 7, 128, 96, (1, 1), (0, 0, 0, 0)),      # 1x1, two channel chunks, oC 96, odd row count (half-empty last tile)
+    (1, 5, 70, 64, 64, (3, 3), (1, 1, 1, 1)),      # wider than one window: two column blocks (62 + 8), odd row count
+    (2, 56, 56, 64, 64, (3, 3), (1, 1, 1, 1)),     # the geometry of the ResNet-style stage
+    (1, 6, 130, 128, 32, (3, 3), (1, 1, 1, 1)),    # three column blocks, two channel chunks
+    (2, 9, 7, 128, 128, (1, 1), (0, 0, 0, 0)),     # oC 128: two staged output chunks; the residual read directly
     (1, 14, 14, 64, 128, (5, 5), (2, 2, 2, 2)),    # 5x5 (25 taps resident: 200 KiB > limit) -> must be refused
     (2, 10, 10, 64, 64, (3, 3), (0, 0, 0, 0)),     # no padding: output 8x8
     (1, 11, 13, 64, 64, (3, 2), (2, 0, 2, 0)),     # asymmetric window and padding
