@@ -9,6 +9,13 @@
 // offsets, stages file-initialised tensors through a host buffer, and synchronises before results are
 // read back and printed.
 //
+// With `fuse` (and tensor-core precision) the generator plans at emit time: it matches the chains the
+// lowering pass leaves behind -- MatrixMatrixMul -> MatrixVectorAdd -> Tanh/Relu, and
+// Conv2d -> BatchNormalization -> ElementAdd -> Relu -- and prints ONE fused table call for each
+// (swcb200_fc_bf16, swcb200_conv2d_bf16).  Weights and filters are packed to bf16 once after loading,
+// activations that only fused calls read are kept in bf16, and casts are printed only where an fp32
+// consumer (an unfused op, a displayed tensor) meets a bf16 producer or the other way round.
+//
 // This header needs the reference's headers on the include path (-I<reference>/src); it is compiled
 // only where a reference checkout is present (swcompiler_b200/codegen/build_codegen.py).
 #pragma once
@@ -26,7 +33,8 @@ class B200Codegen : public swc::codegen::Codegen {
   public:
     // precision: 0 = strict fp32 (bit-exact with the reference's generated C), 1 = tensor-core bf16 for the
     // fp32 entry points (see swc_b200.h)
-    B200Codegen(swc::IRGraph *graph, Config &config, int device = 0, int precision = 0);
+    // fuse: plan fused calls as described above (ignored in strict precision: there are no fused strict kernels)
+    B200Codegen(swc::IRGraph *graph, Config &config, int device = 0, int precision = 0, bool fuse = false);
 
     void emitHeader() override;
     void emitEnvInit() override;
@@ -44,13 +52,53 @@ class B200Codegen : public swc::codegen::Codegen {
     std::string makefileText(const std::string &repo_root) const;
     size_t arenaBytes() const { return arena_bytes_; }
 
+    // number of fused calls planned (after genCode)
+    int fusedGroups() const { return (int)groups_.size(); }
+
   private:
+    // A chain of op nodes printed as one call.  Intermediate tensors of the chain are never materialised.
+    struct Group {
+        enum Kind { FC, CONV } kind;
+        std::vector<swc::OpNode *> ops;      // in chain order; ops[0] is the head
+        swc::Tensor *in = nullptr;           // A (FC) / input image (conv)
+        swc::Tensor *weight = nullptr;       // W[k,n] (FC) / filter [oC,kh,kw,iC] (conv)
+        swc::Tensor *bias = nullptr;         // may be null for FC
+        swc::Tensor *bn[4] = {nullptr, nullptr, nullptr, nullptr};  // scale, bias, mean, var
+        float bn_eps = 0.f;
+        swc::Tensor *skip = nullptr;         // residual
+        int act = 0;                         // 0 none, 1 relu, 2 tanh
+        swc::Tensor *out = nullptr;          // the chain's last tensor
+    };
+    void planFusion();
+    bool matchFc(swc::OpNode *op, Group &g);
+    bool matchConv(swc::OpNode *op, Group &g);
+    bool needsF32(swc::Tensor *t);
+    void walk(bool dry);                     // prints (or, dry, only records) the calls of the forward pass
+    void emitGroup(const Group &g, std::ostream &os, bool dry);
+    void ensureF32(swc::Tensor *t, std::ostream &os);
+    void ensureBf16(swc::Tensor *t, std::ostream &os);
+    swc::Tensor *root(swc::Tensor *t);       // the tensor a view (Reshape) finally aliases
+    std::string bf16Name(swc::Tensor *t) { return nameOf(root(t)) + "_bf16"; }
+    std::string packedName(swc::Tensor *t) { return nameOf(t) + "_packed"; }
+    std::string dimsArrayTo(std::ostream &os, const std::string &name, const std::vector<size_t> &dims);
+
     void emitOp(swc::OpNode *op);
+    void emitOpTo(swc::OpNode *op, std::ostream &os);
     void emitPrintOutputs();
     std::string dimsArray(const std::string &name, const std::vector<size_t> &dims);
     std::string nameOf(swc::Tensor *t) { return tensors_name_map_[t]; }
+    // the fp32 storage a tensor is read from: its own, or, for a view in a fused plan, the viewed tensor's
+    std::string f32Name(swc::Tensor *t) { return fuse_ ? nameOf(root(t)) : nameOf(t); }
 
     int device_, precision_;
+    bool fuse_;
+    std::vector<Group> groups_;
+    std::map<swc::OpNode *, int> group_of_;          // op node -> index into groups_
+    std::map<swc::Tensor *, swc::Tensor *> alias_;     // view -> viewed
+    std::map<swc::Tensor *, bool> have_f32_, have_bf16_;   // state of the walk, keyed by root tensor
+    std::map<swc::Tensor *, bool> made_f32_, made_bf16_;   // what the dry walk materialised (drives the arena plan)
+    std::map<swc::Tensor *, size_t> bf16_offsets_, packed_offsets_;
+    std::vector<swc::Tensor *> bf16_order_, packed_order_;
     size_t arena_bytes_ = 0, stage_bytes_ = 0;
     std::map<swc::Tensor *, size_t> offsets_;
     std::vector<swc::Tensor *> order_;  // tensors in the order they were placed

@@ -59,7 +59,7 @@ def build(ref: str = "/root/reference", quiet: bool = True) -> str:
 
 def emit(exe: str, out_dir: str = EMITTED):
     os.makedirs(out_dir, exist_ok=True)
-    for which in ("mlp8", "convnet"):
+    for which in ("mlp8", "convnet", "mlp8_fused", "convnet_fused", "resblock", "resblock_fused"):
         # the generator also drops Graph.cpp / G_Makefile / SW_Makefile and *.dot in its working directory
         r = subprocess.run([exe, which, out_dir, "$(abspath ../../..)"], cwd=BUILD, capture_output=True, text=True)
         if r.returncode:

@@ -5,6 +5,11 @@
 //                                              (784-512-10, tanh, softmax, top-3)
 //   gen_driver convnet <out_dir> <repo_root>   Conv3x3 -> BatchNorm -> Add(skip) -> ReLU -> MaxPool -> FC ->
 //                                              Softmax -> top-1 on [4,8,8,4] inputs read from files
+//   gen_driver resblock <out_dir> <repo_root>  [2,8,8,64] -> Conv3x3 -> BN -> ReLU -> Conv3x3 -> BN -> Add(skip) -> ReLU ->
+//                                              MaxPool -> FC -> Softmax -> top-1: a residual block wide enough (64
+//                                              channels) for the tensor-core convolution
+//   A name with the suffix _fused (mlp8_fused, convnet_fused, resblock_fused) selects tensor-core precision and the
+//   emit-time fusion planner: one call per fused chain, bf16 activations between fused calls.
 //
 // Needs a reference checkout to compile (swcompiler_b200/codegen/build_codegen.py).
 #include <fstream>
@@ -100,24 +105,74 @@ IRGraph *build_convnet() {
     return g;
 }
 
+IRGraph *build_resblock() {
+    auto *g = new IRGraph();
+    std::vector<size_t> k3{3, 3}, s1{1, 1}, p1{1, 1, 1, 1}, k2{2, 2}, s2{2, 2}, p0{0, 0, 0, 0};
+    auto *x = tensor(g, "image", {2, 8, 8, 64}, "rb_input.bin");
+    TensorNode *cur = x;
+    TensorNode *bn_out[2];
+    for (int i = 0; i < 2; i++) {
+        const std::string n = std::to_string(i);
+        auto *cw = tensor(g, "conv" + n + "_w", {64, 3, 3, 64}, ("rb_conv" + n + "_w.bin").c_str());
+        auto *cb = tensor(g, "conv" + n + "_b", {64}, ("rb_conv" + n + "_b.bin").c_str());
+        auto *conv = op(g, "conv" + n, new Conv2dOp(k3, s1, p1), cur, cw, cb);
+        auto *c = result(g, "conv" + n + "_out", {2, 8, 8, 64}, conv);
+        auto *sc = tensor(g, "bn" + n + "_scale", {64}, ("rb_bn" + n + "_scale.bin").c_str());
+        auto *bi = tensor(g, "bn" + n + "_bias", {64}, ("rb_bn" + n + "_bias.bin").c_str());
+        auto *me = tensor(g, "bn" + n + "_mean", {64}, ("rb_bn" + n + "_mean.bin").c_str());
+        auto *va = tensor(g, "bn" + n + "_var", {64}, ("rb_bn" + n + "_var.bin").c_str());
+        auto *bn = op(g, "bn" + n, new BatchNormalizationOp(1e-5f), c, sc, bi, me, va);
+        bn_out[i] = result(g, "bn" + n + "_out", {2, 8, 8, 64}, bn);
+        if (i == 0) {
+            auto *relu = op(g, "relu0", new ReluOp(), bn_out[0]);
+            cur = result(g, "relu0_out", {2, 8, 8, 64}, relu);
+        }
+    }
+    auto *add = op(g, "add1", new ElementAddOp(), bn_out[1], x);
+    auto *a1 = result(g, "add1_out", {2, 8, 8, 64}, add);
+    auto *relu1 = op(g, "relu1", new ReluOp(), a1);
+    auto *r1 = result(g, "relu1_out", {2, 8, 8, 64}, relu1);
+    auto *pool = op(g, "pool0", new MaxPoolOp(k2, s2, p0), r1);
+    auto *q0 = result(g, "pool_out", {2, 4, 4, 64}, pool);
+    auto *fw = tensor(g, "fc_w", {1024, 10}, "rb_fc_w.bin");
+    auto *fb = tensor(g, "fc_b", {10}, "rb_fc_b.bin");
+    auto *fc = op(g, "fc0", new MatrixMatrixFCBiasOp(), q0, fw, fb);
+    auto *logits = result(g, "logits", {2, 10}, fc);
+    auto *sm = op(g, "softmax", new MatrixSoftmaxOp(), logits);
+    auto *probs = result(g, "probs", {2, 10}, sm);
+    auto *am = op(g, "argmax", new ArgMaxOp(1), probs);
+    auto *top1 = result(g, "top1", {2, 1}, am, DataType::Int32_t);
+    g->findInOut();
+    g->updateTopology();
+    g->addDisplayTensorNodes(probs, top1);
+    return g;
+}
+
 }  // namespace
 
 int main(int argc, char **argv) {
     if (argc < 4) {
-        std::cerr << "usage: gen_driver mlp8|convnet <out_dir> <repo_root>\n";
+        std::cerr << "usage: gen_driver mlp8|convnet|resblock[_fused] <out_dir> <repo_root>\n";
         return 2;
     }
     const std::string which = argv[1], out_dir = argv[2], repo = argv[3];
-    IRGraph *g = which == "mlp8" ? build_mlp8() : build_convnet();
+    const std::string suffix = "_fused";
+    const bool fused = which.size() > suffix.size() && which.compare(which.size() - suffix.size(), suffix.size(), suffix) == 0;
+    const std::string base = fused ? which.substr(0, which.size() - suffix.size()) : which;
+    IRGraph *g = base == "mlp8" ? build_mlp8() : (base == "convnet" ? build_convnet() : (base == "resblock" ? build_resblock() : nullptr));
+    if (!g) {
+        std::cerr << "unknown graph " << base << "\n";
+        return 2;
+    }
     Config config;  // inference, one device, no MPI: the defaults
     g->setConfig(config);
     Engine engine(g);
     engine.compile();  // the reference's own passes: labeling, FC lowering, renaming
-    swcb200::B200Codegen gen(g, config, /*device=*/0, /*precision=*/0);
+    swcb200::B200Codegen gen(g, config, /*device=*/0, /*precision=*/fused ? 1 : 0, /*fuse=*/fused);
     engine.setCodegenerator(&gen);
     const std::string code = engine.genCode();
     std::ofstream(out_dir + "/" + which + "_Graph.cpp") << code;
     std::ofstream(out_dir + "/" + which + "_Makefile") << gen.makefileText(repo);
-    std::cerr << which << ": " << gen.arenaBytes() << " bytes of device arena\n";
+    std::cerr << which << ": " << gen.arenaBytes() << " bytes of device arena, " << gen.fusedGroups() << " fused calls\n";
     return 0;
 }

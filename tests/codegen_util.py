@@ -48,6 +48,42 @@ def convnet_oracle(impl, t):
     return impl.matrixSoftmax_f(impl.fc(h, t["cn_fc_w.bin"], t["cn_fc_b.bin"]))
 
 
+def resblock_inputs(seed=91):
+    """Files of the residual-block graph (gen_driver resblock): [2,8,8,64] image, two 3x3 64->64 convolutions with
+    batch-norm, FC 1024->10."""
+    r = np.random.default_rng(seed)
+    f = np.float32
+    t = {"rb_input.bin": r.standard_normal((2, 8, 8, 64)).astype(f),
+         "rb_fc_w.bin": (r.standard_normal((1024, 10)) * 0.05).astype(f),
+         "rb_fc_b.bin": (r.standard_normal(10) * 0.1).astype(f)}
+    for i in range(2):
+        t[f"rb_conv{i}_w.bin"] = (r.standard_normal((64, 3, 3, 64)) * np.sqrt(2.0 / 576)).astype(f)
+        t[f"rb_conv{i}_b.bin"] = (r.standard_normal(64) * 0.1).astype(f)
+        t[f"rb_bn{i}_scale.bin"] = r.uniform(0.5, 1.5, 64).astype(f)
+        t[f"rb_bn{i}_bias.bin"] = (r.standard_normal(64) * 0.1).astype(f)
+        t[f"rb_bn{i}_mean.bin"] = (r.standard_normal(64) * 0.1).astype(f)
+        t[f"rb_bn{i}_var.bin"] = r.uniform(0.5, 1.5, 64).astype(f)
+    return t
+
+
+def resblock_oracle(impl, t, rnd=lambda a: a):
+    """The graph op by op through the CPU oracle.  `rnd` is applied where the fused tensor-core program rounds to
+    bf16 (image, filters, FC weight, stored activations), so that what is compared is the arithmetic, not the storage."""
+    k3, s1, p1 = (3, 3), (1, 1), (1, 1, 1, 1)
+    x = rnd(t["rb_input.bin"])
+
+    def conv_bn(h, i):
+        h = impl.conv2d_f(h, rnd(t[f"rb_conv{i}_w.bin"]), t[f"rb_conv{i}_b.bin"], k3, s1, p1)
+        return impl.batchnormalization_f(h, t[f"rb_bn{i}_mean.bin"], t[f"rb_bn{i}_var.bin"], t[f"rb_bn{i}_scale.bin"],
+                                         t[f"rb_bn{i}_bias.bin"], 1e-5)
+
+    h = rnd(impl.relu_f(conv_bn(x, 0)))
+    h = conv_bn(h, 1)
+    h = rnd(impl.relu_f(impl.vecAdd_f(h.reshape(-1), x.reshape(-1)).reshape(h.shape)))
+    h = impl.maxpool_f(h, (2, 2), (2, 2), (0, 0, 0, 0))
+    return impl.matrixSoftmax_f(impl.fc(h, rnd(t["rb_fc_w.bin"]), t["rb_fc_b.bin"]))
+
+
 def parse_printed(text: str):
     """{name: 2-D array} from the program's print_device output."""
     out, name, rows = {}, None, []
