@@ -39,6 +39,8 @@
 // Restrictions: stride 1, group 1, iC a multiple of 64, oC a multiple of 32 and <= 256, kw <= 9, filter at
 // most 96 KiB in bf16, two windows fitting beside it.  Other shapes return SWCB200_ERR_UNSUPPORTED (the
 // strict kernel takes them).
+#include <stdlib.h>
+
 #include "tc_common.cuh"
 
 namespace {
@@ -51,6 +53,7 @@ constexpr int OUT_CHUNK_BYTES = 16384;   // staging slot of one 64-channel chunk
 constexpr int kThreads = 320;            // TMA producer, MMA issuer, 8 epilogue warps
 constexpr int kEpilogueThreads = 256;
 constexpr int kMaxFilterBytes = 96 * 1024;
+constexpr int kMaxGroups = kMaxFilterBytes / (32 * 128);  // filter slices of [oC x 64] bf16 at the smallest oC (32)
 constexpr int kMaxSmem = 227 * 1024;
 
 struct ConvParams {
@@ -63,6 +66,10 @@ struct ConvParams {
     int hr, cw, col_blocks, row_blocks, chunk_bytes, stage_bytes;
     int out_tma, res_tma;   // staged epilogue / residual brought in by TMA
     int out_tile_bytes;     // (OC / 64) * OUT_CHUNK_BYTES
+    // MMA groups of a tile (one per filter tap and 64-channel chunk, 4 MMAs each), in filter-slice order:
+    // a_off[g] = offset of the group's A operand inside a window, in 16-byte descriptor address units
+    int groups, lean_issue;
+    uint32_t a_off[kMaxGroups];
     const float *bias;
     const float *bn_scale, *bn_bias, *bn_mean, *bn_var;
     float bn_eps;
@@ -287,10 +294,19 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap tmIn, const __grid_constant__
         tc_fence_after();
         uint32_t it = 0, ph = 0;
         int st = 0;
-        // descriptors differ from window to window and from tap to tap only in the 14-bit address field
+        // Descriptors differ from window to window and from tap to tap only in the 14-bit address field, the low
+        // bits of the low word (no carry leaves the field: shared-memory addresses stay below 256 KiB).
+        // Two forms of the issue loop.  The tensor pipe finishes an N = 64 MMA every 48 cycles, and every
+        // instruction the issuing lane spends between two tcgen05.mma beyond that shows up in the tile time
+        // (measured: 90 cycles per MMA with the nested tap loops below, against 48 to 69 for bare loops in a
+        // stand-alone probe).  The lean form -- a table look-up and two 32-bit adds per group of four MMAs --
+        // issues the identical descriptor sequence; it is selected with SWCB200_CONV_LEAN_ISSUE=1 until it has
+        // been timed and checked on the hardware.
         const uint64_t da0 = smem_desc_sw128(smem_u32(s_a)), db0 = smem_desc_sw128(smem_u32(s_filter));
-        const uint64_t b_step = (uint64_t)((p.OC * 128) >> 4);
-        const uint64_t chunk_step = (uint64_t)(p.chunk_bytes >> 4), stage_step = (uint64_t)(p.stage_bytes >> 4);
+        const uint32_t desc_hi = (uint32_t)(da0 >> 32);  // same for A and B: stride 1024 B, version, 128-byte swizzle
+        const uint32_t a_lo0 = (uint32_t)da0, b_lo0 = (uint32_t)db0;
+        const uint32_t b_step = (uint32_t)((p.OC * 128) >> 4), stage_step = (uint32_t)(p.stage_bytes >> 4);
+        auto desc = [desc_hi](uint32_t lo) { return ((uint64_t)desc_hi << 32) | lo; };
         for (long long tile = blockIdx.x; tile < p.num_tiles && ok; tile += gridDim.x, it++) {
             const uint32_t buf = it % p.num_acc, aph = (it / p.num_acc) & 1;
             TIMING(const long long tm0 = clock64();)
@@ -302,23 +318,38 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap tmIn, const __grid_constant__
             if (!ok) break;
             tc_fence_after();
             const uint32_t d_tmem = tmem_base + buf * p.acc_stride;
-            const uint64_t da_stage = da0 + (uint64_t)st * stage_step;
-            uint64_t db = db0;
-            for (int kx = 0; kx < p.kh; kx++) {
-                for (int ky = 0; ky < p.kw; ky++) {
-                    // tap (kx, ky): the window read from (kx*64 + ky) pixels further on; one pixel = 128 B = 8 address units
-                    uint64_t da = da_stage + (uint64_t)((kx * ROW_PIX + ky) * 8);
-                    for (int kc = 0; kc < p.kchunks; kc++) {
-                        if (leader) {
-                            // advancing K by 16 elements = 32 bytes inside the swizzle row: +2 in the >>4 address field
-                            umma_bf16(d_tmem, da, db, idesc, (uint32_t)((kx | ky | kc) != 0));
-                            umma_bf16(d_tmem, da + 2, db + 2, idesc, 1u);
-                            umma_bf16(d_tmem, da + 4, db + 4, idesc, 1u);
-                            umma_bf16(d_tmem, da + 6, db + 6, idesc, 1u);
+            if (p.lean_issue) {
+                const uint32_t a_win = a_lo0 + (uint32_t)st * stage_step;
+                uint32_t b = b_lo0;
+                for (int g = 0; g < p.groups; g++, b += b_step) {
+                    // group g: tap (kx, ky) and channel chunk kc; its A operand is the window read from (kx*64 + ky)
+                    // pixels further on.  Advancing K by 16 elements = 32 bytes inside the swizzle row: +2 in the field.
+                    const uint32_t a = a_win + p.a_off[g];
+                    if (leader) {
+                        umma_bf16(d_tmem, desc(a), desc(b), idesc, (uint32_t)(g != 0));
+                        umma_bf16(d_tmem, desc(a + 2), desc(b + 2), idesc, 1u);
+                        umma_bf16(d_tmem, desc(a + 4), desc(b + 4), idesc, 1u);
+                        umma_bf16(d_tmem, desc(a + 6), desc(b + 6), idesc, 1u);
+                    }
+                }
+            } else {
+                // the same sequence from nested tap loops with 64-bit descriptor arithmetic
+                const uint64_t da_stage = da0 + (uint64_t)st * (uint64_t)stage_step;
+                uint64_t db = db0;
+                for (int kx = 0; kx < p.kh; kx++) {
+                    for (int ky = 0; ky < p.kw; ky++) {
+                        uint64_t da = da_stage + (uint64_t)((kx * ROW_PIX + ky) * 8);  // one pixel = 128 B = 8 address units
+                        for (int kc = 0; kc < p.kchunks; kc++) {
+                            if (leader) {
+                                umma_bf16(d_tmem, da, db, idesc, (uint32_t)((kx | ky | kc) != 0));
+                                umma_bf16(d_tmem, da + 2, db + 2, idesc, 1u);
+                                umma_bf16(d_tmem, da + 4, db + 4, idesc, 1u);
+                                umma_bf16(d_tmem, da + 6, db + 6, idesc, 1u);
+                            }
+                            __syncwarp();
+                            da += (uint64_t)(p.chunk_bytes >> 4);
+                            db += (uint64_t)b_step;
                         }
-                        __syncwarp();
-                        da += chunk_step;
-                        db += b_step;
                     }
                 }
             }
@@ -443,6 +474,16 @@ SWC_EXPORT int swcb200_debug_conv_timing(long long *out16) {
 }
 #endif
 
+// SWCB200_CONV_LEAN_ISSUE=1 in the environment selects the table-driven issue loop (see the kernel).
+static bool swc_conv_lean_issue() {
+    static int v = -1;
+    if (v < 0) {
+        const char *e = getenv("SWCB200_CONV_LEAN_ISSUE");
+        v = (e && e[0] == '1') ? 1 : 0;
+    }
+    return v == 1;
+}
+
 // input/filter bf16; output and residual bf16 or fp32
 int swc_conv_tc(swcb200_ctx *ctx, void *output, int out_dtype, const void *input, const void *filt, const float *bias,
                 const size_t *odims, const size_t *idims, const size_t *fdims, const size_t *kernels, const size_t *strides,
@@ -505,6 +546,13 @@ int swc_conv_tc(swcb200_ctx *ctx, void *output, int out_dtype, const void *input
     p.row_blocks = (p.OH + 1) / 2;
     p.col_blocks = (p.OW + p.cw - 1) / p.cw;
     p.num_tiles = (long long)p.N * p.row_blocks * p.col_blocks;
+    p.lean_issue = swc_conv_lean_issue();
+    p.groups = p.kh * p.kw * p.kchunks;  // <= kMaxGroups: the filter fits in kMaxFilterBytes and oC >= 32
+    SWC_REQUIRE(ctx, p.groups <= kMaxGroups, SWCB200_ERR_UNSUPPORTED, "conv2d_bf16: %d filter slices", p.groups);
+    for (int kx = 0, g = 0; kx < p.kh; kx++)
+        for (int ky = 0; ky < p.kw; ky++)
+            for (int kc = 0; kc < p.kchunks; kc++, g++)
+                p.a_off[g] = (uint32_t)(((kx * ROW_PIX + ky) * 128 + kc * p.chunk_bytes) >> 4);
 
     CUtensorMap tmIn, tmF, tmOut, tmRes;
     {
