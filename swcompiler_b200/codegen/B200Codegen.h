@@ -16,6 +16,15 @@
 // activations that only fused calls read are kept in bf16, and casts are printed only where an fp32
 // consumer (an unfused op, a displayed tensor) meets a bf16 producer or the other way round.
 //
+// Partitioned graphs (config.mpi with config.mpi_size ranks, after the reference's ParallelLabeling and
+// ParallelLowering passes): the program is printed once and run as one process per GPU.  Where the
+// reference's ParallelCodegen prints MPI text for the Scatter / Gather / Reduce / Transform nodes
+// (src/codegen/ParallelCodegen.cpp:457-896) this generator prints swcb200_scatter / _gather /
+// _reduce_sum / _transform (NCCL over NVLink).  Tensors the passes label "master" (device rank 0) live in
+// an arena only rank 0 allocates; tiles and replicas live in every rank's arena; an op whose tensors are
+// not on every rank is printed inside `if (rank == 0)`, as the reference does (:959-1006).  The ranks
+// find each other without MPI: rank and count come from the environment, the NCCL id through a file.
+//
 // This header needs the reference's headers on the include path (-I<reference>/src); it is compiled
 // only where a reference checkout is present (swcompiler_b200/codegen/build_codegen.py).
 #pragma once
@@ -26,6 +35,10 @@
 
 #include "common.h"
 #include "codegen/Codegen.h"
+
+namespace swc {
+class IRNode;
+}
 
 namespace swcb200 {
 
@@ -90,8 +103,20 @@ class B200Codegen : public swc::codegen::Codegen {
     // the fp32 storage a tensor is read from: its own, or, for a view in a fused plan, the viewed tensor's
     std::string f32Name(swc::Tensor *t) { return fuse_ ? nameOf(root(t)) : nameOf(t); }
 
+    // partitioned graphs
+    bool onEveryRank(swc::IRNode *tensor_node);
+    bool runsOnEveryRank(swc::OpNode *op);
+    bool isLoadTimeScatter(swc::OpNode *op);
+    bool isConstant(swc::IRNode *tensor_node);
+    void emitCommOp(swc::OpNode *op, std::ostream &os);
+    void emitGuarded(swc::OpNode *op, std::ostream &os);   // the op's call, inside `if (rank == 0)` where it must be
+
     int device_, precision_;
     bool fuse_;
+    bool parallel_ = false;
+    int nranks_ = 1;
+    size_t master_bytes_ = 0;
+    std::map<swc::Tensor *, bool> on_master_;
     std::vector<Group> groups_;
     std::map<swc::OpNode *, int> group_of_;          // op node -> index into groups_
     std::map<swc::Tensor *, swc::Tensor *> alias_;     // view -> viewed

@@ -22,6 +22,11 @@ BUILD = os.path.join(HERE, "build")
 EMITTED = os.path.join(HERE, "emitted")
 
 
+# the sample programs: <graph>[_dp<N> | _mp<N>][_fused], see gen_driver.cpp
+PROGRAMS = ("mlp8", "convnet", "resblock", "mlp8_fused", "convnet_fused", "resblock_fused",
+            "mlp8_dp2", "mlp8_dp2_fused", "fcpair_mp2")
+
+
 def reference_sources(ref: str):
     srcs = []
     for path in glob.glob(os.path.join(ref, "src", "**", "*.cpp"), recursive=True):
@@ -59,7 +64,7 @@ def build(ref: str = "/root/reference", quiet: bool = True) -> str:
 
 def emit(exe: str, out_dir: str = EMITTED):
     os.makedirs(out_dir, exist_ok=True)
-    for which in ("mlp8", "convnet", "mlp8_fused", "convnet_fused", "resblock", "resblock_fused"):
+    for which in PROGRAMS:
         # the generator also drops Graph.cpp / G_Makefile / SW_Makefile and *.dot in its working directory
         r = subprocess.run([exe, which, out_dir, "$(abspath ../../..)"], cwd=BUILD, capture_output=True, text=True)
         if r.returncode:

@@ -8,6 +8,13 @@
 //   gen_driver resblock <out_dir> <repo_root>  [2,8,8,64] -> Conv3x3 -> BN -> ReLU -> Conv3x3 -> BN -> Add(skip) -> ReLU ->
 //                                              MaxPool -> FC -> Softmax -> top-1: a residual block wide enough (64
 //                                              channels) for the tensor-core convolution
+//   gen_driver fcpair   <out_dir> <repo_root>  [64,256] -> FC 256->512 -> ReLU -> FC 512->128, no bias: the model-parallel
+//                                              pair (only meaningful with _mp<N>)
+//   A name with _dp<N> (mlp8_dp2) partitions the graph over N ranks by the batch: config.mpi, config.mpi_size = N,
+//   config.force_data_parallel, the reference's ParallelLabeling / ParallelLowering passes unchanged.
+//   A name with _mp<N> (fcpair_mp2) sets the model-parallel strategies by hand -- first FC split by output columns
+//   {-1,1,1}, ReLU {1,1}, second FC by input rows {1,0,-2} -- and runs ParallelLowering on them (the labeling pass
+//   draws strategies from std::random_device, so it is skipped for a reproducible program).
 //   A name with the suffix _fused (mlp8_fused, convnet_fused, resblock_fused) selects tensor-core precision and the
 //   emit-time fusion planner: one call per fused chain, bf16 activations between fused calls.
 //
@@ -19,6 +26,9 @@
 
 #include "B200Codegen.h"
 #include "SWC.h"
+#include "pass/EliminationPass.h"
+#include "pass/ParallelLoweringPass.h"
+#include "pass/RenamingNodePass.h"
 
 using namespace swc;
 using namespace swc::op;
@@ -105,6 +115,23 @@ IRGraph *build_convnet() {
     return g;
 }
 
+IRGraph *build_fcpair() {
+    auto *g = new IRGraph();
+    auto *x = tensor(g, "x", {64, 256}, "fp_x.bin");
+    auto *w1 = tensor(g, "w1", {256, 512}, "fp_w1.bin");
+    auto *fc1 = op(g, "fc1", new MatrixMatrixFCOp(), x, w1);
+    auto *h = result(g, "h", {64, 512}, fc1);
+    auto *relu = op(g, "relu", new ReluOp(), h);
+    auto *hr = result(g, "hr", {64, 512}, relu);
+    auto *w2 = tensor(g, "w2", {512, 128}, "fp_w2.bin");
+    auto *fc2 = op(g, "fc2", new MatrixMatrixFCOp(), hr, w2);
+    auto *y = result(g, "y", {64, 128}, fc2);
+    g->findInOut();
+    g->updateTopology();
+    g->addDisplayTensorNodes(y);
+    return g;
+}
+
 IRGraph *build_resblock() {
     auto *g = new IRGraph();
     std::vector<size_t> k3{3, 3}, s1{1, 1}, p1{1, 1, 1, 1}, k2{2, 2}, s2{2, 2}, p0{0, 0, 0, 0};
@@ -152,22 +179,63 @@ IRGraph *build_resblock() {
 
 int main(int argc, char **argv) {
     if (argc < 4) {
-        std::cerr << "usage: gen_driver mlp8|convnet|resblock[_fused] <out_dir> <repo_root>\n";
+        std::cerr << "usage: gen_driver mlp8|convnet|resblock|fcpair[_dp<N>|_mp<N>][_fused] <out_dir> <repo_root>\n";
         return 2;
     }
     const std::string which = argv[1], out_dir = argv[2], repo = argv[3];
+    // name = <graph>[_dp<N> | _mp<N>][_fused]
+    std::string base = which;
     const std::string suffix = "_fused";
-    const bool fused = which.size() > suffix.size() && which.compare(which.size() - suffix.size(), suffix.size(), suffix) == 0;
-    const std::string base = fused ? which.substr(0, which.size() - suffix.size()) : which;
-    IRGraph *g = base == "mlp8" ? build_mlp8() : (base == "convnet" ? build_convnet() : (base == "resblock" ? build_resblock() : nullptr));
+    const bool fused = base.size() > suffix.size() && base.compare(base.size() - suffix.size(), suffix.size(), suffix) == 0;
+    if (fused) base = base.substr(0, base.size() - suffix.size());
+    int ranks = 1;
+    bool model_parallel = false;
+    for (const char *tag : {"_dp", "_mp"}) {
+        const size_t at = base.rfind(tag);
+        if (at != std::string::npos && at + 3 < base.size() && isdigit(base[at + 3])) {
+            ranks = atoi(base.c_str() + at + 3);
+            model_parallel = std::string(tag) == "_mp";
+            base = base.substr(0, at);
+        }
+    }
+    IRGraph *g = base == "mlp8" ? build_mlp8()
+                 : base == "convnet" ? build_convnet()
+                 : base == "resblock" ? build_resblock()
+                 : base == "fcpair" ? build_fcpair() : nullptr;
     if (!g) {
         std::cerr << "unknown graph " << base << "\n";
         return 2;
     }
     Config config;  // inference, one device, no MPI: the defaults
+    if (ranks > 1) {
+        config.mpi = true;
+        config.mpi_size = ranks;
+        config.force_data_parallel = !model_parallel;
+    }
     g->setConfig(config);
     Engine engine(g);
-    engine.compile();  // the reference's own passes: labeling, FC lowering, renaming
+    if (!model_parallel) {
+        engine.compile();  // the reference's own passes: labeling, FC lowering, renaming (+ the parallel passes)
+    } else {
+        engine.runInferPasses();
+        g->resetParallelStrategy();
+        auto label = [&](const char *name, std::vector<int> strategy) {
+            auto *n = dynamic_cast<OpNode *>(g->getNodeByName(name));
+            if (!n) {
+                std::cerr << "no op node " << name << "\n";
+                exit(2);
+            }
+            n->setStrategyLabel(new StrategyLabel(strategy));
+        };
+        label("fc1_mm", {-1, 1, 1});
+        label("relu", {1, 1});
+        label("fc2_mm", {1, 0, -2});
+        pass::ParallelLoweringPass(g).run();
+        pass::RenamingNodePass(g).run();
+        pass::EliminationPass(g).run();
+        g->findInOut();
+        g->updateTopology();
+    }
     swcb200::B200Codegen gen(g, config, /*device=*/0, /*precision=*/fused ? 1 : 0, /*fuse=*/fused);
     engine.setCodegenerator(&gen);
     const std::string code = engine.genCode();

@@ -68,7 +68,45 @@ def test_fused_convnet_falls_back_per_op_where_the_kernel_cannot_take_the_shape(
                                        "maxpool_f", "cast_f32_to_bf16", "fc_bf16", "matrixSoftmax_f", "argMax_i", "sync", "destroy"]
 
 
-ALL_PROGRAMS = ["mlp8", "convnet", "resblock", "mlp8_fused", "convnet_fused", "resblock_fused"]
+def test_data_parallel_mlp8_scatters_gathers_and_guards_the_master():
+    """config.mpi, mpi_size 2, force_data_parallel through the reference's own tiling passes: inputs are scattered
+    (batch split) or broadcast (weights) once after loading, every rank runs the forward pass on its tile, the results
+    are gathered on rank 0, which alone holds the un-partitioned tensors and prints."""
+    calls = _calls("mlp8_dp2")
+    assert calls == ["init", "comm_load", "comm_init"] + ["scatter"] * 5 + ["matrixMatrixMul_f", "batchedadd_f", "matrixTanh_f",
+                                                                 "matrixMatrixMul_f", "batchedadd_f", "matrixSoftmax_f", "argMax_i",
+                                                                 "gather", "gather", "sync", "comm_destroy", "destroy"]
+    text = open(os.path.join(EMITTED, "mlp8_dp2_Graph.cpp")).read()
+    assert "swcb200_scatter(ctx, data0, data0_tile, data0_fork_dims_0, 2, 0, SWCB200_F32, 0)" in text       # batch split
+    assert "swcb200_scatter(ctx, weight0, weight0_replicate, weight0_fork_dims_1, 2, -1, SWCB200_F32, 0)" in text   # replicate
+    assert "swcb200_matrixMatrixMul_f(ctx, 4, 512, 784, data0_tile" in text                                  # 8 rows / 2 ranks
+    assert "top3_join_dims_6, 2, 0, SWCB200_I32, 0)" in text
+    assert "data0 = rank == 0 ? reinterpret_cast<float *>(gpu_master + 0) : nullptr;" in text
+    assert "MPI_Send" not in text and "MPI_Init" not in text and "mpi.h" not in text
+    # with the planner: the replicated weights are packed after the load-time scatters, the tile is cast once
+    assert _calls("mlp8_dp2_fused") == ["init", "comm_load", "comm_init"] + ["scatter"] * 5 + ["pack_weight_bf16"] * 2 + [
+        "cast_f32_to_bf16", "fc_bf16", "fc_bf16", "matrixSoftmax_f", "argMax_i", "gather", "gather", "sync", "comm_destroy",
+        "destroy"]
+
+
+def test_model_parallel_fc_pair_is_column_split_row_split_and_a_reduce():
+    """Strategies {-1,1,1}, {1,1}, {1,0,-2} lowered by the reference's ParallelLoweringPass: X replicated, W1 split by
+    columns, W2 by rows, the hidden activation never leaves its rank, and the one collective of the forward pass is
+    the Reduce of the partial outputs (MPI_Reduce in the reference, NCCL here)."""
+    assert _calls("fcpair_mp2") == ["init", "comm_load", "comm_init", "scatter", "scatter", "scatter", "matrixMatrixMul_f", "relu_f",
+                                    "matrixMatrixMul_f", "reduce_sum", "sync", "comm_destroy", "destroy"]
+    text = open(os.path.join(EMITTED, "fcpair_mp2_Graph.cpp")).read()
+    assert "swcb200_scatter(ctx, x, x_replicate, x_fork_dims_0, 2, -1, SWCB200_F32, 0)" in text
+    assert "swcb200_scatter(ctx, w1, w1_tile, w1_fork_dims_1, 2, 1, SWCB200_F32, 0)" in text
+    assert "swcb200_scatter(ctx, w2, w2_tile, w2_fork_dims_2, 2, 0, SWCB200_F32, 0)" in text
+    assert "swcb200_matrixMatrixMul_f(ctx, 64, 256, 256, x_replicate, 256, w1_tile, 256, h_tile, 256)" in text
+    assert "swcb200_matrixMatrixMul_f(ctx, 64, 128, 256, hr_tile, 256, w2_tile, 128, y_reduce, 128)" in text
+    assert "swcb200_reduce_sum(ctx, y_reduce, y, 8192, SWCB200_F32, 0)" in text
+    mk = open(os.path.join(EMITTED, "fcpair_mp2_Makefile")).read()
+    assert "for r in 0 1; do SWCB200_RANK=$$r SWCB200_NRANKS=2" in mk
+
+
+from swcompiler_b200.codegen.build_codegen import PROGRAMS as ALL_PROGRAMS  # noqa: E402
 
 
 @pytest.mark.parametrize("which", ALL_PROGRAMS)
@@ -76,7 +114,9 @@ def test_emitted_programs_compile_and_link(which, tmp_path):
     exe = compile_emitted(which, str(tmp_path))
     import torch
     if not torch.cuda.is_available():
-        r = subprocess.run([exe], capture_output=True, text=True, cwd=str(tmp_path))
+        ranks = 2 if ("_dp2" in which or "_mp2" in which) else 1
+        env = dict(os.environ, SWCB200_RANK="0", SWCB200_NRANKS=str(ranks), SWCB200_ID_FILE=os.path.join(str(tmp_path), "id"))
+        r = subprocess.run([exe], capture_output=True, text=True, cwd=str(tmp_path), env=env)
         assert r.returncode != 0 and "no sm_100 CUDA device" in r.stderr   # fails loudly, no CPU path
 
 
@@ -85,5 +125,5 @@ def test_committed_programs_are_what_the_generator_emits(tmp_path):
     from swcompiler_b200.codegen import build_codegen as bc
     exe = bc.build(REF)
     out = bc.emit(exe, str(tmp_path))
-    for f in [w + "_Graph.cpp" for w in ALL_PROGRAMS] + ["mlp8_Makefile"]:
+    for f in [w + "_Graph.cpp" for w in ALL_PROGRAMS] + ["mlp8_Makefile", "fcpair_mp2_Makefile"]:
         assert open(os.path.join(out, f)).read() == open(os.path.join(EMITTED, f)).read(), f
