@@ -12,8 +12,9 @@
 //                                              pair (only meaningful with _mp<N>)
 //   A name with _dp<N> (mlp8_dp2) partitions the graph over N ranks by the batch: config.mpi, config.mpi_size = N,
 //   config.force_data_parallel, the reference's ParallelLabeling / ParallelLowering passes unchanged.
-//   A name with _mp<N> (fcpair_mp2) sets the model-parallel strategies by hand -- first FC split by output columns
-//   {-1,1,1}, ReLU {1,1}, second FC by input rows {1,0,-2} -- and runs ParallelLowering on them (the labeling pass
+//   A name with _mp<N> (fcpair_mp2, mlp8_mp2) sets the model-parallel strategies by hand -- first FC split by output
+//   columns {-1,1,1}, the activation on column tiles {1,1}, second FC by input rows {1,0,-2}; for the MLP the bias-adds
+//   on row tiles, which makes the passes insert Transform nodes -- and runs ParallelLowering on them (the labeling pass
 //   draws strategies from std::random_device, so it is skipped for a reproducible program).
 //   A name with the suffix _fused (mlp8_fused, convnet_fused, resblock_fused) selects tensor-core precision and the
 //   emit-time fusion planner: one call per fused chain, bf16 activations between fused calls.
@@ -227,9 +228,24 @@ int main(int argc, char **argv) {
             }
             n->setStrategyLabel(new StrategyLabel(strategy));
         };
-        label("fc1_mm", {-1, 1, 1});
-        label("relu", {1, 1});
-        label("fc2_mm", {1, 0, -2});
+        if (base == "fcpair") {
+            label("fc1_mm", {-1, 1, 1});
+            label("relu", {1, 1});
+            label("fc2_mm", {1, 0, -2});
+        } else if (base == "mlp8") {
+            // column-split first FC, bias-add on row tiles (a 1 -> 0 re-tiling), tanh on column tiles (0 -> 1),
+            // row-split second FC (partial sums, Reduce), the rest on row tiles
+            label("fc0_mm", {-1, 1, 1});
+            label("fc0_add", {0, -1, 0});
+            label("tanh0", {1, 1});
+            label("fc1_mm", {1, 0, -2});
+            label("fc1_add", {0, -1, 0});
+            label("softmax", {0, 0});
+            label("argmax", {0, 0});
+        } else {
+            std::cerr << "no model-parallel strategies written down for " << base << "\n";
+            return 2;
+        }
         pass::ParallelLoweringPass(g).run();
         pass::RenamingNodePass(g).run();
         pass::EliminationPass(g).run();

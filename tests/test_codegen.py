@@ -106,6 +106,17 @@ def test_model_parallel_fc_pair_is_column_split_row_split_and_a_reduce():
     assert "for r in 0 1; do SWCB200_RANK=$$r SWCB200_NRANKS=2" in mk
 
 
+def test_model_parallel_mlp8_retiles_between_ops_that_disagree():
+    """Column-split FC, bias-add on row tiles, tanh on column tiles, row-split FC: the lowering pass inserts Transform
+    nodes (1 -> 0 and 0 -> 1), a Reduce to the master and a Scatter back out; all four kinds of communication node."""
+    assert _calls("mlp8_mp2")[3:-3] == ["scatter"] * 5 + ["matrixMatrixMul_f", "transform", "batchedadd_f", "transform",
+                                                          "matrixTanh_f", "matrixMatrixMul_f", "reduce_sum", "scatter",
+                                                          "batchedadd_f", "matrixSoftmax_f", "argMax_i", "gather", "gather"]
+    text = open(os.path.join(EMITTED, "mlp8_mp2_Graph.cpp")).read()
+    assert "fc0_mm_out_transform_dims_5[] = {8, 512};" in text and "fc0_mm_out_transform_dims_5, 2, 1, 0, SWCB200_F32)" in text
+    assert "data1_transform_dims_6[] = {8, 512};" in text and "data1_transform_dims_6, 2, 0, 1, SWCB200_F32)" in text
+
+
 from swcompiler_b200.codegen.build_codegen import PROGRAMS as ALL_PROGRAMS  # noqa: E402
 
 

@@ -74,6 +74,13 @@ def test_data_parallel_fused_mlp8_on_two_ranks(tmp_path, golden):
     assert np.abs(got["data4"] - golden["mnist8/probs"]).max() <= 2e-2
 
 
+def test_model_parallel_mlp8_on_two_ranks(tmp_path, golden):
+    """Transform (1 -> 0, 0 -> 1), Reduce, Scatter and Gather nodes in one forward pass."""
+    got = _run_ranks("mlp8_mp2", tmp_path, _mnist8_files(), 2)
+    assert got["top3"][:, 0].astype(int).tolist() == [5, 0, 4, 1, 9, 2, 1, 3]
+    assert np.allclose(got["data4"], golden["mnist8/probs"], atol=6e-4)     # the second FC sums two partial products
+
+
 def test_model_parallel_fc_pair_on_two_ranks(tmp_path, oracle):
     """FC1 split by output columns, ReLU on the column shards, FC2 split by input rows, partial sums joined by Reduce."""
     r = np.random.default_rng(404)
