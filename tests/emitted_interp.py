@@ -1,0 +1,204 @@
+"""Test infrastructure: runs the call sequence of a program B200Codegen emitted, on the CPU.
+
+The emitted C++ is read as text: the `const size_t name[] = {...}` shape arrays, the `load_to_device` lines and the
+`SWC_CHECK(swcb200_*(ctx, ...))` calls of main(), in order, with `if (rank == 0) { ... }` blocks honoured.  Every
+table call is carried out by the CPU oracle on numpy arrays (bf16 entry points: operands rounded to bf16, fp32
+accumulation), and the communication calls by `swcompiler_b200.parallel.TorchComm` over gloo when there is more than
+one rank.  What this checks is the GENERATOR: call order, operand names, shapes, leading dimensions, axes, guards,
+the storage plan of the fusion planner.  It says nothing about the CUDA kernels, which the GPU tests cover.
+"""
+import os
+import re
+
+import numpy as np
+
+import cases
+
+_CALL = re.compile(r"SWC_CHECK\(swcb200_(\w+)\((.*)\)\);")
+_DIMS = re.compile(r"const size_t (\w+)\[\] = \{([^}]*)\};")
+_LOAD = re.compile(r"load_to_device<(\w+)>\((\w+), (\d+), (\d+), \"([^\"]+)\", host_stage\);")
+_PRINT = re.compile(r"print_device<(\w+)>\(\"(\w+)\", (\w+), (\d+), (\d+), host_stage\);")
+_ALIAS = re.compile(r"^(\w+) = (\w+);$")   # a view (Reshape): the child names the parent's storage
+_EPI = re.compile(r"const swcb200_conv_epilogue (\w+) = \{([^}]*)\};")
+
+
+def _tanh(x):
+    return (1.0 - 2.0 / (np.exp(2.0 * x.astype(np.float64)) + 1.0)).astype(np.float32)
+
+
+class Interp:
+    def __init__(self, oracle, files_dir, rank=0, nranks=1, comm=None):
+        self.o, self.dir, self.rank, self.nranks, self.comm = oracle, files_dir, rank, nranks, comm
+        self.t, self.dims, self.epi, self.printed, self.calls = {}, {}, {}, {}, []
+
+    # ---- helpers
+    def _get(self, name):
+        name = name.strip().lstrip("&")
+        if name in ("nullptr", "NULL"):
+            return None
+        return self.t.get(name)   # a master-only tensor off the master: None
+
+    def _int(self, s):
+        return int(s.strip().rstrip("f"))
+
+    def run(self, path):
+        text = open(path).read()
+        body = text[text.index("int main("):]
+        guarded = False
+        for raw in body.splitlines():
+            line = raw.strip()
+            if line == "if (rank == 0) {":
+                guarded = True
+                continue
+            if line == "}" and guarded:
+                guarded = False
+                continue
+            if guarded and self.rank != 0:
+                continue
+            m = _DIMS.search(line)
+            if m:
+                self.dims[m.group(1)] = tuple(int(v) for v in m.group(2).split(","))
+                continue
+            m = _EPI.search(line)
+            if m:
+                self.epi[m.group(1)] = [v.strip() for v in m.group(2).split(",")]
+                continue
+            m = _LOAD.search(line)
+            if m:
+                dt = np.float32 if m.group(1) == "float" else np.int32
+                a = np.fromfile(os.path.join(self.dir, m.group(5)), dtype=dt)
+                self.t[m.group(2)] = a[int(m.group(4)):int(m.group(4)) + int(m.group(3))].copy()
+                continue
+            m = _PRINT.search(line)
+            if m:
+                self.printed[m.group(2)] = self.t[m.group(3)].reshape(int(m.group(4)), int(m.group(5)))
+                continue
+            m = _ALIAS.match(line)
+            if m and m.group(2) in self.t:
+                self.t[m.group(1)] = self.t[m.group(2)]
+                continue
+            m = _CALL.search(line)
+            if m:
+                args = [a.strip() for a in m.group(2).split(",")][1:]   # drop ctx
+                self.calls.append(m.group(1))
+                getattr(self, "op_" + m.group(1), self._ignore)(*args)
+        return self.printed
+
+    def _ignore(self, *a):
+        pass
+
+    # ---- fp32 table
+    def op_matrixMatrixMul_f(self, m, n, k, a, lda, b, ldb, c, ldc):
+        m, n, k = int(m), int(n), int(k)
+        assert int(lda) == k and int(ldb) == n and int(ldc) == n
+        self.t[c] = self.o.matrixMatrixMul_f(self._get(a).reshape(m, k), self._get(b).reshape(k, n)).reshape(-1)
+
+    def op_batchedadd_f(self, dest, batch, sl, rows, cols):
+        self.t[dest] = self.o.batchedadd_f(self._get(batch).reshape(int(rows), int(cols)), self._get(sl)).reshape(-1)
+
+    def op_matrixTanh_f(self, m, n, a, lda, b, ldb):
+        self.t[b] = self.o.matrixTanh_f(self._get(a).reshape(int(m), int(n))).reshape(-1)
+
+    def op_matrixSoftmax_f(self, m, n, a, lda, b, ldb):
+        self.t[b] = self.o.matrixSoftmax_f(self._get(a).reshape(int(m), int(n))).reshape(-1)
+
+    def op_argMax_i(self, a, idx, m, n, k):
+        self.t[idx] = self.o.argMax_i(self._get(a).reshape(int(m), int(n)), int(k)).reshape(-1).astype(np.int32)
+
+    def op_relu_f(self, src, dst, size):
+        self.t[dst] = self.o.relu_f(self._get(src)[:int(size)])
+
+    def op_vecAdd_f(self, size, a, b, c):
+        self.t[c] = self.o.vecAdd_f(self._get(a)[:int(size)], self._get(b)[:int(size)])
+
+    def op_conv2d_f(self, out, x, f, b, od, idm, fd, bd, kd, sd, pd, group):
+        y = self.o.conv2d_f(self._get(x).reshape(self.dims[idm]), self._get(f).reshape(self.dims[fd]), self._get(b),
+                            self.dims[kd], self.dims[sd], self.dims[pd])
+        assert y.shape == self.dims[od]
+        self.t[out] = y.reshape(-1)
+
+    def op_batchnormalization_f(self, out, x, mean, var, scale, bias, idm, eps):
+        self.t[out] = self.o.batchnormalization_f(self._get(x).reshape(self.dims[idm]), self._get(mean), self._get(var),
+                                                  self._get(scale), self._get(bias), float(eps.rstrip("f"))).reshape(-1)
+
+    def op_maxpool_f(self, x, out, idm, od, kd, sd, pd):
+        y = self.o.maxpool_f(self._get(x).reshape(self.dims[idm]), self.dims[kd], self.dims[sd], self.dims[pd])
+        assert y.shape == self.dims[od]
+        self.t[out] = y.reshape(-1)
+
+    # ---- bf16 storage entry points: bf16-rounded operands, fp32 arithmetic
+    def op_cast_f32_to_bf16(self, src, dst, count):
+        self.t[dst] = cases.bf16_round(self._get(src)[:int(count)])
+
+    def op_cast_bf16_to_f32(self, src, dst, count):
+        self.t[dst] = self._get(src)[:int(count)].copy()
+
+    def op_pack_weight_bf16(self, w, k, n, ldb, wp):
+        assert int(ldb) == int(n)
+        self.t[wp] = np.ascontiguousarray(cases.bf16_round(self._get(w).reshape(int(k), int(n))).T).reshape(-1)   # [n, k]
+
+    def op_pack_filter_bf16(self, f, fd, fp):
+        self.t[fp] = cases.bf16_round(self._get(f))
+
+    def op_fc_bf16(self, m, n, k, a, lda, wp, ldw, bias, act, c, c_dtype, ldc):
+        m, n, k = int(m), int(n), int(k)
+        assert int(lda) == k and int(ldw) == k and int(ldc) == n
+        y = self.o.matrixMatrixMul_f(self._get(a).reshape(m, k), np.ascontiguousarray(self._get(wp).reshape(n, k).T))
+        if self._get(bias) is not None:
+            y = self.o.batchedadd_f(y, self._get(bias))
+        y = {"SWCB200_ACT_NONE": lambda v: v, "SWCB200_ACT_RELU": lambda v: np.maximum(v, 0), "SWCB200_ACT_TANH": _tanh}[act](y)
+        self.t[c] = (cases.bf16_round(y) if c_dtype == "SWCB200_BF16" else y).reshape(-1)
+
+    def op_conv2d_bf16(self, out, x, fp, b, od, idm, fd, kd, sd, pd, ep):
+        y = self.o.conv2d_f(self._get(x).reshape(self.dims[idm]), self._get(fp).reshape(self.dims[fd]), self._get(b),
+                            self.dims[kd], self.dims[sd], self.dims[pd])
+        scale, bias, mean, var, eps, res, relu = self.epi[ep.lstrip("&")]
+        if scale != "nullptr":
+            y = self.o.batchnormalization_f(y, self._get(mean), self._get(var), self._get(scale), self._get(bias),
+                                            float(eps.rstrip("f")))
+        if res != "nullptr":
+            y = y + self._get(res).reshape(y.shape)
+        if int(relu):
+            y = np.maximum(y, 0)
+        assert y.shape == self.dims[od]
+        self.t[out] = cases.bf16_round(y.astype(np.float32)).reshape(-1)
+
+    def op_maxpool_bf16(self, x, out, idm, od, kd, sd, pd):
+        self.op_maxpool_f(x, out, idm, od, kd, sd, pd)
+
+    # ---- communication
+    def _torch(self, a, dtype):
+        import torch
+        return None if a is None else torch.from_numpy(np.ascontiguousarray(a)).to(dtype)
+
+    def _dt(self, name):
+        import torch
+        return torch.int32 if name == "SWCB200_I32" else torch.float32
+
+    def op_scatter(self, src, dst, dims, ndim, axis, dt, root):
+        d = self.dims[dims]
+        assert len(d) == int(ndim) and int(root) == 0
+        full = self._get(src)
+        assert (full is not None) == (self.rank == 0)
+        full = None if full is None else self._torch(full.reshape(d), self._dt(dt))
+        self.t[dst] = self.comm.scatter(full, d, int(axis), dtype=self._dt(dt)).numpy().reshape(-1)
+
+    def op_gather(self, src, dst, dims, ndim, axis, dt, root):
+        d = self.dims[dims]
+        from swcompiler_b200.parallel import shard_dims
+        local = self._torch(self._get(src).reshape(shard_dims(d, int(axis), self.nranks)), self._dt(dt))
+        out = self.comm.gather(local, d, int(axis))
+        if self.rank == 0:
+            self.t[dst] = out.numpy().reshape(-1)
+
+    def op_reduce_sum(self, src, dst, count, dt, root):
+        out = self.comm.reduce_sum(self._torch(self._get(src)[:int(count)], self._dt(dt)))
+        if self.rank == 0:
+            self.t[dst] = out.numpy()
+
+    def op_transform(self, src, dst, dims, ndim, pre, post, dt):
+        d = self.dims[dims]
+        from swcompiler_b200.parallel import shard_dims
+        pre, post = int(pre), int(post)
+        shape = d if pre < 0 else shard_dims(d, pre, self.nranks)
+        self.t[dst] = self.comm.transform(self._torch(self._get(src).reshape(shape), self._dt(dt)), d, pre, post).numpy().reshape(-1)

@@ -117,6 +117,39 @@ def test_model_parallel_mlp8_retiles_between_ops_that_disagree():
     assert "data1_transform_dims_6[] = {8, 512};" in text and "data1_transform_dims_6, 2, 0, 1, SWCB200_F32)" in text
 
 
+def _interpret(which, files, oracle, tmp_path):
+    from emitted_interp import Interp
+    for name, arr in files.items():
+        arr.tofile(os.path.join(tmp_path, name))
+    it = Interp(oracle, str(tmp_path))
+    return it.run(os.path.join(EMITTED, which + "_Graph.cpp"))
+
+
+def test_emitted_call_sequences_compute_the_right_thing_on_the_cpu(oracle, golden, tmp_path):
+    """The emitted programs' calls, carried out one by one by the CPU oracle (tests/emitted_interp.py): operand names,
+    shapes, leading dimensions, the fusion planner's storage plan and casts.  (The CUDA kernels are the GPU tests' job.)"""
+    import numpy as np
+
+    import cases
+    from codegen_util import convnet_inputs, convnet_oracle, resblock_inputs, resblock_oracle
+    from conftest import GOLDEN, bits
+    d = os.path.join(GOLDEN, "mnist8")
+    mnist = {f: np.fromfile(os.path.join(d, f), dtype=np.uint8) for f in os.listdir(d)}
+    got = _interpret("mlp8", mnist, oracle, tmp_path)
+    assert np.array_equal(bits(got["data4"]), bits(golden["mnist8/probs"])) and np.array_equal(got["top3"], golden["mnist8/top3"])
+    got = _interpret("mlp8_fused", mnist, oracle, tmp_path)
+    assert got["top3"][:, 0].tolist() == [5, 0, 4, 1, 9, 2, 1, 3] and np.abs(got["data4"] - golden["mnist8/probs"]).max() <= 2e-2
+    t = convnet_inputs()
+    want = convnet_oracle(oracle, t)
+    assert np.array_equal(bits(_interpret("convnet", t, oracle, tmp_path)["probs"]), bits(want))
+    assert np.abs(_interpret("convnet_fused", t, oracle, tmp_path)["probs"] - want).max() <= 2e-2
+    t = resblock_inputs()
+    assert np.array_equal(bits(_interpret("resblock", t, oracle, tmp_path)["probs"]), bits(resblock_oracle(oracle, t)))
+    fused = _interpret("resblock_fused", t, oracle, tmp_path)["probs"]
+    assert np.abs(fused - resblock_oracle(oracle, t, rnd=cases.bf16_round)).max() <= 1e-3   # same rounding points
+    assert np.abs(fused - resblock_oracle(oracle, t)).max() <= 5e-2
+
+
 from swcompiler_b200.codegen.build_codegen import PROGRAMS as ALL_PROGRAMS  # noqa: E402
 
 

@@ -104,7 +104,44 @@ def _batch_split(rank, world):
         assert torch.equal(y, torch.softmax(x @ w, dim=1))
 
 
-@pytest.mark.parametrize("fn", [_scatter_gather, _transform, _fc_pair, _batch_split])
+def _emitted_programs(rank, world):
+    """The partitioned programs B200Codegen emitted, call by call (tests/emitted_interp.py): compute by the CPU oracle,
+    Scatter / Gather / Reduce / Transform by TorchComm over gloo, one interpreter per rank.  Checks the generator's
+    reading of the reference's tiling labels -- axes, tile shapes, master-only guards, load-time scatters."""
+    import sys
+    here = os.path.dirname(os.path.abspath(__file__))
+    sys.path[:0] = [os.path.dirname(here), here]
+    import tempfile
+
+    from codegen_util import EMITTED
+    from emitted_interp import Interp
+    from oracle import oracle as orc
+    o = orc.Oracle()
+    o.set_threads(1)
+    golden = np.load(os.path.join(here, "golden", "ref_outputs.npz"))
+    mnist = os.path.join(here, "golden", "mnist8")
+    comm = par.TorchComm()
+    for which, tol in (("mlp8_dp2", 0.0), ("mlp8_mp2", 1e-6), ("mlp8_dp2_fused", 2e-2)):
+        out = Interp(o, mnist, rank, world, comm).run(os.path.join(EMITTED, which + "_Graph.cpp"))
+        if rank == 0:
+            assert out["top3"][:, 0].tolist() == [5, 0, 4, 1, 9, 2, 1, 3], which
+            assert np.abs(out["data4"] - golden["mnist8__probs"]).max() <= tol, which
+        else:
+            assert out == {}, which   # only the master prints
+    r = np.random.default_rng(404)
+    x = r.standard_normal((64, 256)).astype(np.float32)
+    w1 = (r.standard_normal((256, 512)) / 16).astype(np.float32)
+    w2 = (r.standard_normal((512, 128)) / 22.6).astype(np.float32)
+    with tempfile.TemporaryDirectory() as d:
+        for name, arr in (("fp_x.bin", x), ("fp_w1.bin", w1), ("fp_w2.bin", w2)):
+            arr.tofile(os.path.join(d, name))
+        out = Interp(o, d, rank, world, comm).run(os.path.join(EMITTED, "fcpair_mp2_Graph.cpp"))
+    if rank == 0:
+        want = o.matrixMatrixMul_f(o.relu_f(o.matrixMatrixMul_f(x, w1)), w2)
+        assert np.allclose(out["y"], want, rtol=1e-5, atol=1e-5)
+
+
+@pytest.mark.parametrize("fn", [_scatter_gather, _transform, _fc_pair, _batch_split, _emitted_programs])
 def test_two_ranks_gloo(fn):
     run_ranks(fn, 2)
 
