@@ -106,6 +106,19 @@ def test_model_parallel_fc_pair_is_column_split_row_split_and_a_reduce():
     assert "for r in 0 1; do SWCB200_RANK=$$r SWCB200_NRANKS=2" in mk
 
 
+def test_batch_split_residual_block_runs_untiled_ops_on_the_master():
+    """BatchNormalization and ElementAdd have no tiling descriptor in the reference (src/op/dlOp/dlOp.h:747-761, :347-355):
+    its passes bracket them with Gather and Scatter and the generator prints them inside `if (rank == 0)`."""
+    text = open(os.path.join(EMITTED, "resblock_dp2_Graph.cpp")).read()
+    body = text[text.index("int main("):]
+    guarded = [l.strip() for blk in body.split("if (rank == 0) {")[1:] for l in blk.split("\n    }")[0].splitlines()]
+    assert sum("swcb200_batchnormalization_f(" in l for l in guarded) == 2 and sum("swcb200_vecAdd_f(" in l for l in guarded) == 1
+    calls = _calls("resblock_dp2")
+    i = calls.index("batchnormalization_f")
+    assert calls[i - 1] == "gather" and calls[i + 1] == "scatter"
+    assert calls.count("conv2d_f") == 2 and "swcb200_conv2d_f(ctx, conv0_out_tile, image_tile" in text   # convolutions on tiles
+
+
 def test_model_parallel_mlp8_retiles_between_ops_that_disagree():
     """Column-split FC, bias-add on row tiles, tanh on column tiles, row-split FC: the lowering pass inserts Transform
     nodes (1 -> 0 and 0 -> 1), a Reduce to the master and a Scatter back out; all four kinds of communication node."""

@@ -139,6 +139,16 @@ def _emitted_programs(rank, world):
     if rank == 0:
         want = o.matrixMatrixMul_f(o.relu_f(o.matrixMatrixMul_f(x, w1)), w2)
         assert np.allclose(out["y"], want, rtol=1e-5, atol=1e-5)
+    # batch-split residual block: BatchNormalization and ElementAdd carry no tiling descriptor in the reference, so its
+    # passes gather their inputs to the master, run them there (printed inside `if (rank == 0)`) and scatter again
+    from codegen_util import resblock_inputs, resblock_oracle
+    t = resblock_inputs()
+    with tempfile.TemporaryDirectory() as d:
+        for name, arr in t.items():
+            arr.tofile(os.path.join(d, name))
+        out = Interp(o, d, rank, world, comm).run(os.path.join(EMITTED, "resblock_dp2_Graph.cpp"))
+    if rank == 0:
+        assert np.array_equal(out["probs"], resblock_oracle(o, t))      # every op is per-sample: bit for bit
 
 
 @pytest.mark.parametrize("fn", [_scatter_gather, _transform, _fc_pair, _batch_split, _emitted_programs])
