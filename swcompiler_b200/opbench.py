@@ -39,6 +39,42 @@ def _time(fn, iters):
     return e0.elapsed_time(e1) / iters * 1e-3
 
 
+def latency(iters):
+    """The two configurations that are bound by launch latency, not by any roofline (52 and 182 MFLOP per forward):
+    X[64,784] -> FC 784->512 -> Tanh -> FC 512->10 -> Softmax, and [32,28,28,1] -> Conv5x5 1->16 -> ReLU -> MaxPool ->
+    Conv5x5 16->32 -> ReLU -> MaxPool -> FC 1568->10 -> Softmax.  One table call per op node, strict fp32 kernels and
+    the tensor-core mode of the same entry points; microseconds per forward pass and samples per second."""
+    dev = torch.device("cuda", 0)
+    g = torch.Generator(device=dev).manual_seed(1001)
+    rn = lambda *shape, s=1.0: torch.randn(shape, generator=g, device=dev) * s
+    x1, w0, b0, w1, b1 = torch.rand((64, 784), generator=g, device=dev), rn(784, 512, s=0.05), torch.zeros(512, device=dev), \
+        rn(512, 10, s=0.05), torch.zeros(10, device=dev)
+    x2 = torch.rand((32, 28, 28, 1), generator=g, device=dev)
+    cw0, cb0 = rn(16, 5, 5, 1, s=(2 / 25) ** 0.5), torch.zeros(16, device=dev)
+    cw1, cb1 = rn(32, 5, 5, 16, s=(2 / 400) ** 0.5), torch.zeros(32, device=dev)
+    fw, fb = rn(1568, 10, s=0.02), torch.zeros(10, device=dev)
+    k5, s1, p2, k2, s2, p0 = (5, 5), (1, 1), (2, 2, 2, 2), (2, 2), (2, 2), (0, 0, 0, 0)
+    for mode, name in ((swc.STRICT_F32, "strict fp32"), (swc.TC_BF16, "tensor-core mode")):
+        be = swc.Backend(0, mode)
+
+        def mlp():
+            return be.mlp_forward(x1, w0, b0, w1, b1)
+
+        def lenet():
+            h = be.maxpool_f(be.relu_f(be.conv2d_f(x2, cw0, cb0, k5, s1, p2)), k2, s2, p0)
+            h = be.maxpool_f(be.relu_f(be.conv2d_f(h, cw1, cb1, k5, s1, p2)), k2, s2, p0)
+            return be.matrixSoftmax_f(be.fc(h, fw, fb))
+
+        for label, fn, batch in (("MLP 784-512-10, batch 64", mlp, 64), ("LeNet-style conv net, batch 32", lenet, 32)):
+            n0 = be.launches
+            fn()
+            per_forward = be.launches - n0
+            t = _time(fn, iters)
+            print(json.dumps({"config": label, "mode": name, "us_per_forward": t * 1e6, "samples_per_s": batch / t,
+                              "launches_per_forward": per_forward}))
+        be.sync()
+
+
 def conv_roles():
     """Cycle counters of CTA 0 of the convolution kernel on the config-5 layer, per tile: where the producer, the
     MMA-issuing warp and one epilogue warp spend their time.  Needs `python -m swcompiler_b200.build --conv-timing`."""
@@ -74,11 +110,15 @@ def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--only", default=None)
     ap.add_argument("--iters", type=int, default=20)
+    ap.add_argument("--latency", action="store_true",
+                    help="the two small configurations (MLP batch 64, LeNet-style net batch 32): microseconds per forward")
     ap.add_argument("--conv-roles", action="store_true",
                     help="per-role cycle counters of the convolution kernel (library built with --conv-timing)")
     args = ap.parse_args()
     if args.conv_roles:
         return conv_roles()
+    if args.latency:
+        return latency(args.iters)
     hbm, tflops, src = _peaks()
     be = swc.Backend(0, swc.STRICT_F32)
     dev = be.device
