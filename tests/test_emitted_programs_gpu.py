@@ -47,7 +47,7 @@ def _run_ranks(which, tmp_path, files, nranks):
     outs = []
     try:
         for p in procs:
-            outs.append(p.communicate(timeout=180))
+            outs.append(p.communicate(timeout=90))
     finally:
         for p in procs:
             if p.poll() is None:
