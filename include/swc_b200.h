@@ -95,6 +95,11 @@ int swcb200_matrixSoftmax_f(swcb200_ctx *ctx, int m, int n, const float *a, int 
 /* Top-k column indices per row, ties to the higher index.  Replaces argMax_i
  * (kernels.h:601-613; Codegen.cpp:2372-2386).  top_k <= n. */
 int swcb200_argMax_i(swcb200_ctx *ctx, const float *input, int *idx, int m, int n, int top_k);
+/* Running hit count of a streaming evaluation: accum_cnt[0] += number of rows i whose label[i] is among
+ * the n predictions pred[i, :], accum_cnt[1] += m.  Replaces accuracy_i (kernels.h:617-627;
+ * Codegen.cpp:2387-2398).  The caller zeroes accum_cnt before the first batch. */
+int swcb200_accuracy_i(swcb200_ctx *ctx, const int *pred, const int *label, int *accum_cnt, int m,
+                       int n);
 
 /* The same product as swcb200_matrixMatrixMul_f in SWCB200_TC_BF16 mode, for callers that must not
  * allocate device memory (a generated program whose single arena already owns the GPU, a server with a

@@ -113,6 +113,15 @@ class _Base:
         self._f["argmax"](_fp(a), idx.ctypes.data_as(_I), C.c_int(m), C.c_int(n), C.c_int(top_k))
         return idx
 
+    def accuracy_i(self, pred: np.ndarray, label: np.ndarray, accum: np.ndarray | None = None) -> np.ndarray:
+        """accum [2] int32 = (rows whose label is among their predictions, rows), added to `accum` if given."""
+        pred = np.ascontiguousarray(pred, np.int32)
+        label = np.ascontiguousarray(label, np.int32)
+        m, n = pred.shape
+        accum = np.zeros(2, np.int32) if accum is None else np.ascontiguousarray(accum, np.int32).copy()
+        self._f["accuracy"](pred.ctypes.data_as(_I), label.ctypes.data_as(_I), accum.ctypes.data_as(_I), C.c_int(m), C.c_int(n))
+        return accum
+
     # ---- NHWC -------------------------------------------------------------
     def conv2d_f(self, x, filt, bias, kernels, strides, pads, group=1) -> np.ndarray:
         odims = conv_out_dims(x.shape, filt.shape, kernels, strides, pads)
@@ -169,7 +178,7 @@ class _Base:
 class Oracle(_Base):
     _names = dict(mm="orc_matmul_f32", badd="orc_bias_add_f32", tanh="orc_tanh_f32",
                   relu="orc_relu_f32", add="orc_add_f32", softmax="orc_softmax_f32",
-                  argmax="orc_argmax_i32", conv="orc_conv2d_f32", maxpool="orc_maxpool_f32",
+                  argmax="orc_argmax_i32", accuracy="orc_accuracy_i32", conv="orc_conv2d_f32", maxpool="orc_maxpool_f32",
                   avgpool="orc_avgpool_f32", bn="orc_batchnorm_f32", t2="orc_transpose2d_f32",
                   t4="orc_transpose4d_f32")
 
@@ -193,7 +202,7 @@ class Oracle(_Base):
 class Reference(_Base):
     _names = dict(mm="ref_matrixMatrixMul_f", badd="ref_batchedadd_f", tanh="ref_matrixTanh_f",
                   relu="ref_relu_f", add="ref_vecAdd_f", softmax="ref_matrixSoftmax_f",
-                  argmax="ref_argMax_i", conv="ref_conv2d_f", maxpool="ref_maxpool_f",
+                  argmax="ref_argMax_i", accuracy="ref_accuracy_i", conv="ref_conv2d_f", maxpool="ref_maxpool_f",
                   avgpool="ref_avgpool_f", bn="ref_batchnormalization_f", t2="ref_transpose2d_f",
                   t4="ref_transpose4d_f")
     kind = "reference"

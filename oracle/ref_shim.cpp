@@ -39,6 +39,9 @@ REF_API void ref_matrixSoftmax_f(int m, int n, const float *a, int lda, float *b
 REF_API void ref_argMax_i(const float *in, int *idx, int m, int n, int top_k) {
     argMax_i(in, idx, m, n, top_k);
 }
+REF_API void ref_accuracy_i(const int *pred, const int *label, int *accum, int m, int n) {
+    accuracy_i(pred, label, accum, m, n);
+}
 REF_API void ref_conv2d_f(float *output, const float *input, const float *filter,
                           const float *bias, const size_t *odims, const size_t *idims,
                           const size_t *fdims, const size_t *bdims, const size_t *kernels,

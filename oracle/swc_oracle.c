@@ -129,6 +129,22 @@ ORC_API void orc_softmax_f32(int m, int n, const float *a, int lda, float *b, in
 }
 
 /*
+ * Running accuracy counters.  accuracy_i, kernels.h:617-627: for every row, cnt (accum[1]) goes up by one, and
+ * right_cnt (accum[0]) by one if the row's label equals any of its n predictions.
+ */
+ORC_API void orc_accuracy_i32(const int *pred, const int *label, int *accum, int m, int n) {
+    for (int i = 0; i < m; i++) {
+        accum[1] += 1;
+        for (int j = 0; j < n; j++) {
+            if (pred[(size_t)i * n + j] == label[i]) {
+                accum[0] += 1;
+                break;
+            }
+        }
+    }
+}
+
+/*
  * Top-k column indices per row, best first.  argMax_i, kernels.h:601-613 sorts
  * (value, index) pairs with std::greater, i.e. descending by value and, among
  * equal values, descending by index: a tie goes to the HIGHER index.  Restated

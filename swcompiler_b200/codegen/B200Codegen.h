@@ -25,6 +25,11 @@
 // not on every rank is printed inside `if (rank == 0)`, as the reference does (:959-1006).  The ranks
 // find each other without MPI: rank and count come from the environment, the NCCL id through a file.
 //
+// With config.use_dataloader (IRGraph::setInferDataNodes, config.dataloader_src / _samples / data_bytes) the forward
+// pass is printed inside a streaming evaluation loop over a record file, the counterpart of the reference's
+// `while (loader.next(label, data))` (src/codegen/Codegen.cpp:930-995): double-buffered pinned host buffers and
+// device slots, uploads on a second stream, AccuracyOp -> swcb200_accuracy_i.
+//
 // This header needs the reference's headers on the include path (-I<reference>/src); it is compiled
 // only where a reference checkout is present (swcompiler_b200/codegen/build_codegen.py).
 #pragma once
@@ -57,6 +62,7 @@ class B200Codegen : public swc::codegen::Codegen {
     void emitMemAllocations() override;
     void emitTensorAddresses() override;
     void emitTensorInitializations() override;
+    void emitInferDataLoaderInit() override {}  // the loader is set up where the evaluation loop is printed (emitExecute)
     void emitExecute() override;
     void emitFuncCalls() override;
     void emitMemFree() override;
@@ -108,6 +114,7 @@ class B200Codegen : public swc::codegen::Codegen {
     bool runsOnEveryRank(swc::OpNode *op);
     bool isLoadTimeScatter(swc::OpNode *op);
     bool isConstant(swc::IRNode *tensor_node);
+    bool isLoaderFed(swc::Tensor *t);
     void emitCommOp(swc::OpNode *op, std::ostream &os);
     void emitGuarded(swc::OpNode *op, std::ostream &os);   // the op's call, inside `if (rank == 0)` where it must be
 

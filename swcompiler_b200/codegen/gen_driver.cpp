@@ -8,6 +8,8 @@
 //   gen_driver resblock <out_dir> <repo_root>  [2,8,8,64] -> Conv3x3 -> BN -> ReLU -> Conv3x3 -> BN -> Add(skip) -> ReLU ->
 //                                              MaxPool -> FC -> Softmax -> top-1: a residual block wide enough (64
 //                                              channels) for the tensor-core convolution
+//   gen_driver mlp_eval <out_dir> <repo_root>  the MLP inside a streaming evaluation loop: batches of 4 from a record file
+//                                              (config.use_dataloader), top-1, running accuracy counters
 //   gen_driver fcpair   <out_dir> <repo_root>  [64,256] -> FC 256->512 -> ReLU -> FC 512->128, no bias: the model-parallel
 //                                              pair (only meaningful with _mp<N>)
 //   A name with _dp<N> (mlp8_dp2) partitions the graph over N ranks by the batch: config.mpi, config.mpi_size = N,
@@ -116,6 +118,36 @@ IRGraph *build_convnet() {
     return g;
 }
 
+// The MNIST MLP as a streaming evaluation: batches of 4 from a record file, top-1, running accuracy
+// (the graph of the reference's test/engine/testEngineMLPInfer.cpp).
+IRGraph *build_mlp_eval() {
+    auto *g = new IRGraph();
+    auto *x = tensor(g, "data0", {4, 784});
+    auto *w0 = tensor(g, "weight0", {784, 512}, "mlp_weight0.bin");
+    auto *b0 = tensor(g, "bias0", {512}, "mlp_bias0.bin");
+    auto *fc0 = op(g, "fc0", new MatrixMatrixFCBiasOp(), x, w0, b0);
+    auto *h0 = result(g, "data1", {4, 512}, fc0);
+    auto *th = op(g, "tanh0", new MatrixTanhOp(), h0);
+    auto *h1 = result(g, "data2", {4, 512}, th);
+    auto *w1 = tensor(g, "weight1", {512, 10}, "mlp_weight1.bin");
+    auto *b1 = tensor(g, "bias1", {10}, "mlp_bias1.bin");
+    auto *fc1 = op(g, "fc1", new MatrixMatrixFCBiasOp(), h1, w1, b1);
+    auto *logits = result(g, "data3", {4, 10}, fc1);
+    auto *sm = op(g, "softmax", new MatrixSoftmaxOp(), logits);
+    auto *probs = result(g, "data4", {4, 10}, sm);
+    auto *am = op(g, "argmax", new ArgMaxOp(1), probs);
+    auto *top1 = result(g, "top1", {4, 1}, am, DataType::Int32_t);
+    auto *label = tensor(g, "selected", {4}, nullptr, DataType::Int32_t);
+    auto *acc = op(g, "accuracy", new AccuracyOp(), top1, label);
+    auto *accur = result(g, "accur", {1, 2}, acc, DataType::Int32_t);
+    accur->getTensor()->setTensorInit(TensorInitType::CONSTANT, 0);
+    g->findInOut();
+    g->updateTopology();
+    g->setInferDataNodes(label, x);
+    g->addDisplayTensorNodes(accur);
+    return g;
+}
+
 IRGraph *build_fcpair() {
     auto *g = new IRGraph();
     auto *x = tensor(g, "x", {64, 256}, "fp_x.bin");
@@ -202,12 +234,20 @@ int main(int argc, char **argv) {
     IRGraph *g = base == "mlp8" ? build_mlp8()
                  : base == "convnet" ? build_convnet()
                  : base == "resblock" ? build_resblock()
-                 : base == "fcpair" ? build_fcpair() : nullptr;
+                 : base == "fcpair" ? build_fcpair()
+                 : base == "mlp_eval" ? build_mlp_eval() : nullptr;
     if (!g) {
         std::cerr << "unknown graph " << base << "\n";
         return 2;
     }
     Config config;  // inference, one device, no MPI: the defaults
+    if (base == "mlp_eval") {
+        config.use_dataloader = true;
+        config.dataloader_src = "mnist8_records.bin";
+        config.label_bytes = BytesProto::ONE_BYTE_AS_INT;
+        config.data_bytes = BytesProto::FOUR_BYTES_AS_FLOAT;
+        config.dataloader_samples = 10;  // 8 images + 2 more: batches of 4 use 8, the tail is dropped
+    }
     if (ranks > 1) {
         config.mpi = true;
         config.mpi_size = ranks;

@@ -214,6 +214,26 @@ __global__ void __launch_bounds__(256) argmax_kernel(const float *__restrict__ i
     }
 }
 
+// accum[0] += rows whose label is among their n predictions, accum[1] += rows; integer counters, so the result does
+// not depend on the order of the atomic additions
+__global__ void __launch_bounds__(256) accuracy_kernel(const int *__restrict__ pred, const int *__restrict__ label,
+                                                       int *__restrict__ accum, int m, int n) {
+    int hits = 0;
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < (size_t)m; i += (size_t)gridDim.x * blockDim.x) {
+        const int want = label[i];
+        const int *row = pred + i * (size_t)n;
+        for (int j = 0; j < n; j++)
+            if (row[j] == want) {
+                hits++;
+                break;
+            }
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) hits += __shfl_xor_sync(kFull, hits, o);
+    if ((threadIdx.x & 31) == 0 && hits) atomicAdd(accum, hits);
+    if (blockIdx.x == 0 && threadIdx.x == 0) atomicAdd(accum + 1, m);
+}
+
 template <bool kStrict>
 int launch_softmax(swcb200_ctx *ctx, int m, int n, const float *a, int lda, float *b, int ldb) {
     const int warps = 8;
@@ -268,4 +288,14 @@ SWC_EXPORT int swcb200_argMax_i(swcb200_ctx *ctx, const float *input, int *idx, 
     unsigned grid = swc_grid(ctx, (size_t)m, 8, 8);
     argmax_kernel<<<grid, 256, 0, ctx->stream>>>(input, idx, m, n, top_k);
     return swc_check_launch(ctx, "argMax_i");
+}
+
+SWC_EXPORT int swcb200_accuracy_i(swcb200_ctx *ctx, const int *pred, const int *label, int *accum_cnt, int m, int n) {
+    SWC_CTX(ctx);
+    SWC_REQUIRE(ctx, m >= 0 && n >= 0, SWCB200_ERR_BAD_ARG, "accuracy_i: negative shape");
+    if (m == 0) return SWCB200_OK;
+    SWC_REQUIRE(ctx, label && accum_cnt && (n == 0 || pred), SWCB200_ERR_BAD_ARG, "accuracy_i: null tensor");
+    unsigned grid = swc_grid(ctx, (size_t)m, 256, 4);
+    accuracy_kernel<<<grid, 256, 0, ctx->stream>>>(pred, label, accum_cnt, m, n);
+    return swc_check_launch(ctx, "accuracy_i");
 }

@@ -137,6 +137,17 @@ class Backend:
         self._call("argMax_i", _p(a), _p(idx), C.c_int(m), C.c_int(n), C.c_int(top_k))
         return idx
 
+    def accuracy_i(self, pred, label, accum=None):
+        """accum [2] int32 += (rows whose label is among their predictions pred[i, :], rows); a fresh zeroed
+        counter pair if `accum` is None."""
+        m, n = pred.shape
+        if accum is None:
+            accum = torch.zeros(2, dtype=torch.int32, device=self.device)
+            if self.torch_stream is None:  # the library's own stream knows nothing of torch's fill kernel
+                torch.cuda.current_stream(self.device).synchronize()
+        self._call("accuracy_i", _p(pred), _p(label), _p(accum), C.c_int(m), C.c_int(n))
+        return accum
+
     def relu_f(self, a, out=None):
         self._f32(a)
         out = out if out is not None else torch.empty_like(a)

@@ -63,6 +63,19 @@ def argmax_cases():
     return out
 
 
+def accuracy_cases():
+    """Predictions [m, n] int32 (top-n indices) against labels [m]."""
+    out = {}
+    r = _rng(37)
+    out["acc_64x1"] = dict(pred=r.integers(0, 10, (64, 1)).astype(np.int32), label=r.integers(0, 10, 64).astype(np.int32))
+    out["acc_1000x3"] = dict(pred=r.integers(0, 10, (1000, 3)).astype(np.int32), label=r.integers(0, 10, 1000).astype(np.int32))
+    # a label that appears twice among a row's predictions counts once
+    out["acc_dups_5x4"] = dict(pred=np.array([[1, 1, 1, 1], [0, 2, 2, 0], [3, 4, 5, 6], [7, 7, 8, 9], [9, 9, 9, 9]], np.int32),
+                               label=np.array([1, 2, 0, 7, 3], np.int32))
+    out["acc_1x1"] = dict(pred=np.array([[4]], np.int32), label=np.array([4], np.int32))
+    return out
+
+
 def flat_cases():
     """Flat vectors for relu / add; lengths around the 128-bit vector width."""
     out = {}
@@ -142,7 +155,7 @@ def transpose_cases():
     return out
 
 
-def run_all(impl):
+def run_all(impl, accuracy=True):
     """Outputs of every case through ``impl`` (an Oracle/Reference-shaped object), keyed by case name."""
     res = {}
     for k, c in matmul_cases().items():
@@ -153,6 +166,8 @@ def run_all(impl):
         res[k + "/softmax"] = impl.matrixSoftmax_f(c["x"])
     for k, c in argmax_cases().items():
         res[k] = impl.argMax_i(c["x"], c["k"])
+    for k, c in (accuracy_cases() if accuracy else {}).items():
+        res[k] = impl.accuracy_i(c["pred"], c["label"])
     for k, c in flat_cases().items():
         res[k + "/relu"] = impl.relu_f(c["a"])
         res[k + "/add"] = impl.vecAdd_f(c["a"], c["b"])

@@ -84,6 +84,22 @@ def resblock_oracle(impl, t, rnd=lambda a: a):
     return impl.matrixSoftmax_f(impl.fc(h, rnd(t["rb_fc_w.bin"]), t["rb_fc_b.bin"]))
 
 
+def write_mnist8_records(dirname, wrong=(3,)):
+    """A record file in the reference DataLoader's format, <1 label byte><784 floats> per sample: the 8 fixture images and
+    2 more (a tail that batches of 4 drop); the labels listed in `wrong` are made wrong on purpose."""
+    g = os.path.join(ROOT, "tests", "golden", "mnist8")
+    x = np.fromfile(os.path.join(g, "mnist_images_8.bin"), np.float32).reshape(8, 784)
+    labels = np.loadtxt(os.path.join(g, "mnist_images_8.meta.txt"), dtype=np.int32)
+    for f in os.listdir(g):
+        shutil.copyfile(os.path.join(g, f), os.path.join(dirname, f))
+    with open(os.path.join(dirname, "mnist8_records.bin"), "wb") as f:
+        for n, i in enumerate(list(range(8)) + [0, 1]):
+            lab = int(labels[i]) if n not in wrong else (int(labels[i]) + 1) % 10
+            f.write(bytes([lab]))
+            f.write(x[i].tobytes())
+    return 8 - len([w for w in wrong if w < 8])
+
+
 def parse_printed(text: str):
     """{name: 2-D array} from the program's print_device output."""
     out, name, rows = {}, None, []

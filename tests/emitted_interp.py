@@ -19,6 +19,9 @@ _DIMS = re.compile(r"const size_t (\w+)\[\] = \{([^}]*)\};")
 _LOAD = re.compile(r"load_to_device<(\w+)>\((\w+), (\d+), (\d+), \"([^\"]+)\", host_stage\);")
 _PRINT = re.compile(r"print_device<(\w+)>\(\"(\w+)\", (\w+), (\d+), (\d+), host_stage\);")
 _ALIAS = re.compile(r"^(\w+) = (\w+);$")   # a view (Reshape): the child names the parent's storage
+_FILL = re.compile(r"fill_device<(\w+)>\((\w+), (\d+), \(\w+\)([-\d.e+]+), host_stage\);")
+_LOADER = re.compile(r"RecordLoader loader\(\"([^\"]+)\", (true|false), (\d+), (\d+), (\d+)\);")
+_SLOT = re.compile(r"^(\w+) = \1_slot\[s\];$")
 _EPI = re.compile(r"const swcb200_conv_epilogue (\w+) = \{([^}]*)\};")
 
 
@@ -43,46 +46,84 @@ class Interp:
 
     def run(self, path):
         text = open(path).read()
-        body = text[text.index("int main("):]
-        guarded = False
-        for raw in body.splitlines():
-            line = raw.strip()
-            if line == "if (rank == 0) {":
-                guarded = True
+        lines = [l.strip() for l in text[text.index("int main("):].splitlines()]
+        i = 0
+        while i < len(lines):
+            line = lines[i]
+            m = _LOADER.search(line)
+            if m:   # streaming evaluation: run the loop body once per batch the record file can fill
+                start = next(j for j in range(i, len(lines)) if lines[j].startswith("for (int s = 0; have;"))
+                end = next(j for j in range(start, len(lines)) if lines[j].startswith("SWC_CHECK(swcb200_sync(ctx)"))
+                body = lines[start + 1:end - 1]
+                fed = [_SLOT.match(l).group(1) for l in body if _SLOT.match(l)]   # label tensor, then data tensor
+                samples, batch, size = int(m.group(3)), int(m.group(4)), int(m.group(5))
+                raw = open(os.path.join(self.dir, m.group(1)), "rb").read()
+                rec = 1 + size * (4 if m.group(2) == "true" else 1)
+                self.batches = 0
+                for b0 in range(0, samples - batch + 1, batch):
+                    recs = [raw[(b0 + k) * rec:(b0 + k + 1) * rec] for k in range(batch)]
+                    assert all(len(r) == rec for r in recs), "record file shorter than the sample count"
+                    self.t[fed[0]] = np.array([np.frombuffer(r[:1], np.int8)[0] for r in recs], np.int32)
+                    self.t[fed[1]] = np.concatenate([np.frombuffer(r[1:], np.float32) if m.group(2) == "true"
+                                                     else np.frombuffer(r[1:], np.int8).astype(np.float32) for r in recs])
+                    self._block(body)
+                    self.batches += 1
+                i = end
                 continue
-            if line == "}" and guarded:
-                guarded = False
-                continue
-            if guarded and self.rank != 0:
-                continue
-            m = _DIMS.search(line)
-            if m:
-                self.dims[m.group(1)] = tuple(int(v) for v in m.group(2).split(","))
-                continue
-            m = _EPI.search(line)
-            if m:
-                self.epi[m.group(1)] = [v.strip() for v in m.group(2).split(",")]
-                continue
-            m = _LOAD.search(line)
-            if m:
-                dt = np.float32 if m.group(1) == "float" else np.int32
-                a = np.fromfile(os.path.join(self.dir, m.group(5)), dtype=dt)
-                self.t[m.group(2)] = a[int(m.group(4)):int(m.group(4)) + int(m.group(3))].copy()
-                continue
-            m = _PRINT.search(line)
-            if m:
-                self.printed[m.group(2)] = self.t[m.group(3)].reshape(int(m.group(4)), int(m.group(5)))
-                continue
-            m = _ALIAS.match(line)
-            if m and m.group(2) in self.t:
-                self.t[m.group(1)] = self.t[m.group(2)]
-                continue
-            m = _CALL.search(line)
-            if m:
-                args = [a.strip() for a in m.group(2).split(",")][1:]   # drop ctx
-                self.calls.append(m.group(1))
-                getattr(self, "op_" + m.group(1), self._ignore)(*args)
+            i = self._block(lines, i, single=True)
         return self.printed
+
+    def _block(self, lines, i=0, single=False):
+        """Executes lines[i:] (or, with single, one statement or one `if (rank == 0) {...}` block); returns the next index."""
+        while i < len(lines):
+            line = lines[i]
+            if line == "if (rank == 0) {":
+                j = i + 1
+                while lines[j] != "}":
+                    if self.rank == 0:
+                        self._line(lines[j])
+                    j += 1
+                i = j + 1
+            else:
+                self._line(line)
+                i += 1
+            if single:
+                break
+        return i
+
+    def _line(self, line):
+        m = _DIMS.search(line)
+        if m:
+            self.dims[m.group(1)] = tuple(int(v) for v in m.group(2).split(","))
+            return
+        m = _EPI.search(line)
+        if m:
+            self.epi[m.group(1)] = [v.strip() for v in m.group(2).split(",")]
+            return
+        m = _LOAD.search(line)
+        if m:
+            dt = np.float32 if m.group(1) == "float" else np.int32
+            a = np.fromfile(os.path.join(self.dir, m.group(5)), dtype=dt)
+            self.t[m.group(2)] = a[int(m.group(4)):int(m.group(4)) + int(m.group(3))].copy()
+            return
+        m = _FILL.search(line)
+        if m:
+            dt = np.float32 if m.group(1) == "float" else np.int32
+            self.t[m.group(2)] = np.full(int(m.group(3)), float(m.group(4)), dt)
+            return
+        m = _PRINT.search(line)
+        if m:
+            self.printed[m.group(2)] = self.t[m.group(3)].reshape(int(m.group(4)), int(m.group(5)))
+            return
+        m = _ALIAS.match(line)
+        if m and m.group(2) in self.t:
+            self.t[m.group(1)] = self.t[m.group(2)]
+            return
+        m = _CALL.search(line)
+        if m:
+            args = [a.strip() for a in m.group(2).split(",")][1:]   # drop ctx
+            self.calls.append(m.group(1))
+            getattr(self, "op_" + m.group(1), self._ignore)(*args)
 
     def _ignore(self, *a):
         pass
@@ -104,6 +145,9 @@ class Interp:
 
     def op_argMax_i(self, a, idx, m, n, k):
         self.t[idx] = self.o.argMax_i(self._get(a).reshape(int(m), int(n)), int(k)).reshape(-1).astype(np.int32)
+
+    def op_accuracy_i(self, pred, label, accum, m, n):
+        self.t[accum] = self.o.accuracy_i(self._get(pred).reshape(int(m), int(n)), self._get(label), self._get(accum))
 
     def op_relu_f(self, src, dst, size):
         self.t[dst] = self.o.relu_f(self._get(src)[:int(size)])

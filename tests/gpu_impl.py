@@ -38,6 +38,9 @@ class GpuImpl:
     def argMax_i(self, a, k):
         return self._n(self.be.argMax_i(self._t(a), k))
 
+    def accuracy_i(self, pred, label, accum=None):
+        return self._n(self.be.accuracy_i(self._t(pred), self._t(label), None if accum is None else self._t(accum)))
+
     def conv2d_f(self, x, w, b, kernels, strides, pads, group=1):
         return self._n(self.be.conv2d_f(self._t(x), self._t(w), self._t(b), kernels, strides, pads, group))
 

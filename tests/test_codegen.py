@@ -130,6 +130,27 @@ def test_model_parallel_mlp8_retiles_between_ops_that_disagree():
     assert "data1_transform_dims_6[] = {8, 512};" in text and "data1_transform_dims_6, 2, 0, 1, SWCB200_F32)" in text
 
 
+def test_streaming_evaluation_program(oracle, tmp_path):
+    """config.use_dataloader: the forward pass inside a loop over a record file, two device slots and two pinned host
+    buffers for the loader-fed tensors, uploads on a second stream, AccuracyOp as swcb200_accuracy_i; the counters are
+    zeroed once and accumulate over the batches; a tail the file cannot fill a batch from is dropped."""
+    from codegen_util import write_mnist8_records
+    from emitted_interp import Interp
+    text = open(os.path.join(EMITTED, "mlp_eval_Graph.cpp")).read()
+    assert 'RecordLoader loader("mnist8_records.bin", true, 10, 4, 784);' in text
+    assert "data0 = data0_slot[s];" in text and "selected = selected_slot[s];" in text
+    assert "cudaMemcpyAsync(data0, host_data[s], 3136 * sizeof(float), cudaMemcpyHostToDevice, copy_stream)" in text
+    assert "swcb200_accuracy_i(ctx, top1, selected, accur, 4, 1)" in text
+    assert text.index("fill_device<int>(accur, 2, (int)0, host_stage);") < text.index("for (int s = 0; have; s ^= 1) {")
+    assert 'load_to_device<float>(data0' not in text          # the loader fills it, batch by batch
+    right = write_mnist8_records(str(tmp_path), wrong=(3,))
+    for which in ("mlp_eval", "mlp_eval_fused"):
+        it = Interp(oracle, str(tmp_path))
+        out = it.run(os.path.join(EMITTED, which + "_Graph.cpp"))
+        assert it.batches == 2 and out["accur"].tolist() == [[right, 8]], which
+    assert _calls("mlp_eval_fused").count("fc_bf16") == 2 and _calls("mlp_eval_fused").count("pack_weight_bf16") == 2
+
+
 def _interpret(which, files, oracle, tmp_path):
     from emitted_interp import Interp
     for name, arr in files.items():

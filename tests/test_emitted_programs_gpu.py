@@ -92,6 +92,17 @@ def test_model_parallel_fc_pair_on_two_ranks(tmp_path, oracle):
     assert np.allclose(got["y"], want, atol=6e-4)   # two partial sums instead of one k-sequential sum, three decimals printed
 
 
+@pytest.mark.parametrize("which", ["mlp_eval", "mlp_eval_fused"])
+def test_streaming_evaluation_counts(which, tmp_path):
+    from codegen_util import write_mnist8_records
+    right = write_mnist8_records(str(tmp_path), wrong=(3,))
+    exe = compile_emitted(which, str(tmp_path))
+    r = subprocess.run([exe], capture_output=True, text=True, cwd=str(tmp_path), timeout=120)
+    assert r.returncode == 0, r.stderr
+    assert "batches: 2" in r.stdout
+    assert parse_printed(r.stdout)["accur"].astype(int).tolist() == [[right, 8]]
+
+
 def test_fused_mlp8_reproduces_the_known_answer(tmp_path, golden):
     exe = compile_emitted("mlp8_fused", str(tmp_path))
     for f in os.listdir(os.path.join(GOLDEN, "mnist8")):
