@@ -52,7 +52,10 @@ class B200Codegen : public swc::codegen::Codegen {
     // precision: 0 = strict fp32 (bit-exact with the reference's generated C), 1 = tensor-core bf16 for the
     // fp32 entry points (see swc_b200.h)
     // fuse: plan fused calls as described above (ignored in strict precision: there are no fused strict kernels)
-    B200Codegen(swc::IRGraph *graph, Config &config, int device = 0, int precision = 0, bool fuse = false);
+    // graph_replays > 0: the forward pass is captured into a CUDA graph after one plain run and launched that many
+    // times (for forward passes that are bound by launch latency; single-GPU programs without a data loader)
+    B200Codegen(swc::IRGraph *graph, Config &config, int device = 0, int precision = 0, bool fuse = false,
+                int graph_replays = 0);
 
     void emitHeader() override;
     void emitEnvInit() override;
@@ -120,6 +123,7 @@ class B200Codegen : public swc::codegen::Codegen {
 
     int device_, precision_;
     bool fuse_;
+    int graph_replays_ = 0;
     bool parallel_ = false;
     int nranks_ = 1;
     size_t master_bytes_ = 0;

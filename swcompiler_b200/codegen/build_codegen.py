@@ -24,7 +24,8 @@ EMITTED = os.path.join(HERE, "emitted")
 
 # the sample programs: <graph>[_dp<N> | _mp<N>][_fused], see gen_driver.cpp
 PROGRAMS = ("mlp8", "convnet", "resblock", "mlp8_fused", "convnet_fused", "resblock_fused",
-            "mlp8_dp2", "mlp8_dp2_fused", "fcpair_mp2", "mlp8_mp2", "resblock_dp2", "mlp_eval", "mlp_eval_fused")
+            "mlp8_dp2", "mlp8_dp2_fused", "fcpair_mp2", "mlp8_mp2", "resblock_dp2", "mlp_eval", "mlp_eval_fused",
+            "mlp8_graph", "resblock_fused_graph")
 
 
 def reference_sources(ref: str):

@@ -18,6 +18,8 @@
 //   columns {-1,1,1}, the activation on column tiles {1,1}, second FC by input rows {1,0,-2}; for the MLP the bias-adds
 //   on row tiles, which makes the passes insert Transform nodes -- and runs ParallelLowering on them (the labeling pass
 //   draws strategies from std::random_device, so it is skipped for a reproducible program).
+//   A name that ends in _graph (mlp8_graph, convnet_fused_graph) has the forward pass captured into a CUDA graph and
+//   replayed three times.
 //   A name with the suffix _fused (mlp8_fused, convnet_fused, resblock_fused) selects tensor-core precision and the
 //   emit-time fusion planner: one call per fused chain, bf16 activations between fused calls.
 //
@@ -216,11 +218,15 @@ int main(int argc, char **argv) {
         return 2;
     }
     const std::string which = argv[1], out_dir = argv[2], repo = argv[3];
-    // name = <graph>[_dp<N> | _mp<N>][_fused]
+    // name = <graph>[_dp<N> | _mp<N>][_fused][_graph]
     std::string base = which;
-    const std::string suffix = "_fused";
-    const bool fused = base.size() > suffix.size() && base.compare(base.size() - suffix.size(), suffix.size(), suffix) == 0;
-    if (fused) base = base.substr(0, base.size() - suffix.size());
+    auto strip = [&base](const std::string &suffix) {
+        if (base.size() <= suffix.size() || base.compare(base.size() - suffix.size(), suffix.size(), suffix) != 0) return false;
+        base = base.substr(0, base.size() - suffix.size());
+        return true;
+    };
+    const bool graph = strip("_graph");
+    const bool fused = strip("_fused");
     int ranks = 1;
     bool model_parallel = false;
     for (const char *tag : {"_dp", "_mp"}) {
@@ -292,7 +298,7 @@ int main(int argc, char **argv) {
         g->findInOut();
         g->updateTopology();
     }
-    swcb200::B200Codegen gen(g, config, /*device=*/0, /*precision=*/fused ? 1 : 0, /*fuse=*/fused);
+    swcb200::B200Codegen gen(g, config, /*device=*/0, /*precision=*/fused ? 1 : 0, /*fuse=*/fused, /*graph_replays=*/graph ? 3 : 0);
     engine.setCodegenerator(&gen);
     const std::string code = engine.genCode();
     std::ofstream(out_dir + "/" + which + "_Graph.cpp") << code;

@@ -70,6 +70,18 @@ class Interp:
                     self.batches += 1
                 i = end
                 continue
+            if line == "auto forward = [&]() {":   # CUDA-graph form: the forward pass as a closure, run plainly then replayed
+                end = next(j for j in range(i, len(lines)) if lines[j] == "};")
+                self.forward_body, self.forward_runs = lines[i + 1:end], 0
+                i = end + 1
+                continue
+            if line == "forward();" or line.startswith("for (int rep = 0;") and "cudaGraphLaunch" in line:
+                reps = int(re.search(r"rep < (\d+)", line).group(1)) if line.startswith("for (int rep") else 1
+                for _ in range(reps):
+                    self._block(self.forward_body)
+                    self.forward_runs += 1
+                i += 1
+                continue
             i = self._block(lines, i, single=True)
         return self.printed
 

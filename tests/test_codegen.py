@@ -130,6 +130,27 @@ def test_model_parallel_mlp8_retiles_between_ops_that_disagree():
     assert "data1_transform_dims_6[] = {8, 512};" in text and "data1_transform_dims_6, 2, 0, 1, SWCB200_F32)" in text
 
 
+def test_cuda_graph_form(oracle, golden, tmp_path):
+    """graph_replays: the calls of the forward pass sit in a closure that runs once plainly (the library's first-call
+    set-up must not happen inside a capture), once under stream capture, and is then replayed as a CUDA graph."""
+    import numpy as np
+
+    from conftest import GOLDEN, bits
+    from emitted_interp import Interp
+    text = open(os.path.join(EMITTED, "mlp8_graph_Graph.cpp")).read()
+    body = text[text.index("auto forward = [&]() {"):text.index("};\n    forward();")]
+    assert body.count("SWC_CHECK(swcb200_") == 7 and "swcb200_sync" not in body     # nothing that synchronises inside
+    order = [text.index(t) for t in ("forward();\n    SWC_CHECK(swcb200_sync(ctx));", "cudaStreamBeginCapture(run_stream",
+                                     "cudaStreamEndCapture(run_stream, &graph)", "cudaGraphInstantiate(&graph_exec, graph, 0)",
+                                     "cudaGraphLaunch(graph_exec, run_stream)", "print_device<float>")]
+    assert order == sorted(order)
+    d = os.path.join(GOLDEN, "mnist8")
+    it = Interp(oracle, d)
+    out = it.run(os.path.join(EMITTED, "mlp8_graph_Graph.cpp"))
+    assert it.forward_runs == 5 and np.array_equal(bits(out["data4"]), bits(golden["mnist8/probs"]))   # 1 plain + 1 captured + 3 replays
+    assert _calls("resblock_fused_graph").count("conv2d_bf16") == 2
+
+
 def test_streaming_evaluation_program(oracle, tmp_path):
     """config.use_dataloader: the forward pass inside a loop over a record file, two device slots and two pinned host
     buffers for the loader-fed tensors, uploads on a second stream, AccuracyOp as swcb200_accuracy_i; the counters are

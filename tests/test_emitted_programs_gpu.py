@@ -103,6 +103,18 @@ def test_streaming_evaluation_counts(which, tmp_path):
     assert parse_printed(r.stdout)["accur"].astype(int).tolist() == [[right, 8]]
 
 
+def test_cuda_graph_replay_of_mlp8(tmp_path, golden):
+    got = _run("mlp8_graph", tmp_path, _mnist8_files())
+    assert got["top3"].astype(int).tolist() == golden["mnist8/top3"].tolist()
+    assert np.allclose(got["data4"], golden["mnist8/probs"], atol=5.1e-4)
+
+
+def test_cuda_graph_replay_of_the_fused_residual_block(tmp_path, oracle):
+    t = resblock_inputs()
+    got = _run("resblock_fused_graph", tmp_path, t)
+    assert np.abs(got["probs"] - resblock_oracle(oracle, t, rnd=cases.bf16_round)).max() <= 2e-2
+
+
 def test_fused_mlp8_reproduces_the_known_answer(tmp_path, golden):
     exe = compile_emitted("mlp8_fused", str(tmp_path))
     for f in os.listdir(os.path.join(GOLDEN, "mnist8")):
