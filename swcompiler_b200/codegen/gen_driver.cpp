@@ -18,6 +18,8 @@
 //   columns {-1,1,1}, the activation on column tiles {1,1}, second FC by input rows {1,0,-2}; for the MLP the bias-adds
 //   on row tiles, which makes the passes insert Transform nodes -- and runs ParallelLowering on them (the labeling pass
 //   draws strategies from std::random_device, so it is skipped for a reproducible program).
+//   A name with _rp<N> leaves the choice to the reference's labeling pass, which draws from std::random_device: every run
+//   gives another partitioning (used to fuzz the generator, not for committed samples).
 //   A name that ends in _graph (mlp8_graph, convnet_fused_graph) has the forward pass captured into a CUDA graph and
 //   replayed three times.
 //   A name with the suffix _fused (mlp8_fused, convnet_fused, resblock_fused) selects tensor-core precision and the
@@ -229,11 +231,13 @@ int main(int argc, char **argv) {
     const bool fused = strip("_fused");
     int ranks = 1;
     bool model_parallel = false;
-    for (const char *tag : {"_dp", "_mp"}) {
+    bool random_strategies = false;  // _rp<N>: whatever the reference's labeling pass draws (not reproducible: for fuzzing)
+    for (const char *tag : {"_dp", "_mp", "_rp"}) {
         const size_t at = base.rfind(tag);
         if (at != std::string::npos && at + 3 < base.size() && isdigit(base[at + 3])) {
             ranks = atoi(base.c_str() + at + 3);
             model_parallel = std::string(tag) == "_mp";
+            random_strategies = std::string(tag) == "_rp";
             base = base.substr(0, at);
         }
     }
@@ -257,7 +261,7 @@ int main(int argc, char **argv) {
     if (ranks > 1) {
         config.mpi = true;
         config.mpi_size = ranks;
-        config.force_data_parallel = !model_parallel;
+        config.force_data_parallel = !model_parallel && !random_strategies;
     }
     g->setConfig(config);
     Engine engine(g);

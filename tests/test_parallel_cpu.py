@@ -156,6 +156,39 @@ def test_two_ranks_gloo(fn):
     run_ranks(fn, 2)
 
 
+def _fuzz_program(rank, world):
+    import sys
+    here = os.path.dirname(os.path.abspath(__file__))
+    sys.path[:0] = [os.path.dirname(here), here]
+    from emitted_interp import Interp
+    from oracle import oracle as orc
+    o = orc.Oracle()
+    o.set_threads(1)
+    out = Interp(o, os.path.join(here, "golden", "mnist8"), rank, world, par.TorchComm()).run(os.environ["SWC_FUZZ_PROGRAM"])
+    if rank == 0:
+        assert out["top3"][:, 0].tolist() == [5, 0, 4, 1, 9, 2, 1, 3]
+
+
+@pytest.mark.skipif(not os.path.exists(os.path.join(os.environ.get("REFERENCE_ROOT", "/root/reference"), "include", "SWC.h")),
+                    reason="no reference checkout")
+@pytest.mark.parametrize("which", ["mlp8_rp2", "mlp8_rp2_fused"])
+def test_whatever_partitioning_the_reference_draws(which, tmp_path):
+    """The reference's ParallelLabelingPass picks each op's strategy from std::random_device: every run of the generator
+    gives another mix of batch, column and row splits with their Scatter / Gather / Reduce / Transform nodes.  Two
+    draws are emitted here and interpreted on two gloo ranks; whatever was drawn, the known answer must come out."""
+    import subprocess
+
+    from swcompiler_b200.codegen import build_codegen as bc
+    exe = bc.build(os.environ.get("REFERENCE_ROOT", "/root/reference"))
+    for draw in range(2):
+        d = tmp_path / str(draw)
+        d.mkdir()
+        r = subprocess.run([exe, which, str(d), "x"], cwd=os.path.dirname(exe), capture_output=True, text=True)
+        assert r.returncode == 0, r.stderr[-2000:]
+        os.environ["SWC_FUZZ_PROGRAM"] = str(d / (which + "_Graph.cpp"))
+        run_ranks(_fuzz_program, 2)
+
+
 def test_shapes_and_costs():
     assert par.shard_dims((8, 12), 1, 4) == (8, 3) and par.shard_dims((8, 12), -1, 4) == (8, 12)
     with pytest.raises(ValueError):
