@@ -238,10 +238,10 @@ int swcb200_allreduce_sum(swcb200_ctx *ctx, const void *src, void *dst, size_t c
 /* Gather along axis 0 with the result on every rank. */
 int swcb200_allgather(swcb200_ctx *ctx, const void *src, void *dst, size_t count_per_rank,
                       int dtype);
-/* Transform node (:685-871): re-tile a 2-D tensor [R, C] from pre_axis to post_axis.  Axes: 0 / 1 =
- * split along rows / columns (shards packed), -1 = whole tensor on every rank, -2 (pre only) = a
- * full-size partial sum on every rank.  i -> j is an all-to-all, -2 -> j a reduce(-scatter), -1 -> j a
- * local slice, j -> -1 an all-gather. */
+/* Transform node (:685-871): re-tile a tensor of un-partitioned shape dims[ndim] from pre_axis to
+ * post_axis.  Axes: a >= 0 = split along axis a (shards packed: dims[a] / p), -1 = whole tensor on every
+ * rank, -2 (pre only) = a full-size partial sum on every rank.  i -> j is an all-to-all, -2 -> j a
+ * reduce(-scatter), -1 -> j a local slice, j -> -1 an all-gather. */
 int swcb200_transform(swcb200_ctx *ctx, const void *src, void *dst, const size_t *dims, int ndim,
                       int pre_axis, int post_axis, int dtype);
 

@@ -419,15 +419,118 @@ SWC_EXPORT int swcb200_allgather(swcb200_ctx *ctx, const void *src, void *dst, s
     return SWCB200_OK;
 }
 
-// Re-tiling of a 2-D tensor [R, C].  Shards are packed: split along 0 -> [R/p, C]; along 1 -> [R, C/p];
-// -1 -> the whole tensor on every rank; -2 -> a full-size partial sum on every rank.
+namespace {
+
+// Re-tiling of a tensor with any number of dimensions.  A tile split along axis a, seen as `outer` rows of
+// `inner` elements (outer = product of the tile's dims before a, inner = of those from a on), holds for every
+// rank q one window of inner/p columns; the reference builds MPI vector types of exactly this shape
+// (src/codegen/ParallelCodegen.cpp:723-797).  split i -> split j: the window for q along j of the local tile is
+// packed, exchanged, and unpacked as the window from q along i of the result tile; both sides enumerate the same
+// sub-box (i in the sender's range, j in the receiver's) in row-major order.
+int transform_nd(swcb200_ctx *ctx, const void *src, void *dst, const size_t *dims, int ndim, int pre, int post, int dtype) {
+    size_t elem;
+    int type = nccl_type(dtype, &elem);
+    SWC_REQUIRE(ctx, type >= 0, SWCB200_ERR_BAD_ARG, "transform: unknown dtype");
+    swcb200_comm *c = ctx->comm;
+    const size_t p = (size_t)c->nranks;
+    size_t total = 1;
+    for (int d = 0; d < ndim; d++) total *= dims[d];
+    if (total == 0) return SWCB200_OK;
+    SWC_REQUIRE(ctx, src && dst, SWCB200_ERR_BAD_ARG, "transform: null tensor");
+    SWC_REQUIRE(ctx, pre < 0 || dims[pre] % p == 0, SWCB200_ERR_BAD_SHAPE, "transform: dims[%d] not divisible by the ranks", pre);
+    SWC_REQUIRE(ctx, post < 0 || dims[post] % p == 0, SWCB200_ERR_BAD_SHAPE, "transform: dims[%d] not divisible by the ranks", post);
+    // (outer, inner) of a tensor whose dims are `dims` with dims[split] divided by p (split < 0: undivided), seen along `axis`
+    auto view = [&](int split, int axis, size_t *outer, size_t *inner) {
+        *outer = 1;
+        *inner = 1;
+        for (int d = 0; d < ndim; d++) {
+            const size_t e = d == split ? dims[d] / p : dims[d];
+            if (d < axis)
+                *outer *= e;
+            else
+                *inner *= e;
+        }
+    };
+    const uint8_t *s = (const uint8_t *)src;
+    uint8_t *d = (uint8_t *)dst;
+    const size_t tile = total / p;
+    int rc;
+    if (pre == post) {
+        const size_t n = pre >= 0 ? tile : total;
+        if (dst != src) SWC_CUDA(ctx, cudaMemcpyAsync(dst, src, n * elem, cudaMemcpyDeviceToDevice, ctx->stream));
+        return SWCB200_OK;
+    }
+    if (pre == -1 || pre == -2) {
+        const uint8_t *full = s;
+        if (pre == -2) {  // partial sums: reduce first (MPI_Reduce + master scatter in the reference, :798-862)
+            if (post == -1) {
+                SWC_NCCL(ctx, g_nccl.AllReduce(src, dst, total, type, ncclSum, c->comm, ctx->stream));
+                return SWCB200_OK;
+            }
+            void *stage = nullptr;
+            rc = swc_scratch(ctx, total * elem, &stage);
+            if (rc) return rc;
+            SWC_NCCL(ctx, g_nccl.AllReduce(src, stage, total, type, ncclSum, c->comm, ctx->stream));
+            full = (const uint8_t *)stage;
+        }
+        size_t outer, inner;  // replicated -> split: the local window, no communication (:864-867)
+        view(-1, post, &outer, &inner);
+        const size_t blk = inner / p;
+        return copy_window(ctx, d, blk, full + (size_t)c->rank * blk * elem, inner, blk, outer, elem);
+    }
+    if (post == -1) {  // split -> replicated: all-gather the tiles, then place each as its window along `pre`
+        void *stage = nullptr;
+        rc = swc_scratch(ctx, total * elem, &stage);
+        if (rc) return rc;
+        SWC_NCCL(ctx, g_nccl.AllGather(src, stage, tile, type, c->comm, ctx->stream));
+        size_t outer, inner;
+        view(-1, pre, &outer, &inner);
+        const size_t blk = inner / p;
+        for (size_t q = 0; q < p; q++) {
+            rc = copy_window(ctx, d + q * blk * elem, inner, (const uint8_t *)stage + q * tile * elem, blk, blk, outer, elem);
+            if (rc) return rc;
+        }
+        return SWCB200_OK;
+    }
+    // split pre -> split post
+    size_t so, si, ro, ri;
+    view(pre, post, &so, &si);   // the local tile, seen along `post`
+    view(post, pre, &ro, &ri);   // the result tile, seen along `pre`
+    const size_t sblk = si / p, rblk = ri / p, box = tile / p;
+    void *stage = nullptr;
+    rc = swc_scratch(ctx, 2 * tile * elem, &stage);
+    if (rc) return rc;
+    uint8_t *st_send = (uint8_t *)stage, *st_recv = st_send + tile * elem;
+    for (size_t q = 0; q < p; q++) {
+        rc = copy_window(ctx, st_send + q * box * elem, sblk, s + q * sblk * elem, si, sblk, so, elem);
+        if (rc) return rc;
+    }
+    SWC_NCCL(ctx, g_nccl.GroupStart());
+    for (size_t q = 0; q < p; q++) {
+        SWC_NCCL(ctx, g_nccl.Send(st_send + q * box * elem, box, type, (int)q, c->comm, ctx->stream));
+        SWC_NCCL(ctx, g_nccl.Recv(st_recv + q * box * elem, box, type, (int)q, c->comm, ctx->stream));
+    }
+    SWC_NCCL(ctx, g_nccl.GroupEnd());
+    for (size_t q = 0; q < p; q++) {
+        rc = copy_window(ctx, d + q * rblk * elem, ri, st_recv + q * box * elem, rblk, rblk, ro, elem);
+        if (rc) return rc;
+    }
+    return SWCB200_OK;
+}
+
+}  // namespace
+
+// Re-tiling.  Shards are packed: split along axis a -> the tensor with dims[a] / p; -1 -> the whole tensor on every
+// rank; -2 -> a full-size partial sum on every rank.  2-D tensors [R, C] take the paths below (contiguous blocks are
+// exchanged in place); other ranks of tensor go through transform_nd.
 SWC_EXPORT int swcb200_transform(swcb200_ctx *ctx, const void *src, void *dst, const size_t *dims, int ndim, int pre_axis,
                                  int post_axis, int dtype) {
     SWC_CTX(ctx);
     SWC_REQUIRE(ctx, ctx->comm != nullptr, SWCB200_ERR_NCCL, "transform: no communicator");
-    SWC_REQUIRE(ctx, dims && ndim == 2, SWCB200_ERR_UNSUPPORTED, "transform: only 2-D tensors are re-tiled");
-    SWC_REQUIRE(ctx, pre_axis >= -2 && pre_axis <= 1 && post_axis >= -1 && post_axis <= 1, SWCB200_ERR_BAD_ARG,
-                "transform: axes must be in {-2,-1,0,1} -> {-1,0,1}");
+    SWC_REQUIRE(ctx, dims && ndim >= 1 && ndim <= 8, SWCB200_ERR_BAD_ARG, "transform: bad dims");
+    SWC_REQUIRE(ctx, pre_axis >= -2 && pre_axis < ndim && post_axis >= -1 && post_axis < ndim, SWCB200_ERR_BAD_ARG,
+                "transform: axes must be in {-2,-1,0..%d} -> {-1,0..%d}", ndim - 1, ndim - 1);
+    if (ndim != 2) return transform_nd(ctx, src, dst, dims, ndim, pre_axis, post_axis, dtype);
     size_t elem;
     int type = nccl_type(dtype, &elem);
     SWC_REQUIRE(ctx, type >= 0, SWCB200_ERR_BAD_ARG, "transform: unknown dtype");

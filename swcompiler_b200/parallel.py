@@ -123,10 +123,9 @@ class TorchComm:
         return torch.cat(outs, dim=0)
 
     def transform(self, local, dims, pre, post):
-        """Re-tile a 2-D tensor from tiling `pre` to tiling `post` (see module docstring)."""
+        """Re-tile a tensor of un-partitioned shape `dims` from tiling `pre` to tiling `post` (see module docstring);
+        any number of dimensions."""
         p, r = self.nranks, self.rank
-        if len(dims) != 2:
-            raise ValueError("only 2-D tensors are re-tiled")
         if pre == post:
             return local
         if pre == REPLICATE:
@@ -138,7 +137,7 @@ class TorchComm:
             outs = [torch.empty_like(local) for _ in range(p)]
             dist.all_gather(outs, local.contiguous(), group=self.group)
             return torch.cat(outs, dim=pre)
-        # split i -> split j: all-to-all of [R/p, C/p] blocks
+        # split i -> split j: all-to-all of the sub-boxes (i in the sender's range, j in the receiver's)
         send = [take_shard(local, post, q, p) for q in range(p)]
         recv = [torch.empty_like(send[0]) for _ in range(p)]
         ops = []

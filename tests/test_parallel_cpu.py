@@ -70,6 +70,21 @@ def _transform(rank, world):
     assert torch.equal(comm.allgather(par.take_shard(full, 0, rank, world)), full)
 
 
+def _transform_nd(rank, world):
+    """Tensors with four dimensions (NHWC activations): every split axis to every other, to replicated, and from
+    replicated or partial sums."""
+    comm = par.TorchComm()
+    full = torch.arange(2 * 4 * 6 * 8, dtype=torch.float32).reshape(2, 4, 6, 8)
+    for pre in (0, 1, 2, 3, -1):
+        for post in (0, 1, 2, 3, -1):
+            out = comm.transform(par.take_shard(full, pre, rank, world), full.shape, pre, post)
+            assert torch.equal(out, par.take_shard(full, post, rank, world)), (pre, post)
+    part = full * (rank + 1)
+    total = full * sum(range(1, world + 1))
+    for post in (0, 2, 3, -1):
+        assert torch.equal(comm.transform(part, full.shape, par.PARTIAL, post), par.take_shard(total, post, rank, world))
+
+
 def _fc_pair(rank, world):
     """FC1 by output columns -> ReLU -> FC2 by input rows -> Reduce equals the un-partitioned chain (up to the
     order of the final sum)."""
@@ -151,7 +166,7 @@ def _emitted_programs(rank, world):
         assert np.array_equal(out["probs"], resblock_oracle(o, t))      # every op is per-sample: bit for bit
 
 
-@pytest.mark.parametrize("fn", [_scatter_gather, _transform, _fc_pair, _batch_split, _emitted_programs])
+@pytest.mark.parametrize("fn", [_scatter_gather, _transform, _transform_nd, _fc_pair, _batch_split, _emitted_programs])
 def test_two_ranks_gloo(fn):
     run_ranks(fn, 2)
 
@@ -160,33 +175,57 @@ def _fuzz_program(rank, world):
     import sys
     here = os.path.dirname(os.path.abspath(__file__))
     sys.path[:0] = [os.path.dirname(here), here]
+    from codegen_util import resblock_inputs, resblock_oracle
     from emitted_interp import Interp
     from oracle import oracle as orc
     o = orc.Oracle()
     o.set_threads(1)
-    out = Interp(o, os.path.join(here, "golden", "mnist8"), rank, world, par.TorchComm()).run(os.environ["SWC_FUZZ_PROGRAM"])
-    if rank == 0:
+    prog = os.environ["SWC_FUZZ_PROGRAM"]
+    mlp = "mlp8" in os.path.basename(prog)
+    files = os.path.join(here, "golden", "mnist8") if mlp else os.path.dirname(prog)
+    out = Interp(o, files, rank, world, par.TorchComm()).run(prog)
+    if rank != 0:
+        return
+    if mlp:
         assert out["top3"][:, 0].tolist() == [5, 0, 4, 1, 9, 2, 1, 3]
+    else:
+        want = resblock_oracle(o, resblock_inputs())
+        assert np.allclose(out["probs"], want, rtol=1e-4, atol=1e-5), np.abs(out["probs"] - want).max()
 
 
 @pytest.mark.skipif(not os.path.exists(os.path.join(os.environ.get("REFERENCE_ROOT", "/root/reference"), "include", "SWC.h")),
                     reason="no reference checkout")
-@pytest.mark.parametrize("which", ["mlp8_rp2", "mlp8_rp2_fused"])
+@pytest.mark.parametrize("which", ["mlp8_rp2", "mlp8_rp2_fused", "resblock_rp2"])
 def test_whatever_partitioning_the_reference_draws(which, tmp_path):
     """The reference's ParallelLabelingPass picks each op's strategy from std::random_device: every run of the generator
-    gives another mix of batch, column and row splits with their Scatter / Gather / Reduce / Transform nodes.  Two
-    draws are emitted here and interpreted on two gloo ranks; whatever was drawn, the known answer must come out."""
+    gives another mix of batch, column, row and spatial splits with their Scatter / Gather / Reduce / Transform nodes
+    (4-D re-tilings included).  Two draws are emitted here and interpreted on two gloo ranks; whatever was drawn, the
+    un-partitioned result must come out.  One family of draws is left out: a convolution split by INPUT channels adds
+    its bias on every rank before the Reduce in the reference's scheme, so the bias is counted once per rank."""
+    import re
     import subprocess
 
+    from codegen_util import resblock_inputs
     from swcompiler_b200.codegen import build_codegen as bc
     exe = bc.build(os.environ.get("REFERENCE_ROOT", "/root/reference"))
-    for draw in range(2):
+    done = 0
+    for draw in range(12):
         d = tmp_path / str(draw)
         d.mkdir()
+        if which.startswith("resblock"):
+            for name, arr in resblock_inputs().items():
+                arr.tofile(str(d / name))
         r = subprocess.run([exe, which, str(d), "x"], cwd=os.path.dirname(exe), capture_output=True, text=True)
         assert r.returncode == 0, r.stderr[-2000:]
-        os.environ["SWC_FUZZ_PROGRAM"] = str(d / (which + "_Graph.cpp"))
+        prog = str(d / (which + "_Graph.cpp"))
+        if re.search(r"swcb200_scatter\(ctx, conv\d_w, \w+, \w+, 4, 3,", open(prog).read()):
+            continue
+        os.environ["SWC_FUZZ_PROGRAM"] = prog
         run_ranks(_fuzz_program, 2)
+        done += 1
+        if done == 2:
+            break
+    assert done >= 1
 
 
 def test_shapes_and_costs():
