@@ -406,6 +406,112 @@ def run_fcpair(args, rank, world, local_rank):
         dist.destroy_process_group()
 
 
+def run_resstage(args, rank, world, local_rank):
+    """ResNet-style stage (BASELINE configs[4]): [256,56,56,64] bf16 NHWC -> 3 x (Conv3x3+BN+ReLU, Conv3x3+BN+Add+ReLU) ->
+    MaxPool 2x2/2, every Conv-BN-[Add]-ReLU chain one tensor-core launch.  The batch is split evenly over the ranks
+    (every op is per-image, no collective inside the stage); the pooled outputs are gathered on rank 0 by peer copies."""
+    import torch
+    import torch.distributed as dist
+
+    import swcompiler_b200 as swc
+    from swcompiler_b200.programs import ResStageProgram
+
+    N, HW, CH, BLOCKS = 256, 56, 64, 3
+    torch.cuda.set_device(local_rank)
+    device = torch.device("cuda", local_rank)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=device)
+    n = N // world
+    be = swc.Backend(local_rank, swc.TC_BF16)
+    g = torch.Generator(device=device).manual_seed(1005)
+    convs = [dict(w=torch.randn((CH, 3, 3, CH), generator=g, device=device) * (2.0 / (9 * CH)) ** 0.5,
+                  b=torch.zeros(CH, device=device)) for _ in range(2 * BLOCKS)]
+    bns = [dict(scale=torch.rand(CH, generator=g, device=device) + 0.5, bias=torch.randn(CH, generator=g, device=device) * 0.1,
+                mean=torch.randn(CH, generator=g, device=device) * 0.1, var=torch.rand(CH, generator=g, device=device) + 0.5,
+                eps=1e-5) for _ in range(2 * BLOCKS)]
+    gx = torch.Generator(device=device).manual_seed(1005 * 1000 + rank)
+    x = torch.randn((n, HW, HW, CH), generator=gx, device=device).to(torch.bfloat16)
+    prog = ResStageProgram(be, convs, bns, max_batch=n, hw=HW, ch=CH)
+    comm = gathered = None
+    if world > 1:
+        from swcompiler_b200 import parallel as par
+
+        def exchange(uid):
+            box = [uid]
+            dist.broadcast_object_list(box, src=0)
+            return box[0]
+
+        comm = par.NcclComm(swc.Backend(local_rank, swc.TC_BF16, stream=torch.cuda.Stream(device)), rank, world, exchange)
+        if rank == 0:
+            gathered = torch.empty((N, HW // 2, HW // 2, CH), dtype=torch.bfloat16, device=device)
+        comm.gather_rows_setup(gathered, n * (HW // 2) * (HW // 2) * CH * 2, root=0)
+    main_stream = torch.cuda.current_stream(device)
+
+    def step(on_launch=None):
+        out = prog.forward(x, on_launch=on_launch)
+        if world > 1:
+            ready = torch.cuda.Event()
+            ready.record(main_stream)
+            comm.be.torch_stream.wait_event(ready)
+            comm.gather_rows(out)
+            main_stream.wait_stream(comm.be.torch_stream)  # one pooled buffer: the next pass may overwrite it
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    for _ in range(max(args.warmup, 3)):
+        step()
+    barrier()
+    nl = prog.launches_per_forward
+    ev = [[(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(nl)]
+          for _ in range(args.steps)]
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    launches0 = be.launches
+    with ClockSampler(local_rank) as clocks:
+        barrier()
+        e0.record()
+        for s in range(args.steps):
+            step(on_launch=lambda i, when, s=s: ev[s][i][when].record())
+        e1.record()
+        barrier()
+    launches = be.launches - launches0
+    be.sync()
+    ms = e0.elapsed_time(e1)
+    conv_ms = [ev[s][i][0].elapsed_time(ev[s][i][1]) for s in range(args.steps) for i in range(nl - 1)]
+    conv_avg = sum(conv_ms) / len(conv_ms)
+    if world > 1:
+        t = torch.tensor([ms, conv_avg], device=device)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms, conv_avg = float(t[0].item()), float(t[1].item())
+    flops = 2.0 * n * HW * HW * CH * 9 * CH
+    try:
+        peak, peak_src = float(json.load(open(os.path.join(ROOT, "MEASURED_PEAKS.json")))["bf16_tflops"]), \
+            "measured (MEASURED_PEAKS.json bf16_tflops, burst: the launches are short)"
+    except Exception:
+        peak, peak_src = 1590.0, "fallback (burst figure of the profiling recipe)"
+    if rank == 0:
+        step_ms = ms / args.steps
+        achieved = flops / (conv_avg * 1e-3) / 1e12
+        print(json.dumps({
+            "metric": METRIC, "value": N / (step_ms * 1e-3), "unit": UNIT, "n_gpus": world, "steps": args.steps,
+            "warmup": max(args.warmup, 3), "ms_per_step": step_ms, "higher_is_better": True, "scaling": "strong",
+            "vs_baseline": None, "dtype": "bf16 (fp32 accumulate)", "data": "synthetic",
+            "config": {"workload": "ResNet-style conv stage (BASELINE configs[4]): [256,56,56,64] bf16 NHWC, 3 residual blocks "
+                                   "of two 3x3 64->64 convolutions with BN / skip / ReLU fused, then MaxPool 2x2/2",
+                       "global_batch": N, "images_per_gpu": n, "parallelism": f"dp{world} (batch split; pooled outputs gathered on rank 0)",
+                       "l2": "activations (103 MB per tensor at 256 images) larger than L2 at 1 and 2 GPUs; smaller beyond"},
+            "roofline": {"bound": "tensor", "achieved": achieved, "peak": peak, "unit": "TFLOP/s", "frac": achieved / peak,
+                         "traffic": None, "kernel": "conv_tc_kernel (3x3 64->64 + BN [+ skip] + ReLU, one launch)",
+                         "launch_ms": conv_avg, "flops_per_launch": flops, "peak_source": peak_src},
+            "cpu_baseline": None, "e2e": None, "gpu_launches": launches, "clocks": clocks.summary()}))
+    barrier()
+    if world > 1:
+        comm.close()
+        dist.destroy_process_group()
+
+
 def run_e2e(torch, dist, prog, x, probs, world, device, rows, e2e_steps, barrier):
     """End to end with host buffers (rank-local slice): H2D of X, forward, D2H of the probabilities."""
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
@@ -440,8 +546,9 @@ def main():
     ap.add_argument("--batch", type=int, default=BATCH, help="rows in the whole job (smaller only for profiler captures)")
     ap.add_argument("--skip-cpu-baseline", action="store_true", help="leave the CPU sample out (profiler captures)")
     ap.add_argument("--skip-e2e", action="store_true", help="leave the host-buffer pass out (profiler captures)")
-    ap.add_argument("--workload", default="widemlp", choices=["widemlp", "fcpair"],
-                    help="widemlp: the data-parallel wide MLP (default, the headline); fcpair: the model-parallel FC pair")
+    ap.add_argument("--workload", default="widemlp", choices=["widemlp", "fcpair", "resstage"],
+                    help="widemlp: the data-parallel wide MLP (default, the headline); fcpair: the model-parallel FC pair; "
+                         "resstage: the batch-split ResNet-style conv stage")
     ap.add_argument("--chunks", type=int, default=4, help="fcpair: row chunks per forward (all-reduce overlap)")
     ap.add_argument("--fcpair-rows", type=int, default=8192, help="fcpair: rows of X")
     args = ap.parse_args()
@@ -453,6 +560,8 @@ def main():
         run_reference(args, rank, world)
     elif args.workload == "fcpair":
         run_fcpair(args, rank, world, local_rank)
+    elif args.workload == "resstage":
+        run_resstage(args, rank, world, local_rank)
     else:
         run_ours(args, rank, world, local_rank)
 
