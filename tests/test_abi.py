@@ -21,6 +21,20 @@ def test_every_declared_symbol_is_exported():
     assert not missing, missing
 
 
+def test_header_is_plain_c(tmp_path):
+    """The boundary is a C ABI: the header compiles as C99 with no C++ in sight, and a C program links against the library."""
+    import subprocess
+    src = tmp_path / "use.c"
+    src.write_text('#include "swc_b200.h"\nint main(void) { swcb200_ctx *c = 0; return swcb200_version() > 0 && swcb200_destroy(c) != 0 ? 0 : 1; }\n')
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    lib = os.path.join(root, "swcompiler_b200")
+    exe = tmp_path / "use"
+    r = subprocess.run(["gcc", "-std=c99", "-Wall", "-Wextra", "-pedantic", "-Werror", "-I" + os.path.join(root, "include"), str(src),
+                        "-o", str(exe), "-L" + lib, "-lswc_b200", "-Wl,-rpath," + lib], capture_output=True, text=True)
+    assert r.returncode == 0, r.stderr
+    assert subprocess.run([str(exe)]).returncode == 0    # version > 0; a null context is refused, not dereferenced
+
+
 def test_status_strings():
     assert L.status_string(L.OK) == "ok"
     assert "sm_100" in L.status_string(L.ERR_NO_DEVICE)
