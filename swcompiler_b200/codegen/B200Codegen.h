@@ -76,6 +76,9 @@ class B200Codegen : public swc::codegen::Codegen {
 
     // number of fused calls planned (after genCode)
     int fusedGroups() const { return (int)groups_.size(); }
+    // ops the kernel table cannot carry out (after genCode).  Not empty: the emitted text holds an #error for each
+    // and must not be used.
+    const std::vector<std::string> &unsupportedOps() const { return unsupported_; }
 
   private:
     // A chain of op nodes printed as one call.  Intermediate tensors of the chain are never materialised.
@@ -95,6 +98,8 @@ class B200Codegen : public swc::codegen::Codegen {
     bool matchFc(swc::OpNode *op, Group &g);
     bool matchConv(swc::OpNode *op, Group &g);
     bool needsF32(swc::Tensor *t);
+    bool availableBefore(swc::IRNode *tensor_node, swc::OpNode *head);
+    void unsupported(swc::OpNode *op, const std::string &why, std::ostream &os);
     void walk(bool dry);                     // prints (or, dry, only records) the calls of the forward pass
     void emitGroup(const Group &g, std::ostream &os, bool dry);
     void ensureF32(swc::Tensor *t, std::ostream &os);
@@ -128,6 +133,7 @@ class B200Codegen : public swc::codegen::Codegen {
     int nranks_ = 1;
     size_t master_bytes_ = 0;
     std::map<swc::Tensor *, bool> on_master_;
+    std::vector<std::string> unsupported_;
     std::vector<Group> groups_;
     std::map<swc::OpNode *, int> group_of_;          // op node -> index into groups_
     std::map<swc::Tensor *, swc::Tensor *> alias_;     // view -> viewed

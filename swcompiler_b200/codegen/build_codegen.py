@@ -5,8 +5,10 @@
 The reference's own build system (cmake + protobuf) is not used: its library sources under src/ (all but
 the importer, which needs protobuf, and the emitted-program utilities) are compiled in place with g++,
 together with B200Codegen.cpp and gen_driver.cpp.  Objects and the binary go to codegen/build/ (not
-tracked); the emitted programs are written to codegen/emitted/ (tracked: they are what the GPU test
-compiles and runs, since the GPU machine has no reference checkout).
+tracked); the emitted sample programs are written to tests/golden/emitted/ (tracked test fixtures: they are
+what the GPU tests compile and run, since the GPU machine has no reference checkout).
+
+The reference checkout is looked for at $REFERENCE_ROOT, else in a folder `reference` beside the repository.
 """
 from __future__ import annotations
 
@@ -19,11 +21,16 @@ import sys
 HERE = os.path.dirname(os.path.abspath(__file__))
 ROOT = os.path.dirname(os.path.dirname(HERE))
 BUILD = os.path.join(HERE, "build")
-EMITTED = os.path.join(HERE, "emitted")
+EMITTED = os.path.join(ROOT, "tests", "golden", "emitted")
+
+
+def reference_root() -> str:
+    return os.environ.get("REFERENCE_ROOT") or os.path.join(os.path.dirname(ROOT), "reference")
 
 
 # the sample programs: <graph>[_dp<N> | _mp<N>][_fused], see gen_driver.cpp
 PROGRAMS = ("mlp8", "convnet", "resblock", "mlp8_fused", "convnet_fused", "resblock_fused",
+            "resproj", "resproj_fused", "convact", "convact_fused",
             "mlp8_dp2", "mlp8_dp2_fused", "fcpair_mp2", "mlp8_mp2", "resblock_dp2", "mlp_eval", "mlp_eval_fused",
             "mlp8_graph", "resblock_fused_graph")
 
@@ -38,7 +45,8 @@ def reference_sources(ref: str):
     return sorted(srcs)
 
 
-def build(ref: str = "/root/reference", quiet: bool = True) -> str:
+def build(ref: str = None, quiet: bool = True) -> str:
+    ref = ref or reference_root()
     if not os.path.exists(os.path.join(ref, "include", "SWC.h")):
         raise FileNotFoundError(f"no reference checkout at {ref}")
     os.makedirs(BUILD, exist_ok=True)
@@ -74,5 +82,5 @@ def emit(exe: str, out_dir: str = EMITTED):
 
 
 if __name__ == "__main__":
-    exe = build(sys.argv[1] if len(sys.argv) > 1 else "/root/reference", quiet=False)
+    exe = build(sys.argv[1] if len(sys.argv) > 1 else None, quiet=False)
     print(emit(exe))

@@ -12,6 +12,12 @@
 //                                              (config.use_dataloader), top-1, running accuracy counters
 //   gen_driver fcpair   <out_dir> <repo_root>  [64,256] -> FC 256->512 -> ReLU -> FC 512->128, no bias: the model-parallel
 //                                              pair (only meaningful with _mp<N>)
+//   gen_driver resproj  <out_dir> <repo_root>  a residual block with a projection shortcut on [2,8,8,64]: main branch
+//                                              Conv3x3 -> BN -> ReLU -> Conv3x3 -> BN, shortcut Conv1x1 -> BN, then
+//                                              Add -> ReLU -> MaxPool -> FC -> Softmax -> top-1 (two branches meet at the add)
+//   gen_driver convact  <out_dir> <repo_root>  [2,8,8,64] -> Conv2dWithActivation(3x3, ReLU) -> MaxPool -> FC -> Softmax -> top-1
+//   gen_driver badop    <out_dir> <repo_root>  a graph with an op outside the kernel table (ElementMul): the generator
+//                                              must refuse it (exit code 3, #error in the text)
 //   A name with _dp<N> (mlp8_dp2) partitions the graph over N ranks by the batch: config.mpi, config.mpi_size = N,
 //   config.force_data_parallel, the reference's ParallelLabeling / ParallelLowering passes unchanged.
 //   A name with _mp<N> (fcpair_mp2, mlp8_mp2) sets the model-parallel strategies by hand -- first FC split by output
@@ -212,6 +218,83 @@ IRGraph *build_resblock() {
     return g;
 }
 
+// conv -> batch-norm on `in`, returns the batch-norm output; files <prefix><tag>_*.bin
+TensorNode *conv_bn(IRGraph *g, TensorNode *in, const std::string &tag, const std::string &prefix, size_t k, size_t pad) {
+    std::vector<size_t> kk{k, k}, s1{1, 1}, pp{pad, pad, pad, pad};
+    auto *cw = tensor(g, "conv" + tag + "_w", {64, k, k, 64}, (prefix + "conv" + tag + "_w.bin").c_str());
+    auto *cb = tensor(g, "conv" + tag + "_b", {64}, (prefix + "conv" + tag + "_b.bin").c_str());
+    auto *conv = op(g, "conv" + tag, new Conv2dOp(kk, s1, pp), in, cw, cb);
+    auto *c = result(g, "conv" + tag + "_out", {2, 8, 8, 64}, conv);
+    auto *sc = tensor(g, "bn" + tag + "_scale", {64}, (prefix + "bn" + tag + "_scale.bin").c_str());
+    auto *bi = tensor(g, "bn" + tag + "_bias", {64}, (prefix + "bn" + tag + "_bias.bin").c_str());
+    auto *me = tensor(g, "bn" + tag + "_mean", {64}, (prefix + "bn" + tag + "_mean.bin").c_str());
+    auto *va = tensor(g, "bn" + tag + "_var", {64}, (prefix + "bn" + tag + "_var.bin").c_str());
+    auto *bn = op(g, "bn" + tag, new BatchNormalizationOp(1e-5f), c, sc, bi, me, va);
+    return result(g, "bn" + tag + "_out", {2, 8, 8, 64}, bn);
+}
+
+// pool 2x2/2 -> FC 1024->10 -> softmax -> top-1 behind a [2,8,8,64] activation; files <prefix>fc_*.bin
+void classifier_tail(IRGraph *g, TensorNode *act, const std::string &prefix) {
+    std::vector<size_t> k2{2, 2}, s2{2, 2}, p0{0, 0, 0, 0};
+    auto *pool = op(g, "pool0", new MaxPoolOp(k2, s2, p0), act);
+    auto *q0 = result(g, "pool_out", {2, 4, 4, 64}, pool);
+    auto *fw = tensor(g, "fc_w", {1024, 10}, (prefix + "fc_w.bin").c_str());
+    auto *fb = tensor(g, "fc_b", {10}, (prefix + "fc_b.bin").c_str());
+    auto *fc = op(g, "fc0", new MatrixMatrixFCBiasOp(), q0, fw, fb);
+    auto *logits = result(g, "logits", {2, 10}, fc);
+    auto *sm = op(g, "softmax", new MatrixSoftmaxOp(), logits);
+    auto *probs = result(g, "probs", {2, 10}, sm);
+    auto *am = op(g, "argmax", new ArgMaxOp(1), probs);
+    auto *top1 = result(g, "top1", {2, 1}, am, DataType::Int32_t);
+    g->findInOut();
+    g->updateTopology();
+    g->addDisplayTensorNodes(probs, top1);
+}
+
+// A residual block whose shortcut is itself a convolution (1x1 + batch-norm): two convolution chains end at the add.
+IRGraph *build_resproj() {
+    auto *g = new IRGraph();
+    auto *x = tensor(g, "image", {2, 8, 8, 64}, "rp_input.bin");
+    auto *shortcut = conv_bn(g, x, "S", "rp_", 1, 0);   // declared first: it also comes first in the topological order
+    auto *b0 = conv_bn(g, x, "0", "rp_", 3, 1);
+    auto *relu0 = op(g, "relu0", new ReluOp(), b0);
+    auto *r0 = result(g, "relu0_out", {2, 8, 8, 64}, relu0);
+    auto *b1 = conv_bn(g, r0, "1", "rp_", 3, 1);
+    auto *add = op(g, "add1", new ElementAddOp(), b1, shortcut);
+    auto *a1 = result(g, "add1_out", {2, 8, 8, 64}, add);
+    auto *relu1 = op(g, "relu1", new ReluOp(), a1);
+    auto *r1 = result(g, "relu1_out", {2, 8, 8, 64}, relu1);
+    classifier_tail(g, r1, "rp_");
+    return g;
+}
+
+IRGraph *build_convact() {
+    auto *g = new IRGraph();
+    std::vector<size_t> k3{3, 3}, s1{1, 1}, p1{1, 1, 1, 1};
+    auto *x = tensor(g, "image", {2, 8, 8, 64}, "ca_input.bin");
+    auto *cw = tensor(g, "conv_w", {64, 3, 3, 64}, "ca_conv_w.bin");
+    auto *cb = tensor(g, "conv_b", {64}, "ca_conv_b.bin");
+    auto *conv = op(g, "conv0", new Conv2dWithActivationOp(k3, s1, p1, SWC_ACTIVATION_RELU), x, cw, cb);
+    auto *c = result(g, "conv_out", {2, 8, 8, 64}, conv);
+    classifier_tail(g, c, "ca_");
+    return g;
+}
+
+// an op the kernel table has no entry for, in the middle of a forward pass
+IRGraph *build_badop() {
+    auto *g = new IRGraph();
+    auto *x = tensor(g, "x", {4, 16}, "bo_x.bin");
+    auto *y = tensor(g, "y", {4, 16}, "bo_y.bin");
+    auto *mul = op(g, "mul0", new ElementMulOp(), x, y);
+    auto *m = result(g, "prod", {4, 16}, mul);
+    auto *sm = op(g, "softmax", new MatrixSoftmaxOp(), m);
+    auto *probs = result(g, "probs", {4, 16}, sm);
+    g->findInOut();
+    g->updateTopology();
+    g->addDisplayTensorNodes(probs);
+    return g;
+}
+
 }  // namespace
 
 int main(int argc, char **argv) {
@@ -245,7 +328,10 @@ int main(int argc, char **argv) {
                  : base == "convnet" ? build_convnet()
                  : base == "resblock" ? build_resblock()
                  : base == "fcpair" ? build_fcpair()
-                 : base == "mlp_eval" ? build_mlp_eval() : nullptr;
+                 : base == "mlp_eval" ? build_mlp_eval()
+                 : base == "resproj" ? build_resproj()
+                 : base == "convact" ? build_convact()
+                 : base == "badop" ? build_badop() : nullptr;
     if (!g) {
         std::cerr << "unknown graph " << base << "\n";
         return 2;
@@ -308,5 +394,9 @@ int main(int argc, char **argv) {
     std::ofstream(out_dir + "/" + which + "_Graph.cpp") << code;
     std::ofstream(out_dir + "/" + which + "_Makefile") << gen.makefileText(repo);
     std::cerr << which << ": " << gen.arenaBytes() << " bytes of device arena, " << gen.fusedGroups() << " fused calls\n";
+    if (!gen.unsupportedOps().empty()) {
+        for (const std::string &u : gen.unsupportedOps()) std::cerr << "cannot emit: " << u << "\n";
+        return 3;  // the text written above holds an #error for each: it does not compile
+    }
     return 0;
 }

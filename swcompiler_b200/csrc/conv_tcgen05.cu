@@ -39,7 +39,6 @@
 // Restrictions: stride 1, group 1, iC a multiple of 64, oC a multiple of 32 and <= 256, kw <= 9, filter at
 // most 96 KiB in bf16, two windows fitting beside it.  Other shapes return SWCB200_ERR_UNSUPPORTED (the
 // strict kernel takes them).
-#include <stdlib.h>
 
 #include "tc_common.cuh"
 
@@ -49,9 +48,12 @@ using namespace tc;
 
 constexpr int BM = 128, BK = 64;
 constexpr int ROW_PIX = 64;              // pixels per window row in shared memory (8 KiB)
-constexpr int OUT_CHUNK_BYTES = 16384;   // staging slot of one 64-channel chunk of a tile (2 x cw pixels x 128 B, rounded up)
-constexpr int kThreads = 320;            // TMA producer, MMA issuer, 8 epilogue warps
-constexpr int kEpilogueThreads = 256;
+constexpr int kThreads = 384;            // window producer, two MMA issuers, residual producer, 8 epilogue warps
+constexpr int kIssuers = 2;
+constexpr int kResidualWarp = 3;
+constexpr int kFirstEpilogueWarp = 4;
+constexpr int kEpilogueGroups = 2;        // each of four warps (one per tensor-memory lane quarter)
+constexpr int kEpilogueGroupThreads = 128;
 constexpr int kMaxFilterBytes = 96 * 1024;
 constexpr int kMaxGroups = kMaxFilterBytes / (32 * 128);  // filter slices of [oC x 64] bf16 at the smallest oC (32)
 constexpr int kMaxSmem = 227 * 1024;
@@ -65,10 +67,12 @@ struct ConvParams {
     // tile = 2 output rows x 64 columns of which `cw` are stored; window = `hr` input rows x 64 pixels
     int hr, cw, col_blocks, row_blocks, chunk_bytes, stage_bytes;
     int out_tma, res_tma;   // staged epilogue / residual brought in by TMA
-    int out_tile_bytes;     // (OC / 64) * OUT_CHUNK_BYTES
+    int bw;                 // columns of a staged tile: min(cw, OW)
+    int out_chunk_bytes;    // staging slot of one 64-channel chunk of a tile: 2 x bw pixels x 128 B, rounded up to 1 KiB
+    int out_tile_bytes;     // (OC / 64) * out_chunk_bytes
     // MMA groups of a tile (one per filter tap and 64-channel chunk, 4 MMAs each), in filter-slice order:
     // a_off[g] = offset of the group's A operand inside a window, in 16-byte descriptor address units
-    int groups, lean_issue;
+    int groups;
     uint32_t a_off[kMaxGroups];
     const float *bias;
     const float *bn_scale, *bn_bias, *bn_mean, *bn_var;
@@ -147,6 +151,65 @@ __device__ __forceinline__ void store_global(const ConvParams &p, const float (&
     }
 }
 
+// Position of a CTA's successive tiles, kept without divisions: the tile index advances by a fixed step, so
+// image / row block / column block advance by fixed amounts with one carry each.
+struct TileWalk {
+    int n, rb, cb;
+    int sn, srb, scb, row_blocks, col_blocks;
+    __device__ __forceinline__ TileWalk(long long first, long long step, int row_blocks_, int col_blocks_)
+        : row_blocks(row_blocks_), col_blocks(col_blocks_) {
+        const long long per_image = (long long)row_blocks * col_blocks;
+        n = (int)(first / per_image);
+        int r = (int)(first - (long long)n * per_image);
+        rb = r / col_blocks;
+        cb = r - rb * col_blocks;
+        sn = (int)(step / per_image);
+        r = (int)(step - (long long)sn * per_image);
+        srb = r / col_blocks;
+        scb = r - srb * col_blocks;
+    }
+    __device__ __forceinline__ void advance() {
+        cb += scb;
+        rb += srb;
+        n += sn;
+        if (cb >= col_blocks) {
+            cb -= col_blocks;
+            rb++;
+        }
+        if (rb >= row_blocks) {
+            rb -= row_blocks;
+            n++;
+        }
+    }
+};
+
+// The MMA sequence of one tile with every descriptor offset a compile-time constant: tap (kx, ky), channel chunk kc
+// and the four K = 16 steps of a 64-channel chunk.  The tensor pipe takes a new N = 64 MMA every 48 cycles and runs
+// at most about one instruction ahead of the issuing thread, so anything that thread computes between two
+// tcgen05.mma (a table look-up, a division) lengthens the tile.
+template <int KH, int KW, int KC>
+__device__ __forceinline__ void issue_tile_unrolled(uint32_t d_tmem, uint32_t a_win, uint32_t b0, uint32_t b_step, uint32_t desc_hi,
+                                                    uint32_t idesc, bool leader) {
+    constexpr uint32_t chunk_step = (uint32_t)((KH + 1) * ROW_PIX * 128) >> 4;
+    if (leader) {
+#pragma unroll
+        for (int kx = 0; kx < KH; kx++)
+#pragma unroll
+            for (int ky = 0; ky < KW; ky++)
+#pragma unroll
+                for (int kc = 0; kc < KC; kc++) {
+                    const uint32_t g = (uint32_t)((kx * KW + ky) * KC + kc);
+                    const uint32_t a = a_win + (uint32_t)((kx * ROW_PIX + ky) * 8) + (uint32_t)kc * chunk_step;
+                    const uint32_t b = b0 + g * b_step;
+#pragma unroll
+                    for (int k = 0; k < 4; k++)
+                        umma_bf16(d_tmem, ((uint64_t)desc_hi << 32) | (a + 2 * k), ((uint64_t)desc_hi << 32) | (b + 2 * k), idesc,
+                                  (uint32_t)((g | (uint32_t)k) != 0));
+                }
+    }
+    __syncwarp();
+}
+
 __global__ void __launch_bounds__(kThreads, 1)
 conv_tc_kernel(const __grid_constant__ CUtensorMap tmIn, const __grid_constant__ CUtensorMap tmF,
                const __grid_constant__ CUtensorMap tmOut, const __grid_constant__ CUtensorMap tmRes, const ConvParams p) {
@@ -155,7 +218,8 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap tmIn, const __grid_constant__
     uint8_t *s_filter = smem;                                   // [taps*kchunks][OC x 128 B]
     uint8_t *s_a = smem + p.filter_bytes;                       // stages x kchunks x (hr x 64 pixels x 128 B)
     // 1 KiB of slack after the last window: the scrap columns of the last tap read kw-1 pixels past it
-    uint8_t *s_out = s_a + (size_t)p.stages * p.stage_bytes + 1024;             // 2 x out_tile_bytes (staged epilogue)
+    // windows, then (staged epilogue) 2 x out_tile_bytes, or 1 KiB of slack where there is no staging
+    uint8_t *s_out = s_a + (size_t)p.stages * p.stage_bytes + (p.out_tma ? 0 : 1024);
     uint8_t *s_res = s_out + (p.out_tma ? 2 * p.out_tile_bytes : 0);            // 2 x out_tile_bytes (TMA residual)
     float *s_alpha = reinterpret_cast<float *>(s_res + (p.res_tma ? 2 * p.out_tile_bytes : 0));  // [OC]
     float *s_beta = s_alpha + p.OC;                             // [OC]
@@ -169,8 +233,8 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap tmIn, const __grid_constant__
     uint32_t *tmem_holder = reinterpret_cast<uint32_t *>(res_empty + 2);
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    TIMING(const long long tk0 = clock64(); const unsigned long long tn0 = globaltimer_ns();)
     const int taps = p.kh * p.kw;
-    const int tiles_per_image = p.row_blocks * p.col_blocks;
     const int ochunks = p.OC >> 6;  // 64-channel chunks of the output (staged epilogue only)
 
     if (threadIdx.x == 0) {
@@ -184,11 +248,11 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap tmIn, const __grid_constant__
         }
         for (int b = 0; b < p.num_acc; b++) {
             mbar_init(&tmem_full[b], 1);
-            mbar_init(&tmem_empty[b], 8);  // one arrival per epilogue warp
+            mbar_init(&tmem_empty[b], 4);  // one arrival per warp of the epilogue group that reads it
         }
         for (int b = 0; b < 2; b++) {
-            mbar_init(&res_full[b], 1);
-            mbar_init(&res_empty[b], 8);
+            mbar_init(&res_full[b], 1);   // the residual tile has landed in residual buffer b
+            mbar_init(&res_empty[b], 4);  // one arrival per warp of the epilogue group that read it
         }
         mbar_init(filter_bar, 1);
         fence_barrier_init();
@@ -214,6 +278,7 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap tmIn, const __grid_constant__
     __syncthreads();
     tc_fence_after();
     const uint32_t tmem_base = *tmem_holder;
+    TIMING(if (blockIdx.x == 0 && threadIdx.x == 0) g_conv_timing[9] += clock64() - tk0;)
 
     if (warp == 0) {
         // ------------------------------------------------------------ TMA producer (warp-uniform loop, one elected lane issues)
@@ -228,10 +293,9 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap tmIn, const __grid_constant__
         __syncwarp();
         uint32_t issued = 0, ph = 0;
         int st = 0;
-        const uint32_t res_box_bytes = (uint32_t)(p.cw * 2 * 128);
-        for (long long tile = blockIdx.x; tile < p.num_tiles; tile += gridDim.x) {
-            const int n = (int)(tile / tiles_per_image), r = (int)(tile - (long long)n * tiles_per_image);
-            const int oh0 = (r / p.col_blocks) * 2, ow0 = (r % p.col_blocks) * p.cw;
+        TileWalk tw(blockIdx.x, gridDim.x, p.row_blocks, p.col_blocks);
+        for (long long tile = blockIdx.x; tile < p.num_tiles; tile += gridDim.x, tw.advance()) {
+            const int n = tw.n, oh0 = tw.rb * 2, ow0 = tw.cb * p.cw;
             TIMING(const long long tw0 = clock64();)
             bool ok = mbar_wait(&empty[st], ph ^ 1, p.status, kWaitEmpty);
             ok = __all_sync(0xffffffffu, ok);
@@ -244,20 +308,6 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap tmIn, const __grid_constant__
                     tma_load_4d(dst, &tmIn, &full[st], kc * BK, ow0 - p.pl, oh0 - p.pt, n);  // outside the image: zeros
             }
             __syncwarp();
-            if (p.res_tma) {
-                // the tile's residual, in the layout the epilogue stages its output in
-                const uint32_t b = issued & 1, rph = (issued >> 1) & 1;
-                ok = mbar_wait(&res_empty[b], rph ^ 1, p.status, kWaitEmpty);
-                ok = __all_sync(0xffffffffu, ok);
-                if (!ok) break;
-                if (leader) {
-                    mbar_expect_tx(&res_full[b], res_box_bytes * (uint32_t)ochunks);
-                    for (int oc = 0; oc < ochunks; oc++)
-                        tma_load_4d(s_res + (size_t)b * p.out_tile_bytes + (size_t)oc * OUT_CHUNK_BYTES, &tmRes, &res_full[b],
-                                    oc * 64, ow0, oh0, n);
-                }
-                __syncwarp();
-            }
             issued++;
             if (++st == p.stages) {
                 st = 0;
@@ -277,38 +327,68 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap tmIn, const __grid_constant__
                 s2--;
                 if (!mbar_wait(&full[s2], ph2, p.status, kWaitDrain)) break;
             }
-            if (p.res_tma)
+            mbar_wait(filter_bar, 0, p.status, kWaitDrain);
+        }
+        __syncwarp();
+    } else if (warp == kResidualWarp) {
+        // ------------------------------------------------------------ residual producer (only with a bf16 residual)
+        // A warp of its own, so that the input windows can run ahead of the epilogue by every free stage while the
+        // residual of a tile waits for its staging buffer (the one the epilogue of two tiles back is still reading).
+        if (p.res_tma) {
+            const bool leader = elect_one();
+            const uint32_t res_box_bytes = (uint32_t)(p.bw * 2 * 128);
+            uint32_t issued = 0;
+            TileWalk tw(blockIdx.x, gridDim.x, p.row_blocks, p.col_blocks);
+            for (long long tile = blockIdx.x; tile < p.num_tiles; tile += gridDim.x, tw.advance()) {
+                const int n = tw.n, oh0 = tw.rb * 2, ow0 = tw.cb * p.cw;
+                const uint32_t b = issued & 1, rph = (issued >> 1) & 1;
+                bool ok = mbar_wait(&res_empty[b], rph ^ 1, p.status, kWaitEmpty);
+                ok = __all_sync(0xffffffffu, ok);
+                if (!ok) break;
+                if (leader) {
+                    // in the layout the epilogue stages its output in
+                    mbar_expect_tx(&res_full[b], res_box_bytes * (uint32_t)ochunks);
+                    for (int oc = 0; oc < ochunks; oc++)
+                        tma_load_4d(s_res + (size_t)b * p.out_tile_bytes + (size_t)oc * p.out_chunk_bytes, &tmRes, &res_full[b],
+                                    oc * 64, ow0, oh0, n);
+                }
+                __syncwarp();
+                issued++;
+            }
+            // drain: the last fill of both buffers must have landed before the CTA may leave
+            if (lane == 0)
                 for (uint32_t back = 0; back < 2 && back < issued; back++) {
                     const uint32_t i = issued - 1 - back;
                     if (!mbar_wait(&res_full[i & 1], (i >> 1) & 1, p.status, kWaitDrain)) break;
                 }
-            mbar_wait(filter_bar, 0, p.status, kWaitDrain);
+            __syncwarp();
         }
-        __syncwarp();
-    } else if (warp == 1) {
-        // ------------------------------------------------------------ MMA issuer (warp-uniform loop, one elected lane issues)
+    } else if (warp <= kIssuers) {
+        // ------------------------------------------------------------ MMA issuers (warp-uniform loops, one elected lane issues)
+        // Two warps, each issuing the MMAs of every other tile into its own accumulators.  A tcgen05.mma holds
+        // the issuing thread while the pipe takes its operands, and what that thread executes between two of
+        // them (descriptor arithmetic, the moves into uniform registers) is not overlapped: a single issuer
+        // runs the pipe at 67 cycles per N = 64 MMA against the 48 its shared-memory reads take.  With a second
+        // warp the pipe takes one warp's MMA while the other prepares its next.
+        const uint32_t iw = (uint32_t)(warp - 1);
         const bool leader = elect_one();
         const uint32_t idesc = idesc_bf16_f32(BM, p.OC);
         bool ok = mbar_wait(filter_bar, 0, p.status, kWaitFull);
         ok = __all_sync(0xffffffffu, ok);
         tc_fence_after();
-        uint32_t it = 0, ph = 0;
-        int st = 0;
+        TIMING(if (blockIdx.x == 0 && lane == 0 && iw == 0) g_conv_timing[10] += clock64() - tk0;)
+        uint32_t it = iw, ph = (iw / (uint32_t)p.stages) & 1;
+        int st = (int)(iw % (uint32_t)p.stages);
+        uint32_t buf = iw % (uint32_t)p.num_acc, aph = (iw / (uint32_t)p.num_acc) & 1;
         // Descriptors differ from window to window and from tap to tap only in the 14-bit address field, the low
         // bits of the low word (no carry leaves the field: shared-memory addresses stay below 256 KiB).
-        // Two forms of the issue loop.  The tensor pipe finishes an N = 64 MMA every 48 cycles, and every
-        // instruction the issuing lane spends between two tcgen05.mma beyond that shows up in the tile time
-        // (measured: 90 cycles per MMA with the nested tap loops below, against 48 to 69 for bare loops in a
-        // stand-alone probe).  The lean form -- a table look-up and two 32-bit adds per group of four MMAs --
-        // issues the identical descriptor sequence; it is selected with SWCB200_CONV_LEAN_ISSUE=1 until it has
-        // been timed and checked on the hardware.
         const uint64_t da0 = smem_desc_sw128(smem_u32(s_a)), db0 = smem_desc_sw128(smem_u32(s_filter));
         const uint32_t desc_hi = (uint32_t)(da0 >> 32);  // same for A and B: stride 1024 B, version, 128-byte swizzle
         const uint32_t a_lo0 = (uint32_t)da0, b_lo0 = (uint32_t)db0;
         const uint32_t b_step = (uint32_t)((p.OC * 128) >> 4), stage_step = (uint32_t)(p.stage_bytes >> 4);
         auto desc = [desc_hi](uint32_t lo) { return ((uint64_t)desc_hi << 32) | lo; };
-        for (long long tile = blockIdx.x; tile < p.num_tiles && ok; tile += gridDim.x, it++) {
-            const uint32_t buf = it % p.num_acc, aph = (it / p.num_acc) & 1;
+        for (long long tile = blockIdx.x + (long long)iw * gridDim.x; tile < p.num_tiles && ok;
+             tile += (long long)kIssuers * gridDim.x, it += kIssuers) {
             TIMING(const long long tm0 = clock64();)
             ok = mbar_wait(&tmem_empty[buf], aph ^ 1, p.status, kWaitTmemEmpty);
             TIMING(const long long tm1 = clock64();)
@@ -318,39 +398,23 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap tmIn, const __grid_constant__
             if (!ok) break;
             tc_fence_after();
             const uint32_t d_tmem = tmem_base + buf * p.acc_stride;
-            if (p.lean_issue) {
+            if (p.kh == 3 && p.kw == 3 && p.kchunks == 1) {
+                issue_tile_unrolled<3, 3, 1>(d_tmem, a_lo0 + (uint32_t)st * stage_step, b_lo0, b_step, desc_hi, idesc, leader);
+            } else {
                 const uint32_t a_win = a_lo0 + (uint32_t)st * stage_step;
-                uint32_t b = b_lo0;
+                uint32_t b = b_lo0, a = a_win + p.a_off[0];
                 for (int g = 0; g < p.groups; g++, b += b_step) {
                     // group g: tap (kx, ky) and channel chunk kc; its A operand is the window read from (kx*64 + ky)
                     // pixels further on.  Advancing K by 16 elements = 32 bytes inside the swizzle row: +2 in the field.
-                    const uint32_t a = a_win + p.a_off[g];
+                    // The next group's offset is fetched before this group's MMAs are issued.
+                    const uint32_t a_next = a_win + p.a_off[g + 1 < p.groups ? g + 1 : g];
                     if (leader) {
                         umma_bf16(d_tmem, desc(a), desc(b), idesc, (uint32_t)(g != 0));
                         umma_bf16(d_tmem, desc(a + 2), desc(b + 2), idesc, 1u);
                         umma_bf16(d_tmem, desc(a + 4), desc(b + 4), idesc, 1u);
                         umma_bf16(d_tmem, desc(a + 6), desc(b + 6), idesc, 1u);
                     }
-                }
-            } else {
-                // the same sequence from nested tap loops with 64-bit descriptor arithmetic
-                const uint64_t da_stage = da0 + (uint64_t)st * (uint64_t)stage_step;
-                uint64_t db = db0;
-                for (int kx = 0; kx < p.kh; kx++) {
-                    for (int ky = 0; ky < p.kw; ky++) {
-                        uint64_t da = da_stage + (uint64_t)((kx * ROW_PIX + ky) * 8);  // one pixel = 128 B = 8 address units
-                        for (int kc = 0; kc < p.kchunks; kc++) {
-                            if (leader) {
-                                umma_bf16(d_tmem, da, db, idesc, (uint32_t)((kx | ky | kc) != 0));
-                                umma_bf16(d_tmem, da + 2, db + 2, idesc, 1u);
-                                umma_bf16(d_tmem, da + 4, db + 4, idesc, 1u);
-                                umma_bf16(d_tmem, da + 6, db + 6, idesc, 1u);
-                            }
-                            __syncwarp();
-                            da += (uint64_t)(p.chunk_bytes >> 4);
-                            db += (uint64_t)b_step;
-                        }
-                    }
+                    a = a_next;
                 }
             }
             if (leader) {
@@ -358,57 +422,76 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap tmIn, const __grid_constant__
                 umma_commit(&tmem_full[buf]);  // and the accumulator is complete
             }
             __syncwarp();
-            TIMING(if (blockIdx.x == 0 && lane == 0) {
+            TIMING(if (blockIdx.x == 0 && lane == 0 && iw == 0) {
                 g_conv_timing[1] += tm1 - tm0; g_conv_timing[2] += tm2 - tm1; g_conv_timing[3] += clock64() - tm2; g_conv_timing[4] += 1;
             })
-            if (++st == p.stages) {
-                st = 0;
+            // this warp's next tile is kIssuers further on (stages >= 2 and num_acc >= 2, so one wrap at most)
+            st += kIssuers;
+            if (st >= p.stages) {
+                st -= p.stages;
                 ph ^= 1;
             }
+            buf += kIssuers;
+            if (buf >= (uint32_t)p.num_acc) {
+                buf -= (uint32_t)p.num_acc;
+                aph ^= 1;
+            }
         }
-    } else {
-        // ------------------------------------------------------------ epilogue: one thread per output pixel and 32-channel pass
+        TIMING(if (blockIdx.x == 0 && lane == 0 && iw == 0) g_conv_timing[11] += clock64() - tk0;)
+    } else if (warp >= kFirstEpilogueWarp) {
+        // ------------------------------------------------------------ epilogue: two groups of four warps, alternate tiles
+        // A thread owns one output pixel (one tensor-memory lane) and walks its channels 64 at a time.  One tile's
+        // epilogue is a chain of latencies (accumulator ready -> tcgen05.ld -> arithmetic -> staging -> TMA store)
+        // about as long as the tile's MMAs, so two tiles are kept in flight: group g takes every other tile, with
+        // its own staging buffer, named barrier and bulk-store queue.  The accumulator is handed back as soon as
+        // the last tcgen05.ld has returned, before the arithmetic.
+        const int group = (warp - kFirstEpilogueWarp) >> 2;
         const int quarter = warp & 3;                 // the tensor-memory lane quarter this warp may read
-        const int chalf = (warp - 2) >> 2;            // warps 2-5 take channels [0,32) of every 64, warps 6-9 [32,64)
         const int row = quarter * 32 + lane;          // row of the tile = TMEM lane
         const int trow = row >> 6, tcol = row & 63;   // position inside the 2 x 64 tile
-        const int q = trow * p.cw + tcol;             // pixel's row in the staged tile (box {64 ch, cw, 2, 1})
+        const int q = trow * p.bw + tcol;             // pixel's row in the staged tile (box {64 ch, bw, 2, 1})
         const uint32_t swz = (uint32_t)(q & 7);       // 128-byte swizzle: 16-byte chunk index ^ (row & 7)
-        const bool issuer = warp == 2 && lane == 0;   // issues the tile's TMA stores
-        const int c_first = chalf * 32;
-        uint32_t it = 0;
-        for (long long tile = blockIdx.x; tile < p.num_tiles; tile += gridDim.x, it++) {
-            const uint32_t buf = it % p.num_acc, aph = (it / p.num_acc) & 1;
-            const uint32_t sb = it & 1, sph = (it >> 1) & 1;  // staging buffer of this tile
-            const int n = (int)(tile / tiles_per_image), r = (int)(tile - (long long)n * tiles_per_image);
-            const int oh0 = (r / p.col_blocks) * 2, ow0 = (r % p.col_blocks) * p.cw;
+        const bool issuer = ((warp - kFirstEpilogueWarp) & 3) == 0 && lane == 0;  // issues the group's TMA stores
+        const int bar_id = 1 + group;
+        const uint32_t lane_base = tmem_base + ((uint32_t)(quarter * 32) << 16);
+        uint8_t *const so_tile = s_out + (size_t)group * p.out_tile_bytes;
+        const uint8_t *const sr_tile = s_res + (size_t)group * p.out_tile_bytes;
+        uint32_t buf = (uint32_t)group % (uint32_t)p.num_acc, aph = ((uint32_t)group / (uint32_t)p.num_acc) & 1, sph = 0;
+        TileWalk tw(blockIdx.x + (long long)group * gridDim.x, (long long)kEpilogueGroups * gridDim.x, p.row_blocks, p.col_blocks);
+        for (long long tile = blockIdx.x + (long long)group * gridDim.x; tile < p.num_tiles;
+             tile += (long long)kEpilogueGroups * gridDim.x, tw.advance()) {
+            const int n = tw.n, oh0 = tw.rb * 2, ow0 = tw.cb * p.cw;
             const int oh = oh0 + trow, ow = ow0 + tcol;
             const bool valid = tcol < p.cw && oh < p.OH && ow < p.OW;
+            const bool skip = p.out_tma ? tcol >= p.bw : !valid;  // staged tiles are clipped by the TMA store
             const size_t pix = ((size_t)n * p.OH + oh) * p.OW + ow;
             bool ok = true;
             TIMING(const long long te0 = clock64();)
+            if (p.out_tma) {
+                // the group's previous store must have finished reading the staging buffer before anyone refills it
+                if (issuer) bulk_wait_read_all();
+                named_barrier(bar_id, kEpilogueGroupThreads);
+            }
             if (lane == 0) {
                 ok = mbar_wait(&tmem_full[buf], aph, p.status, kWaitTmemFull);
-                if (ok && p.res_tma) ok = mbar_wait(&res_full[sb], sph, p.status, kWaitFull);
+                if (ok && p.res_tma) ok = mbar_wait(&res_full[group], sph, p.status, kWaitFull);
             }
             ok = __shfl_sync(0xffffffffu, ok, 0);
             TIMING(const long long te1 = clock64();)
             if (!ok) break;
             tc_fence_after();
-            for (int c0 = c_first; c0 < p.OC; c0 += 64) {
-                uint32_t acc[32];
-                __syncwarp();
-                tmem_ld_32x32(tmem_base + ((uint32_t)(quarter * 32) << 16) + buf * p.acc_stride + c0, acc);
-                tmem_ld_wait();
-                if (p.out_tma ? tcol >= p.cw : !valid) continue;
+
+            // one 32-channel pass: affine, residual, ReLU, then staging (or a direct store)
+            auto pass = [&](const uint32_t (&acc)[32], int c0) {
+                if (skip) return;
                 float v[32];
                 apply_affine(acc, s_alpha, s_beta, c0, v);
                 // this pass's 64 bytes of the pixel's 128-byte row in a staged 64-channel chunk: 16-byte chunks ch16 .. ch16+3
-                const uint32_t row_off = (uint32_t)(c0 >> 6) * OUT_CHUNK_BYTES + (uint32_t)q * 128u;
+                const uint32_t row_off = (uint32_t)(c0 >> 6) * p.out_chunk_bytes + (uint32_t)q * 128u;
                 const uint32_t ch16 = (uint32_t)(c0 & 63) >> 3;
                 if (p.residual) {
                     if (p.res_tma) {
-                        const uint8_t *rr = s_res + (size_t)sb * p.out_tile_bytes + row_off;
+                        const uint8_t *rr = sr_tile + row_off;
 #pragma unroll
                         for (int j = 0; j < 4; j++)
                             add_bf16x8(v + 8 * j, *reinterpret_cast<const uint4 *>(rr + (((ch16 + j) ^ swz) << 4)));
@@ -418,38 +501,55 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap tmIn, const __grid_constant__
                 }
                 if (p.relu) {
 #pragma unroll
-                    for (int j = 0; j < 32; j++) v[j] = (v[j] > 0.f) ? v[j] : 0.f;
+                    for (int j = 0; j < 32; j++) v[j] = fmaxf(v[j], 0.f);
                 }
                 if (p.out_tma) {
-                    uint8_t *so = s_out + (size_t)sb * p.out_tile_bytes + row_off;
+                    uint8_t *so = so_tile + row_off;
 #pragma unroll
                     for (int j = 0; j < 4; j++) *reinterpret_cast<uint4 *>(so + (((ch16 + j) ^ swz) << 4)) = pack_bf16x8(v + 8 * j);
                 } else {
                     store_global(p, v, pix, c0);
                 }
+            };
+            const uint32_t acc_base = lane_base + buf * p.acc_stride;
+            for (int c0 = 0; c0 < p.OC; c0 += 64) {
+                uint32_t acc0[32], acc1[32];
+                const bool two = c0 + 32 < p.OC;  // warp-uniform
+                __syncwarp();
+                tmem_ld_32x32(acc_base + c0, acc0);
+                if (two) tmem_ld_32x32(acc_base + c0 + 32, acc1);
+                tmem_ld_wait();
+                if (c0 + 64 >= p.OC) {
+                    // every column of the accumulator is in registers: the MMA issuer may have it back
+                    tc_fence_before();
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive(&tmem_empty[buf]);
+                }
+                pass(acc0, c0);
+                if (two) pass(acc1, c0 + 32);
             }
-            tc_fence_before();
             __syncwarp();
-            TIMING(if (blockIdx.x == 0 && lane == 0 && warp == 2) { g_conv_timing[5] += te1 - te0; g_conv_timing[6] += clock64() - te1; })
-            if (lane == 0) {
-                mbar_arrive(&tmem_empty[buf]);
-                if (p.res_tma) mbar_arrive(&res_empty[sb]);
-            }
+            TIMING(if (blockIdx.x == 0 && lane == 0 && warp == kFirstEpilogueWarp) { g_conv_timing[5] += te1 - te0; g_conv_timing[6] += clock64() - te1; })
+            if (p.res_tma && lane == 0) mbar_arrive(&res_empty[group]);
             if (p.out_tma) {
-                // The staged tile leaves by TMA.  Before the barrier the issuing thread makes sure that every
-                // earlier store has finished reading shared memory: past the barrier the other staging buffer
-                // (read by the previous tile's store) is free for the next tile.
+                // the staged tile leaves by TMA once the whole group has written its part
                 fence_proxy_async();
-                if (issuer) bulk_wait_read_all();
-                named_barrier(1, kEpilogueThreads);
+                named_barrier(bar_id, kEpilogueGroupThreads);
                 if (issuer) {
-                    const uint8_t *so = s_out + (size_t)sb * p.out_tile_bytes;
-                    for (int oc = 0; oc < ochunks; oc++) tma_store_4d(&tmOut, so + (size_t)oc * OUT_CHUNK_BYTES, oc * 64, ow0, oh0, n);
+                    for (int oc = 0; oc < ochunks; oc++) tma_store_4d(&tmOut, so_tile + (size_t)oc * p.out_chunk_bytes, oc * 64, ow0, oh0, n);
                     bulk_commit_group();
                 }
             }
+            buf += kEpilogueGroups;
+            if (buf >= (uint32_t)p.num_acc) {
+                buf -= (uint32_t)p.num_acc;
+                aph ^= 1;
+            }
+            sph ^= 1;
         }
+        TIMING(if (blockIdx.x == 0 && warp == kFirstEpilogueWarp && lane == 0) g_conv_timing[12] += clock64() - tk0;)
         if (p.out_tma && issuer) bulk_wait_all();  // shared memory stays valid until the last store has read it
+        TIMING(if (blockIdx.x == 0 && warp == kFirstEpilogueWarp && lane == 0) g_conv_timing[13] += clock64() - tk0;)
     }
 
     __syncwarp();
@@ -459,6 +559,7 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap tmIn, const __grid_constant__
         tc_fence_after();
         tmem_dealloc(tmem_base, (uint32_t)p.tmem_cols);
     }
+    TIMING(if (blockIdx.x == 0 && threadIdx.x == 0) { g_conv_timing[7] += clock64() - tk0; g_conv_timing[8] += (long long)(globaltimer_ns() - tn0); })
 }
 
 }  // namespace
@@ -473,16 +574,6 @@ SWC_EXPORT int swcb200_debug_conv_timing(long long *out16) {
     return SWCB200_OK;
 }
 #endif
-
-// SWCB200_CONV_LEAN_ISSUE=1 in the environment selects the table-driven issue loop (see the kernel).
-static bool swc_conv_lean_issue() {
-    static int v = -1;
-    if (v < 0) {
-        const char *e = getenv("SWCB200_CONV_LEAN_ISSUE");
-        v = (e && e[0] == '1') ? 1 : 0;
-    }
-    return v == 1;
-}
 
 // input/filter bf16; output and residual bf16 or fp32
 int swc_conv_tc(swcb200_ctx *ctx, void *output, int out_dtype, const void *input, const void *filt, const float *bias,
@@ -524,18 +615,23 @@ int swc_conv_tc(swcb200_ctx *ctx, void *output, int out_dtype, const void *input
     p.res_is_f32 = res_dtype == SWCB200_F32;
     p.status = ctx->dev_status;
 
-    // shared-memory plan: filter | windows | 1 KiB slack | output staging | residual staging | coefficients | barriers
+    // shared-memory plan: filter | windows | output staging, residual staging (or 1 KiB slack) | coefficients | barriers
     p.hr = p.kh + 1;
     p.cw = ROW_PIX - (p.kw - 1);
     p.chunk_bytes = p.hr * ROW_PIX * 128;
     p.stage_bytes = p.chunk_bytes * p.kchunks;
-    p.out_tile_bytes = (p.OC / 64) * OUT_CHUNK_BYTES;
-    const int fixed = p.filter_bytes + 1024 + 2 * p.OC * 4 + 256 + 1024;
+    p.bw = p.OW < p.cw ? p.OW : p.cw;
+    p.out_chunk_bytes = (2 * p.bw * 128 + 1023) & ~1023;  // 1 KiB granules keep every chunk on a swizzle-pattern boundary
+    p.out_tile_bytes = (p.OC / 64) * p.out_chunk_bytes;
+    const int fixed = p.filter_bytes + 2 * p.OC * 4 + 256 + 1024;  // filter, coefficients, barriers, alignment of the base
     p.out_tma = !p.out_is_f32 && p.OC % 64 == 0;
     p.res_tma = p.out_tma && p.residual != nullptr && !p.res_is_f32;
-    auto stages_for = [&](int out_tma, int res_tma) {
-        return (kMaxSmem - fixed - (out_tma ? 2 * p.out_tile_bytes : 0) - (res_tma ? 2 * p.out_tile_bytes : 0)) / p.stage_bytes;
+    // the 1 KiB of slack after the windows (scrap columns of the last tap read up to kw-1 pixels past them) is only
+    // needed where no staging buffer follows
+    auto smem_for = [&](int stages, int out_tma, int res_tma) {
+        return fixed + stages * p.stage_bytes + (out_tma ? 2 * p.out_tile_bytes : 1024) + (res_tma ? 2 * p.out_tile_bytes : 0);
     };
+    auto stages_for = [&](int out_tma, int res_tma) { return (kMaxSmem - smem_for(0, out_tma, res_tma)) / p.stage_bytes; };
     if (stages_for(p.out_tma, p.res_tma) < 2) p.res_tma = 0;
     if (stages_for(p.out_tma, p.res_tma) < 2) p.out_tma = 0;
     p.stages = stages_for(p.out_tma, p.res_tma);
@@ -546,7 +642,6 @@ int swc_conv_tc(swcb200_ctx *ctx, void *output, int out_dtype, const void *input
     p.row_blocks = (p.OH + 1) / 2;
     p.col_blocks = (p.OW + p.cw - 1) / p.cw;
     p.num_tiles = (long long)p.N * p.row_blocks * p.col_blocks;
-    p.lean_issue = swc_conv_lean_issue();
     p.groups = p.kh * p.kw * p.kchunks;  // <= kMaxGroups: the filter fits in kMaxFilterBytes and oC >= 32
     SWC_REQUIRE(ctx, p.groups <= kMaxGroups, SWCB200_ERR_UNSUPPORTED, "conv2d_bf16: %d filter slices", p.groups);
     for (int kx = 0, g = 0; kx < p.kh; kx++)
@@ -576,7 +671,7 @@ int swc_conv_tc(swcb200_ctx *ctx, void *output, int out_dtype, const void *input
         // output (and residual) seen tile by tile: 64 channels x cw columns x 2 rows
         uint64_t dims[4] = {(uint64_t)p.OC, (uint64_t)p.OW, (uint64_t)p.OH, (uint64_t)p.N};
         uint64_t str[4] = {2, (uint64_t)p.OC * 2, (uint64_t)p.OW * p.OC * 2, (uint64_t)p.OH * p.OW * p.OC * 2};
-        uint32_t box[4] = {64, (uint32_t)p.cw, 2, 1};
+        uint32_t box[4] = {64, (uint32_t)p.bw, 2, 1};
         int rc = tc::make_tmap_bf16(ctx, &tmOut, output, 4, dims, str, box);
         if (rc) return rc;
         if (p.res_tma) {
@@ -588,8 +683,7 @@ int swc_conv_tc(swcb200_ctx *ctx, void *output, int out_dtype, const void *input
         SWC_CUDA(ctx, cudaFuncSetAttribute(conv_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kMaxSmem));
         ctx->conv_attr_set = true;
     }
-    const size_t smem = (size_t)fixed + (size_t)p.stages * p.stage_bytes + (p.out_tma ? 2 * p.out_tile_bytes : 0) +
-                        (p.res_tma ? 2 * p.out_tile_bytes : 0);
+    const size_t smem = (size_t)smem_for(p.stages, p.out_tma, p.res_tma);
     unsigned grid = (unsigned)(p.num_tiles < ctx->sm_count ? p.num_tiles : ctx->sm_count);
     conv_tc_kernel<<<grid, kThreads, smem, ctx->stream>>>(tmIn, tmF, tmOut, tmRes, p);
     return swc_check_launch(ctx, "conv2d_bf16");

@@ -103,7 +103,8 @@ def conv_roles():
         print(json.dumps({"kernel": "conv2d_bf16 3x3 64->64 [256,56,56,64]", "residual": res is not None, "tiles_cta0": tiles,
                           "cycles_per_tile": {"producer_wait_window_free": t[0] / tiles, "issuer_wait_accumulator": t[1] / tiles,
                                               "issuer_wait_window": t[2] / tiles, "issuer_issue": t[3] / tiles,
-                                              "epilogue_wait": t[5] / tiles, "epilogue_work": t[6] / tiles}}))
+                                              "epilogue_wait": t[5] / tiles, "epilogue_work": t[6] / tiles},
+                          "cta0_cycles": t[7], "cta0_ns": t[8], "ghz": t[7] / max(1, t[8]), "marks": {"prologue_done": t[9], "filter_ready": t[10], "issuer_done": t[11], "epi_loop_done": t[12], "stores_done": t[13]}}))
 
 
 def main():

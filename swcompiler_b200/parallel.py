@@ -47,7 +47,7 @@ def take_shard(full: torch.Tensor, axis: int, rank: int, p: int) -> torch.Tensor
 def strategy_fc_pair(p: int):
     """Strategy labels of the model-parallel FC -> ReLU -> FC chain, as the reference's tiling pass writes them
     (src/parallel/parallelGen.cpp:23-84; [inputs..., outputs...] axis per operand, the labels the sample program
-    codegen/emitted/fcpair_mp2_Graph.cpp was lowered from): FC1 split by output columns, ReLU on the column shard,
+    the fcpair_mp2 sample of gen_driver.cpp was lowered from): FC1 split by output columns, ReLU on the column shard,
     FC2 split by input rows with a partial-sum output that a Reduce node joins."""
     return {"fc1": (REPLICATE, 1, 1), "relu": (1, 1), "fc2": (1, 0, PARTIAL), "join": "reduce"}
 

@@ -1,4 +1,5 @@
-"""Helpers shared by the CPU and GPU tests of the emitted programs (swcompiler_b200/codegen/emitted)."""
+"""Helpers shared by the CPU and GPU tests of the emitted programs (tests/golden/emitted: what B200Codegen printed for
+the sample graphs of gen_driver.cpp, kept as fixtures because the GPU machine has no reference checkout to print them)."""
 import os
 import re
 import shutil
@@ -7,7 +8,12 @@ import subprocess
 import numpy as np
 
 ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
-EMITTED = os.path.join(ROOT, "swcompiler_b200", "codegen", "emitted")
+EMITTED = os.path.join(ROOT, "tests", "golden", "emitted")
+
+
+def reference_root() -> str:
+    """Where a checkout of the reference is looked for: $REFERENCE_ROOT, else a folder `reference` beside the repository."""
+    return os.environ.get("REFERENCE_ROOT") or os.path.join(os.path.dirname(ROOT), "reference")
 CUDA = os.environ.get("CUDA_HOME", "/usr/local/cuda")
 
 
@@ -82,6 +88,64 @@ def resblock_oracle(impl, t, rnd=lambda a: a):
     h = rnd(impl.relu_f(impl.vecAdd_f(h.reshape(-1), x.reshape(-1)).reshape(h.shape)))
     h = impl.maxpool_f(h, (2, 2), (2, 2), (0, 0, 0, 0))
     return impl.matrixSoftmax_f(impl.fc(h, rnd(t["rb_fc_w.bin"]), t["rb_fc_b.bin"]))
+
+
+def _conv_bn_files(r, t, prefix, tag, k):
+    f = np.float32
+    t[f"{prefix}conv{tag}_w.bin"] = (r.standard_normal((64, k, k, 64)) * np.sqrt(2.0 / (k * k * 64))).astype(f)
+    t[f"{prefix}conv{tag}_b.bin"] = (r.standard_normal(64) * 0.1).astype(f)
+    t[f"{prefix}bn{tag}_scale.bin"] = r.uniform(0.5, 1.5, 64).astype(f)
+    t[f"{prefix}bn{tag}_bias.bin"] = (r.standard_normal(64) * 0.1).astype(f)
+    t[f"{prefix}bn{tag}_mean.bin"] = (r.standard_normal(64) * 0.1).astype(f)
+    t[f"{prefix}bn{tag}_var.bin"] = r.uniform(0.5, 1.5, 64).astype(f)
+
+
+def resproj_inputs(seed=93):
+    """Files of the projection-shortcut block (gen_driver resproj): [2,8,8,64] image; main branch two 3x3 convolutions
+    with batch-norm, shortcut a 1x1 convolution with batch-norm; FC 1024->10."""
+    r = np.random.default_rng(seed)
+    f = np.float32
+    t = {"rp_input.bin": r.standard_normal((2, 8, 8, 64)).astype(f),
+         "rp_fc_w.bin": (r.standard_normal((1024, 10)) * 0.05).astype(f),
+         "rp_fc_b.bin": (r.standard_normal(10) * 0.1).astype(f)}
+    for tag, k in (("S", 1), ("0", 3), ("1", 3)):
+        _conv_bn_files(r, t, "rp_", tag, k)
+    return t
+
+
+def resproj_oracle(impl, t, rnd=lambda a: a):
+    x = rnd(t["rp_input.bin"])
+
+    def conv_bn(h, tag, k, pad):
+        h = impl.conv2d_f(h, rnd(t[f"rp_conv{tag}_w.bin"]), t[f"rp_conv{tag}_b.bin"], (k, k), (1, 1), (pad,) * 4)
+        return impl.batchnormalization_f(h, t[f"rp_bn{tag}_mean.bin"], t[f"rp_bn{tag}_var.bin"], t[f"rp_bn{tag}_scale.bin"],
+                                         t[f"rp_bn{tag}_bias.bin"], 1e-5)
+
+    shortcut = rnd(conv_bn(x, "S", 1, 0))
+    h = rnd(impl.relu_f(conv_bn(x, "0", 3, 1)))
+    h = conv_bn(h, "1", 3, 1)
+    h = rnd(impl.relu_f(impl.vecAdd_f(h.reshape(-1), shortcut.reshape(-1)).reshape(h.shape)))
+    h = impl.maxpool_f(h, (2, 2), (2, 2), (0, 0, 0, 0))
+    return impl.matrixSoftmax_f(impl.fc(h, rnd(t["rp_fc_w.bin"]), t["rp_fc_b.bin"]))
+
+
+def convact_inputs(seed=95):
+    """Files of the Conv2dWithActivation graph (gen_driver convact)."""
+    r = np.random.default_rng(seed)
+    f = np.float32
+    return {"ca_input.bin": r.standard_normal((2, 8, 8, 64)).astype(f),
+            "ca_conv_w.bin": (r.standard_normal((64, 3, 3, 64)) * np.sqrt(2.0 / 576)).astype(f),
+            "ca_conv_b.bin": (r.standard_normal(64) * 0.1).astype(f),
+            "ca_fc_w.bin": (r.standard_normal((1024, 10)) * 0.05).astype(f),
+            "ca_fc_b.bin": (r.standard_normal(10) * 0.1).astype(f)}
+
+
+def convact_oracle(impl, t, rnd=lambda a: a):
+    """conv2d_f then relu_f: the chain Conv2dWithActivationOp stands for."""
+    h = impl.conv2d_f(rnd(t["ca_input.bin"]), rnd(t["ca_conv_w.bin"]), t["ca_conv_b.bin"], (3, 3), (1, 1), (1, 1, 1, 1))
+    h = rnd(impl.relu_f(h))
+    h = impl.maxpool_f(h, (2, 2), (2, 2), (0, 0, 0, 0))
+    return impl.matrixSoftmax_f(impl.fc(h, rnd(t["ca_fc_w.bin"]), t["ca_fc_b.bin"]))
 
 
 def write_mnist8_records(dirname, wrong=(3,)):

@@ -6,9 +6,9 @@ import subprocess
 
 import pytest
 
-from codegen_util import EMITTED, compile_emitted
+from codegen_util import EMITTED, compile_emitted, reference_root
 
-REF = os.environ.get("REFERENCE_ROOT", "/root/reference")
+REF = reference_root()
 
 
 def _calls(which):
@@ -205,6 +205,36 @@ def test_emitted_call_sequences_compute_the_right_thing_on_the_cpu(oracle, golde
     assert np.abs(fused - resblock_oracle(oracle, t)).max() <= 5e-2
 
 
+def test_projection_shortcut_block_and_conv_with_activation(oracle, tmp_path):
+    """Two convolution chains meet at one ElementAdd (a residual block whose shortcut is a 1x1 convolution).  The fused
+    plan must give the add to the chain that is printed LAST, with the other chain's result -- already computed -- as the
+    skip operand; and Conv2dWithActivationOp is conv2d_f + relu_f unfused, one conv2d_bf16 with the ReLU flag fused."""
+    import numpy as np
+
+    import cases
+    from codegen_util import convact_inputs, convact_oracle, resproj_inputs, resproj_oracle
+    from conftest import bits
+    calls = _calls("resproj_fused")
+    assert calls.count("conv2d_bf16") == 3 and "vecAdd_f" not in calls and "relu_f" not in calls
+    text = open(os.path.join(EMITTED, "resproj_fused_Graph.cpp")).read()
+    assert "{bnS_scale, bnS_bias, bnS_mean, bnS_var, 1e-05f, nullptr, 0}" in text             # shortcut: conv + bn only
+    assert "{bn1_scale, bn1_bias, bn1_mean, bn1_var, 1e-05f, bnS_out_bf16, 1}" in text        # main branch takes add + relu
+    assert text.index("convS_epilogue") < text.index("conv1_epilogue")                         # the skip exists by then
+    t = resproj_inputs()
+    assert np.array_equal(bits(_interpret("resproj", t, oracle, tmp_path)["probs"]), bits(resproj_oracle(oracle, t)))
+    fused = _interpret("resproj_fused", t, oracle, tmp_path)["probs"]
+    assert np.abs(fused - resproj_oracle(oracle, t, rnd=cases.bf16_round)).max() <= 1e-3
+    assert np.abs(fused - resproj_oracle(oracle, t)).max() <= 5e-2
+
+    assert _calls("convact")[1:4] == ["conv2d_f", "relu_f", "maxpool_f"]
+    assert _calls("convact_fused").count("conv2d_bf16") == 1 and "relu_f" not in _calls("convact_fused")
+    assert "{nullptr, nullptr, nullptr, nullptr, 0.0f, nullptr, 1}" in open(os.path.join(EMITTED, "convact_fused_Graph.cpp")).read()
+    t = convact_inputs()
+    assert np.array_equal(bits(_interpret("convact", t, oracle, tmp_path)["probs"]), bits(convact_oracle(oracle, t)))
+    fused = _interpret("convact_fused", t, oracle, tmp_path)["probs"]
+    assert np.abs(fused - convact_oracle(oracle, t, rnd=cases.bf16_round)).max() <= 1e-3
+
+
 from swcompiler_b200.codegen.build_codegen import PROGRAMS as ALL_PROGRAMS  # noqa: E402
 
 
@@ -217,6 +247,21 @@ def test_emitted_programs_compile_and_link(which, tmp_path):
         env = dict(os.environ, SWCB200_RANK="0", SWCB200_NRANKS=str(ranks), SWCB200_ID_FILE=os.path.join(str(tmp_path), "id"))
         r = subprocess.run([exe], capture_output=True, text=True, cwd=str(tmp_path), env=env)
         assert r.returncode != 0 and "no sm_100 CUDA device" in r.stderr   # fails loudly, no CPU path
+
+
+@pytest.mark.skipif(not os.path.exists(os.path.join(REF, "include", "SWC.h")), reason="no reference checkout")
+def test_generator_refuses_an_op_outside_the_kernel_table(tmp_path):
+    """A graph with an ElementMul node: the generator records it, gen_driver exits with code 3, and the text it wrote
+    holds an #error, so it cannot be compiled into a program that skips the op."""
+    from swcompiler_b200.codegen import build_codegen as bc
+    exe = bc.build(REF)
+    r = subprocess.run([exe, "badop", str(tmp_path), "x"], cwd=bc.BUILD, capture_output=True, text=True)
+    assert r.returncode == 3 and "cannot emit: mul0 : ElementMul" in r.stderr
+    text = open(os.path.join(str(tmp_path), "badop_Graph.cpp")).read()
+    assert '#error "swc_b200: cannot emit mul0 : ElementMul' in text
+    r = subprocess.run(["g++", "-fsyntax-only", "-I" + os.path.join(os.path.dirname(EMITTED), "..", "..", "include"),
+                        "-I/usr/local/cuda/include", os.path.join(str(tmp_path), "badop_Graph.cpp")], capture_output=True, text=True)
+    assert r.returncode != 0 and "cannot emit" in r.stderr
 
 
 @pytest.mark.skipif(not os.path.exists(os.path.join(REF, "include", "SWC.h")), reason="no reference checkout")

@@ -117,7 +117,6 @@ def _fc_pair(rank, world):
     comm.close()
 
 
-@pytest.mark.xfail(strict=False, reason="first run on GPUs pending")
 def test_two_gpus_transform_of_4d_tensors():
     if torch.cuda.device_count() < 2:
         pytest.skip("needs two GPUs")

@@ -1,10 +1,7 @@
 """GPU: the programs the emit-time fusion planner prints (tensor-core precision, one call per fused chain), the
 residual-block graph printed op by op in strict precision, and the programs printed for graphs the reference's tiling
 passes partitioned over two ranks (one process per GPU, Scatter / Gather / Reduce over NCCL) -- compiled with g++ on
-the spot and run as separate processes.
-
-These programs were written without a GPU at hand; until they have run once on a B200 they are marked as expected
-failures (non-strict), so that a first-run surprise is reported without ending a run that stops at the first failure."""
+the spot and run as separate processes."""
 import os
 import shutil
 import subprocess
@@ -16,7 +13,7 @@ import cases
 from codegen_util import (compile_emitted, convnet_inputs, convnet_oracle, parse_printed, resblock_inputs, resblock_oracle)
 from conftest import GOLDEN
 
-pytestmark = [pytest.mark.gpu, pytest.mark.xfail(strict=False, reason="first run on a GPU pending")]
+pytestmark = pytest.mark.gpu
 
 
 def _run(which, tmp_path, files):

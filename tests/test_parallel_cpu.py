@@ -193,7 +193,7 @@ def _fuzz_program(rank, world):
         assert np.allclose(out["probs"], want, rtol=1e-4, atol=1e-5), np.abs(out["probs"] - want).max()
 
 
-@pytest.mark.skipif(not os.path.exists(os.path.join(os.environ.get("REFERENCE_ROOT", "/root/reference"), "include", "SWC.h")),
+@pytest.mark.skipif(not os.path.exists(os.path.join(__import__("codegen_util").reference_root(), "include", "SWC.h")),
                     reason="no reference checkout")
 @pytest.mark.parametrize("which", ["mlp8_rp2", "mlp8_rp2_fused", "resblock_rp2"])
 def test_whatever_partitioning_the_reference_draws(which, tmp_path):
@@ -207,7 +207,7 @@ def test_whatever_partitioning_the_reference_draws(which, tmp_path):
 
     from codegen_util import resblock_inputs
     from swcompiler_b200.codegen import build_codegen as bc
-    exe = bc.build(os.environ.get("REFERENCE_ROOT", "/root/reference"))
+    exe = bc.build(__import__("codegen_util").reference_root())
     done = 0
     for draw in range(12):
         d = tmp_path / str(draw)

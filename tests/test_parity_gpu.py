@@ -52,7 +52,6 @@ def test_all_cases_against_reference_golden(gpu_out, golden):
             assert np.all(both_nan | (np.abs(v - ref) <= 1e-5 * np.abs(ref) + 1e-30)), k
 
 
-@pytest.mark.xfail(strict=False, reason="first run on a GPU pending")
 def test_accuracy_counters(gpu, golden):
     """swcb200_accuracy_i against the reference's accuracy_i: integer counters, bit for bit, also when accumulated
     over two batches."""
