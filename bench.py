@@ -1,17 +1,23 @@
 #!/usr/bin/env python
-"""Benchmark of the inference forward path on B200: the wide-MLP configuration.
+"""Benchmark of the inference forward path on B200.
 
-    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--workload all|widemlp|...]
 
-Workload (synthetic, seeded): X [65536, 4096] bf16 ~ N(0,1); 4 x (FC 4096->4096, bf16 weights ~ N(0, 1/4096),
-fp32 bias, fp32 accumulation, ReLU); FC 4096->1000; softmax.  One step = one forward pass over the whole
-batch; with N GPUs the batch is split evenly over the ranks (strong scaling) and the probabilities are
-gathered on rank 0.  Prints ONE JSON line on rank 0.
+Headline workload (synthetic, seeded): the wide MLP -- X [65536, 4096] bf16 ~ N(0,1); 4 x (FC 4096->4096, bf16 weights
+~ N(0, 1/4096), fp32 bias, fp32 accumulation, ReLU); FC 4096->1000; softmax.  One step = one forward pass over the
+whole batch; with N GPUs the batch is split evenly over the ranks (strong scaling) and the probabilities are gathered
+on rank 0.  Rank 0 prints ONE JSON line.
 
-`value` is samples/s with the inputs already resident in HBM; `e2e` is the same forward pass called with
-pinned HOST buffers (host->device copy of X and device->host copy of the probabilities inside the timed
-region).  `--impl reference` times the reference's own scalar CPU kernels on a bounded slice of the same
-workload, one slice per host thread.
+`value` is samples/s with the inputs already resident in HBM; `e2e` is the same program called with pinned HOST
+buffers (host->device copy of X, the Gather, and the device->host copy of the gathered probabilities inside the timed
+region).  `--impl reference` times the reference's own scalar CPU kernels on a bounded slice of the same workload,
+one slice per host thread.
+
+With `--workload all` (the default) the same line also carries, under `workloads`, the other configurations --
+`resstage` (the batch-split ResNet-style conv stage), `fcpair` (the model-parallel FC pair, 2 GPUs and more) and
+`latency` (the two small latency-bound networks, 1 GPU) -- and under `ops` every kernel of the table timed alone
+against its own roofline (1 GPU).  At more than one GPU every gathered / reduced result is checked on rank 0 against a
+recomputation from the known seeds (`gather_check`).
 """
 from __future__ import annotations
 
@@ -35,15 +41,17 @@ def config(n_gpus, rows_per_rank):
     return {"workload": "wide MLP forward (BASELINE configs[2]): X[65536,4096] bf16 -> 4x(FC 4096->4096 + bias + ReLU) "
                         "-> FC 4096->1000 + bias -> softmax",
             "global_batch": BATCH, "rows_per_gpu": rows_per_rank, "parallelism": f"dp{n_gpus} (batch split; Gather to rank 0 by peer copies over NVLink, overlapped with the next step)",
+            "precision": "bf16 operands and stored activations, fp32 accumulation (the split-activation mode is reported under workloads.widemlp_split)",
             "l2": "inputs larger than L2 (X 512 MiB, activations 512 MiB per layer); no flush needed"}
 
 
 def peaks():
     try:
         p = json.load(open(os.path.join(ROOT, "MEASURED_PEAKS.json")))
-        return float(p["bf16_tflops_sustained"]), "measured (MEASURED_PEAKS.json bf16_tflops_sustained)"
+        return {"sustained": float(p["bf16_tflops_sustained"]), "burst": float(p["bf16_tflops"]), "hbm": float(p["hbm_gbs"]),
+                "source": "measured (MEASURED_PEAKS.json)"}
     except Exception:
-        return 1400.0, "fallback (sustained figure of the profiling recipe)"
+        return {"sustained": 1400.0, "burst": 1590.0, "hbm": 6650.0, "source": "fallback (figures of the profiling recipe)"}
 
 
 class ClockSampler:
@@ -80,7 +88,7 @@ class ClockSampler:
                         self.reasons.add(k)
             except Exception:
                 pass
-            self._stop.wait(0.05)
+            self._stop.wait(0.02)
 
     def __enter__(self):
         if self.nv:
@@ -99,18 +107,73 @@ class ClockSampler:
         return {"sm_mhz": statistics.median(self.samples), "sm_max_mhz": self.max_mhz, "reasons": sorted(self.reasons)}
 
 
-def make_inputs(torch, device, rows, row0):
-    """Seeded synthetic tensors of the configuration, generated on the device.  Weights are identical on
-    every rank (same seed); each rank draws its own rows of X."""
+class Env:
+    """One process per GPU: device, the process group (more than one rank) and the few collective helpers of the bench."""
+
+    def __init__(self, rank, world, local_rank):
+        import torch
+        import torch.distributed as dist
+        self.torch, self.dist = torch, dist
+        self.rank, self.world, self.local_rank = rank, world, local_rank
+        torch.cuda.set_device(local_rank)
+        self.device = torch.device("cuda", local_rank)
+        if world > 1:
+            dist.init_process_group("nccl", device_id=self.device)
+
+    def barrier(self):
+        if self.world > 1:
+            self.dist.barrier()
+        self.torch.cuda.synchronize()
+
+    def max_over_ranks(self, values):
+        if self.world == 1:
+            return [float(v) for v in values]
+        t = self.torch.tensor([float(v) for v in values], device=self.device)
+        self.dist.all_reduce(t, op=self.dist.ReduceOp.MAX)
+        return [float(v) for v in t.tolist()]
+
+    def gather_floats(self, values):
+        """Every rank's list on rank 0 (a list of lists), None elsewhere."""
+        if self.world == 1:
+            return [[float(v) for v in values]]
+        t = self.torch.tensor([float(v) for v in values], device=self.device)
+        outs = [self.torch.empty_like(t) for _ in range(self.world)]
+        self.dist.all_gather(outs, t)
+        return [[float(v) for v in o.tolist()] for o in outs] if self.rank == 0 else None
+
+    def exchange(self, uid):
+        box = [uid]
+        if self.world > 1:
+            self.dist.broadcast_object_list(box, src=0)
+        return box[0]
+
+    def comm(self, swc):
+        """A communicator of the kernel library on a stream of its own."""
+        from swcompiler_b200 import parallel as par
+        stream = self.torch.cuda.Stream(self.device)
+        return par.NcclComm(swc.Backend(self.local_rank, swc.TC_BF16, stream=stream), self.rank, self.world, self.exchange)
+
+    def close(self):
+        if self.world > 1:
+            self.barrier()
+            self.dist.destroy_process_group()
+
+
+def make_weights(torch, device):
+    """Seeded synthetic weights of the configuration, generated on the device; identical on every rank."""
     g = torch.Generator(device=device).manual_seed(SEED)
     ws, bs = [], []
     for i in range(LAYERS + 1):
         n = WIDTH if i < LAYERS else CLASSES
         ws.append((torch.randn((WIDTH, n), generator=g, device=device) / WIDTH ** 0.5).to(torch.bfloat16).float())
         bs.append(torch.randn(n, generator=g, device=device) * 0.01)
+    return ws, bs
+
+
+def make_rows(torch, device, rows, row0):
+    """The rows [row0, row0 + rows) of X: each rank draws its own slice from a seed that names its first row."""
     gx = torch.Generator(device=device).manual_seed(SEED * 1000 + row0)
-    x = torch.randn((rows, WIDTH), generator=gx, device=device).to(torch.bfloat16)
-    return x, ws, bs
+    return torch.randn((rows, WIDTH), generator=gx, device=device).to(torch.bfloat16)
 
 
 class CpuArm:
@@ -164,48 +227,50 @@ def run_reference(args, rank, world):
         "gpu_launches": 0}))
 
 
-def run_ours(args, rank, world, local_rank):
-    import torch
-    import torch.distributed as dist
+# ---------------------------------------------------------------------------------------------------------------------
+# wide MLP (the headline)
 
+def run_widemlp(env, args, split=False):
+    """Returns the JSON record of the wide-MLP benchmark (rank 0; None elsewhere).  `split`: hidden activations are
+    stored as two bf16 terms (value and rounding remainder) and every layer multiplies both, see fc_tcgen05.cu."""
+    torch, dist = env.torch, env.dist
     import swcompiler_b200 as swc
     from swcompiler_b200.programs import WideMlpProgram
 
-    torch.cuda.set_device(local_rank)
-    device = torch.device("cuda", local_rank)
-    if world > 1:
-        dist.init_process_group("nccl", device_id=device)
+    world, rank, device = env.world, env.rank, env.device
     rows = BATCH // world
     row0 = rank * rows
-    be = swc.Backend(local_rank, swc.TC_BF16)
-    x, ws, bs = make_inputs(torch, device, rows, row0)
-    prog = WideMlpProgram(be, ws, bs, max_rows=rows)
+    be = swc.Backend(env.local_rank, swc.TC_BF16)
+    ws, bs = make_weights(torch, device)
+    x = make_rows(torch, device, rows, row0)
+    prog = WideMlpProgram(be, ws, bs, max_rows=rows, split=split)
     del ws
-    # Two output buffers: with more than one GPU the Gather of step s (NCCL, on its own stream, through the
-    # library's swcb200_gather) runs while the tensor cores work on step s+1.
+    # Two output buffers: with more than one GPU the Gather of step s runs while the tensor cores work on step s+1.
     probs2 = [torch.empty((rows, CLASSES), dtype=torch.float32, device=device) for _ in range(2 if world > 1 else 1)]
-    probs = probs2[0]
     comm = gathered = None
+    use_rows = os.environ.get("SWCB200_BENCH_GATHER", "rows") != "nccl"
     if world > 1:
-        from swcompiler_b200 import parallel as par
-
-        def exchange(uid):
-            box = [uid]
-            dist.broadcast_object_list(box, src=0)
-            return box[0]
-
-        comm_stream = torch.cuda.Stream(device)
-        comm = par.NcclComm(swc.Backend(local_rank, swc.TC_BF16, stream=comm_stream), rank, world, exchange)
+        comm = env.comm(swc)
         if rank == 0:
             gathered = torch.empty((BATCH, CLASSES), dtype=torch.float32, device=device)
         # The Gather: peer copies on the copy engines (swcb200_gather_rows), so that it takes no SM from the
         # persistent GEMMs of the next step; SWCB200_BENCH_GATHER=nccl selects the send/recv path instead.
-        use_rows = os.environ.get("SWCB200_BENCH_GATHER", "rows") != "nccl"
         if use_rows:
             comm.gather_rows_setup(gathered, rows * CLASSES * 4, root=0)
     main_stream = torch.cuda.current_stream(device)
     gather_done = [None, None]
     counter = [0]
+
+    def gather(out):
+        ready = torch.cuda.Event()
+        ready.record(main_stream)
+        comm.be.torch_stream.wait_event(ready)
+        if use_rows:
+            comm.gather_rows(out)
+        else:
+            dst = C.c_void_p(gathered.data_ptr()) if rank == 0 else C.c_void_p(0)
+            comm.be._call("gather", C.c_void_p(out.data_ptr()), dst, (C.c_size_t * 2)(BATCH, CLASSES), C.c_int(2),
+                          C.c_int(0), C.c_int(swc.F32), C.c_int(0))
 
     def step(on_launch=None):
         s = counter[0]
@@ -215,15 +280,7 @@ def run_ours(args, rank, world, local_rank):
             main_stream.wait_event(gather_done[s % 2])  # the buffer's previous Gather has read it
         prog.forward(x, out, on_launch=on_launch)
         if world > 1:
-            ready = torch.cuda.Event()
-            ready.record(main_stream)
-            comm.be.torch_stream.wait_event(ready)
-            if use_rows:
-                comm.gather_rows(out)
-            else:
-                dst = C.c_void_p(gathered.data_ptr()) if rank == 0 else C.c_void_p(0)
-                comm.be._call("gather", C.c_void_p(out.data_ptr()), dst, (C.c_size_t * 2)(BATCH, CLASSES), C.c_int(2),
-                              C.c_int(0), C.c_int(swc.F32), C.c_int(0))
+            gather(out)
             done = torch.cuda.Event()
             done.record(comm.be.torch_stream)
             gather_done[s % 2] = done
@@ -232,14 +289,9 @@ def run_ours(args, rank, world, local_rank):
         if world > 1:
             main_stream.wait_stream(comm.be.torch_stream)
 
-    def barrier():
-        if world > 1:
-            dist.barrier()
-        torch.cuda.synchronize()
-
     for _ in range(max(args.warmup, 3)):
         step()
-    barrier()
+    env.barrier()
 
     # ---- timed region: K steps, device-timed, per-launch events for the dominant kernel
     nl = prog.launches_per_forward
@@ -247,201 +299,321 @@ def run_ours(args, rank, world, local_rank):
           for _ in range(args.steps)]
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     launches0 = be.launches
-    with ClockSampler(local_rank) as clocks:
-        barrier()
+    with ClockSampler(env.local_rank) as clocks:
+        env.barrier()
         e0.record()
         for s in range(args.steps):
             step(on_launch=lambda i, when, s=s: ev[s][i][when].record())
         drain()
         e1.record()
-        barrier()
-    launches = be.launches - launches0 # the Gather is a copy-engine transfer, not a launch
+        env.barrier()
+    launches = be.launches - launches0  # the Gather is a copy-engine transfer, not a launch
     be.sync()  # also surfaces a device-side timeout status, if any
-    ms = e0.elapsed_time(e1)
-    if world > 1:
-        t = torch.tensor([ms], device=device)
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        ms = float(t.item())
+    ms = env.max_over_ranks([e0.elapsed_time(e1)])[0]
     value = BATCH * args.steps / (ms * 1e-3)
 
     # dominant kernel: the hidden-layer FC launches (4 per step)
     fc_ms = [ev[s][i][0].elapsed_time(ev[s][i][1]) for s in range(args.steps) for i in range(LAYERS)]
     fc_avg_ms = sum(fc_ms) / len(fc_ms)
-    flops_per_launch = 2.0 * rows * WIDTH * WIDTH
+    flops_per_launch = 2.0 * rows * WIDTH * WIDTH * (1.0 if not split else 1.75)  # split: layers 2-4 multiply two terms
     achieved = flops_per_launch / (fc_avg_ms * 1e-3) / 1e12
-    peak, peak_src = peaks()
+    pk = peaks()
     per_kernel_ms = [sum(ev[s][i][0].elapsed_time(ev[s][i][1]) for s in range(args.steps)) / args.steps for i in range(nl)]
 
-    e2e_value = e2e_ms = None
-    e2e_steps = max(3, min(args.steps, 10))
-    x_host = probs_host = None
-    if not args.skip_e2e:
-        e2e_value, e2e_ms, x_host, probs_host = run_e2e(torch, dist, prog, x, probs, world, device, rows, e2e_steps,
-                                                        barrier)
+    check = None
+    if world > 1:
+        check = check_gather_widemlp(env, prog, gathered, rows)
+
+    e2e = None
+    if not args.skip_e2e and not split:
+        e2e = run_e2e(env, args, prog, x, probs2, comm, gathered, rows)
 
     cpu = None
-    if rank == 0 and world == 1 and not args.skip_cpu_baseline:
+    if rank == 0 and world == 1 and not args.skip_cpu_baseline and not split:
         threads = os.cpu_count() or 1
         arm = CpuArm(64, threads)
         dt = arm.step()
         cpu = {"value": arm.rows / dt, "unit": UNIT, "cores": threads, "kind": arm.impl.kind,
                "sample": f"{arm.rows} rows (64 per thread x {threads} threads) of the 65536-row batch, one pass, {dt:.1f} s"}
 
+    rec = None
     if rank == 0:
-        e2e = None if e2e_value is None else {
-            "value": e2e_value, "unit": UNIT, "h2d_bytes_per_step": x_host.numel() * 2 * world,
-            "d2h_bytes_per_step": probs_host.numel() * 4 * world, "ms_per_step": e2e_ms / e2e_steps}
-        print(json.dumps({
+        # DRAM traffic of one hidden-layer launch by its operands: A and C once (rows x 4096 bf16 each), the packed
+        # weight once (32 MiB); the ncu capture of an 8192-row launch agrees within 5 % (profiles/).  Not measured here.
+        traffic_model = 2.0 * rows * WIDTH * 2 + WIDTH * WIDTH * 2
+        rec = {
             "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps, "warmup": max(args.warmup, 3),
             "ms_per_step": ms / args.steps, "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
-            "dtype": "bf16 (fp32 accumulate)", "data": "synthetic", "config": config(world, rows),
-            "roofline": {"bound": "tensor", "achieved": achieved, "peak": peak, "unit": "TFLOP/s", "frac": achieved / peak,
-                         "traffic": 32e6 + 127.6e6 * rows / 8192, "traffic_source": "ncu dram bytes of the 8192-row launch (159.6 MB), row-proportional part scaled; profiles/fc_tc_pair_kernel__config3_layer.md", "kernel": "fc_tc_pair_kernel (FC 4096->4096 + bias + ReLU, one launch)",
-                         "launch_ms": fc_avg_ms, "flops_per_launch": flops_per_launch, "peak_source": peak_src},
-            "per_launch_ms": per_kernel_ms,
-            "cpu_baseline": cpu, "e2e": e2e,
-            "gpu_launches": launches, "clocks": clocks.summary()}))
+            "dtype": "bf16 (fp32 accumulate)" + (", hidden activations as two bf16 terms" if split else ""), "data": "synthetic",
+            "config": config(world, rows),
+            "roofline": {"bound": "tensor", "achieved": achieved, "peak": pk["sustained"], "unit": "TFLOP/s",
+                         "frac": achieved / pk["sustained"], "traffic": None if split else traffic_model,
+                         "traffic_source": "operand bytes of one launch (A + C + packed weight), not measured in this run",
+                         "kernel": "fc_tc_pair_kernel (FC 4096->4096 + bias + ReLU, one launch)",
+                         "launch_ms": fc_avg_ms, "flops_per_launch": flops_per_launch,
+                         "peak_source": pk["source"] + " bf16_tflops_sustained"},
+            "per_launch_ms": per_kernel_ms, "cpu_baseline": cpu, "e2e": e2e, "gather_check": check,
+            "gpu_launches": launches, "clocks": clocks.summary()}
     if world > 1:
-        barrier()
+        env.barrier()
         comm.close()
-        dist.destroy_process_group()
+    del prog, probs2, x, gathered
+    torch.cuda.empty_cache()
+    return rec
 
 
-def run_fcpair(args, rank, world, local_rank):
+def check_gather_widemlp(env, prog, gathered, rows, samples=48):
+    """Rank 0 draws every rank's slice of X again from its seed, pushes `samples` rows of each through the forward
+    pass and compares them with what the Gather of the last step left in its buffer."""
+    torch = env.torch
+    env.barrier()
+    if env.rank != 0:
+        return None
+    worst, n = 0.0, 0
+    out = torch.empty((samples, CLASSES), dtype=torch.float32, device=env.device)
+    for r in range(env.world):
+        xr = make_rows(torch, env.device, rows, r * rows)
+        idx = torch.linspace(0, rows - 1, samples, device=env.device).long()
+        prog.forward(xr[idx].contiguous(), out)
+        prog.be.sync()
+        got = gathered[r * rows + idx]
+        worst = max(worst, float((got - out).abs().max().item()))
+        n += samples
+        del xr
+    return {"rows": n, "max_abs": worst, "ok": bool(worst <= 1e-6), "what": "gathered probabilities vs the same rows recomputed on rank 0"}
+
+
+def run_e2e(env, args, prog, x, probs2, comm, gathered, rows):
+    """End to end with host buffers: every rank copies its rows of X in from pinned host memory while earlier chunks
+    compute; with more than one GPU the probabilities are gathered on rank 0, which copies the whole result out
+    (the copy-out of step s overlaps step s+1); with one GPU the copy-out is chunked like the copy-in."""
+    torch = env.torch
+    world, rank, device = env.world, env.rank, env.device
+    steps = max(3, min(args.steps, 10))
+    x_host = torch.empty((rows, WIDTH), dtype=torch.bfloat16).pin_memory()
+    x_host.copy_(x.cpu())
+    x_dev = torch.empty_like(x)
+    chunk = min(8192, max(2048, rows // 4))
+    main = torch.cuda.current_stream(device)
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    if world == 1:
+        probs_host = torch.empty((rows, CLASSES), dtype=torch.float32).pin_memory()
+
+        def one():
+            prog.forward_host(x_host, probs_host, x_dev, probs2[0], chunk_rows=chunk)
+        out_bytes = probs_host.numel() * 4
+    else:
+        out_host = [torch.empty((BATCH, CLASSES), dtype=torch.float32).pin_memory() for _ in range(2)] if rank == 0 else None
+        s_out = torch.cuda.Stream(device)
+        cs = comm.be.torch_stream
+        sync_word = torch.zeros(1, device=device)
+        state = {"s": 0, "gdone": [None, None]}
+
+        def one():
+            # One gathered buffer on rank 0, so the steps hand it over in turn: the Gather of step s (every rank's
+            # peer copy, then a one-word all-reduce that completes on rank 0 only when all copies are in), rank 0's
+            # copy-out of it, and a second one-word all-reduce that rank 0 joins after that copy-out, which tells
+            # the other ranks that the buffer may be overwritten by step s+1.  Copy-in and compute of step s+1 run
+            # on the main stream meanwhile.
+            s = state["s"]
+            state["s"] += 1
+            out = probs2[s % 2]
+            if state["gdone"][s % 2] is not None:
+                main.wait_event(state["gdone"][s % 2])  # the Gather of step s-2 has read this buffer
+            prog.forward_host(x_host, None, x_dev, out, chunk_rows=chunk)
+            ready = torch.cuda.Event()
+            ready.record(main)
+            cs.wait_event(ready)
+            comm.gather_rows(out)
+            gd = torch.cuda.Event()
+            gd.record(cs)
+            state["gdone"][s % 2] = gd
+            comm.allreduce_sum(sync_word, out=sync_word)
+            if rank == 0:
+                arrived = torch.cuda.Event()
+                arrived.record(cs)
+                s_out.wait_event(arrived)
+                with torch.cuda.stream(s_out):
+                    out_host[s % 2].copy_(gathered, non_blocking=True)
+                    od = torch.cuda.Event()
+                    od.record(s_out)
+                cs.wait_event(od)
+            comm.allreduce_sum(sync_word, out=sync_word)
+        out_bytes = BATCH * CLASSES * 4
+
+    def finish():
+        if world > 1:
+            main.wait_stream(comm.be.torch_stream)
+            if rank == 0:
+                main.wait_stream(s_out)
+
+    for _ in range(2):
+        one()
+    finish()
+    env.barrier()
+    e0.record()
+    for _ in range(steps):
+        one()
+    finish()
+    e1.record()
+    env.barrier()
+    e2e_ms = env.max_over_ranks([e0.elapsed_time(e1)])[0]
+
+    # what the host links give each rank when every rank copies at once (plain pinned copies, no compute)
+    def copy_gbs(dst, src, nbytes):
+        c0, c1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        env.barrier()
+        c0.record()
+        for _ in range(3):
+            dst.copy_(src, non_blocking=True)
+        c1.record()
+        torch.cuda.synchronize()
+        return 3 * nbytes / (c0.elapsed_time(c1) * 1e-3) / 1e9
+    h2d = copy_gbs(x_dev, x_host, x_host.numel() * 2)
+    probe_host = torch.empty((rows, CLASSES), dtype=torch.float32).pin_memory()
+    d2h = copy_gbs(probe_host, probs2[0], rows * CLASSES * 4)
+    links = env.gather_floats([h2d, d2h])
+    if rank != 0:
+        return None
+    return {"value": BATCH * steps / (e2e_ms * 1e-3), "unit": UNIT, "h2d_bytes_per_step": x_host.numel() * 2 * world,
+            "d2h_bytes_per_step": out_bytes, "ms_per_step": e2e_ms / steps, "steps": steps, "chunk_rows": chunk,
+            "program": "H2D of each rank's rows in chunks overlapped with compute" +
+                       ("; chunked D2H" if world == 1 else "; Gather on rank 0 (peer copies); D2H of the gathered result by rank 0, overlapped with the next step"),
+            "host_link_GBps_all_ranks_copying": {"h2d_per_rank": [l[0] for l in links], "d2h_per_rank": [l[1] for l in links],
+                                                  "h2d_sum": sum(l[0] for l in links), "d2h_sum": sum(l[1] for l in links)}}
+
+
+# ---------------------------------------------------------------------------------------------------------------------
+# model-parallel FC pair
+
+def run_fcpair(env, args):
     """Model-parallel FC pair (BASELINE configs[3]): X[8192,8192] bf16 replicated; FC1 8192->32768 split by output
     columns -> ReLU; FC2 32768->8192 split by input rows; fp32 partial sums joined by an NCCL all-reduce.  One step =
     one forward pass over the 8192 rows; the rows go through in `--chunks` chunks so that the all-reduce of one chunk
     (communication stream) overlaps the tensor-core work of the next."""
-    import torch
-    import torch.distributed as dist
-
+    torch = env.torch
     import swcompiler_b200 as swc
-    from swcompiler_b200 import parallel as par
+    import swcompiler_b200._lib as L
     from swcompiler_b200.programs import FcPairProgram
 
+    world, rank, device = env.world, env.rank, env.device
     M, K, N1, N2 = args.fcpair_rows, 8192, 32768, 8192
-    torch.cuda.set_device(local_rank)
-    device = torch.device("cuda", local_rank)
-    if world > 1:
-        dist.init_process_group("nccl", device_id=device)
-    be = swc.Backend(local_rank, swc.TC_BF16)
-
-    def exchange(uid):
-        box = [uid]
-        if world > 1:
-            dist.broadcast_object_list(box, src=0)
-        return box[0]
-
-    comm = par.NcclComm(swc.Backend(local_rank, swc.TC_BF16, stream=torch.cuda.Stream(device)), rank, world, exchange)
-    g = torch.Generator(device=device).manual_seed(1004)
-    x = torch.randn((M, K), generator=g, device=device).to(torch.bfloat16)
-    # the rank's shards are drawn directly (same law as the full matrices; the full 512 MiB + 512 MiB fp32 weights
-    # are never materialised): W1[:, cols of this rank] ~ N(0, 1/K), W2[rows of this rank, :] ~ N(0, 1/N1)
-    gs = torch.Generator(device=device).manual_seed(1004 * 100 + rank)
+    be = swc.Backend(env.local_rank, swc.TC_BF16)
+    comm = env.comm(swc)
+    x = torch.randn((M, K), generator=torch.Generator(device=device).manual_seed(1004), device=device).to(torch.bfloat16)
     n1s = N1 // world
 
-    w1s = (torch.randn((K, n1s), generator=gs, device=device) / K ** 0.5)
-    w2s = (torch.randn((n1s, N2), generator=gs, device=device) / N1 ** 0.5)
+    def shards(r):
+        # a rank's shards are drawn directly (same law as the full matrices, which are never materialised):
+        # W1[:, cols of rank r] ~ N(0, 1/K), W2[rows of rank r, :] ~ N(0, 1/N1)
+        gs = torch.Generator(device=device).manual_seed(1004 * 100 + r)
+        w1 = torch.randn((K, n1s), generator=gs, device=device) / K ** 0.5
+        w2 = torch.randn((n1s, N2), generator=gs, device=device) / N1 ** 0.5
+        return w1, w2
+
+    w1s, w2s = shards(rank)
     prog = FcPairProgram(be, comm, w1s, w2s, max_rows=M, sharded=True)
     del w1s, w2s
     chunks = args.chunks
 
-    def barrier():
-        if world > 1:
-            dist.barrier()
-        torch.cuda.synchronize()
+    def timed(fn, steps):
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        env.barrier()
+        e0.record()
+        for _ in range(steps):
+            fn()
+        e1.record()
+        env.barrier()
+        return e0.elapsed_time(e1) / steps
 
     for _ in range(max(args.warmup, 3)):
         prog.forward(x, chunks=chunks)
-    barrier()
-    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     launches0 = be.launches
-    with ClockSampler(local_rank) as clocks:
-        barrier()
-        e0.record()
-        for _ in range(args.steps):
-            prog.forward(x, chunks=chunks)
-        e1.record()
-        barrier()
+    with ClockSampler(env.local_rank) as clocks:
+        step_ms = timed(lambda: prog.forward(x, chunks=chunks), args.steps)
+    launches = be.launches - launches0
     be.sync()
     comm.be.sync()
-    ms = e0.elapsed_time(e1)
-    # the two GEMMs alone (no all-reduce), for the roofline of the dominant kernel
-    g0, g1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    import swcompiler_b200._lib as L
-    g0.record()
-    for _ in range(args.steps):
-        be.fc_bf16(x, prog.wp1, None, L.ACT_RELU, out=prog.h)
-    g1.record()
-    torch.cuda.synchronize()
-    fc1_ms = g0.elapsed_time(g1) / args.steps
-    if world > 1:
-        t = torch.tensor([ms, fc1_ms], device=device)
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        ms, fc1_ms = float(t[0].item()), float(t[1].item())
-    launches = be.launches - launches0 - args.steps
-    flops_fc1 = 2.0 * M * n1s * K
-    peak, peak_src = peaks()
+    serial_ms = timed(lambda: prog.forward(x, chunks=1), args.steps)          # no overlap: GEMMs, then one all-reduce
+    fc1_ms = timed(lambda: be.fc_bf16(x, prog.wp1, None, L.ACT_RELU, out=prog.h), args.steps)   # the dominant kernel alone
+    step_ms, serial_ms, fc1_ms = env.max_over_ranks([step_ms, serial_ms, fc1_ms])
+
+    # check on rank 0: sampled rows against relu(X W1) W2 with every rank's shards drawn again (fp32 matmul of the
+    # bf16-rounded operands; the hidden activation rounded to bf16 as the program stores it)
+    y = prog.forward(x, chunks=chunks)
+    be.sync()
+    comm.be.sync()
+    check = None
     if rank == 0:
-        step_ms = ms / args.steps
+        idx = torch.linspace(0, M - 1, 64, device=device).long()
+        xs = x[idx].float()
+        ref = torch.zeros((64, N2), device=device)
+        for r in range(world):
+            w1, w2 = shards(r)
+            h = torch.relu(xs @ w1.to(torch.bfloat16).float()).to(torch.bfloat16).float()
+            ref += h @ w2.to(torch.bfloat16).float()
+            del w1, w2
+        err = float((y[idx] - ref).abs().max().item())
+        check = {"rows": 64, "max_abs": err, "ok": bool(err <= 2e-2), "what": "all-reduced output vs relu(X W1) W2 from the seeds"}
+    env.barrier()
+    flops_fc1 = 2.0 * M * n1s * K
+    pk = peaks()
+    rec = None
+    if rank == 0:
         total_flops = 2.0 * M * N1 * (K + N2)
-        print(json.dumps({
+        rec = {
             "metric": METRIC, "value": M / (step_ms * 1e-3), "unit": UNIT, "n_gpus": world, "steps": args.steps,
-            "warmup": max(args.warmup, 3), "ms_per_step": step_ms, "higher_is_better": True, "scaling": "strong",
-            "vs_baseline": None, "dtype": "bf16 (fp32 accumulate, fp32 all-reduce)", "data": "synthetic",
+            "ms_per_step": step_ms, "ms_per_step_no_overlap": serial_ms, "scaling": "strong",
+            "dtype": "bf16 (fp32 accumulate, fp32 all-reduce)", "data": "synthetic",
             "config": {"workload": "model-parallel FC pair (BASELINE configs[3]): X[8192,8192] bf16 -> FC 8192->32768 "
                                    "(column split) -> ReLU -> FC 32768->8192 (row split) -> all-reduce(sum)",
                        "global_batch": M, "parallelism": f"mp{world}", "chunks": chunks,
                        "l2": "weights (1 GiB / p per rank) larger than L2; no flush needed"},
             "job_tflops": total_flops / (step_ms * 1e-3) / 1e12,
-            "roofline": {"bound": "tensor", "achieved": flops_fc1 / (fc1_ms * 1e-3) / 1e12, "peak": peak, "unit": "TFLOP/s",
-                         "frac": flops_fc1 / (fc1_ms * 1e-3) / 1e12 / peak, "traffic": None,
+            "roofline": {"bound": "tensor", "achieved": flops_fc1 / (fc1_ms * 1e-3) / 1e12, "peak": pk["sustained"], "unit": "TFLOP/s",
+                         "frac": flops_fc1 / (fc1_ms * 1e-3) / 1e12 / pk["sustained"], "traffic": None,
                          "kernel": "fc_tc_pair_kernel (FC1 shard 8192 x 32768/p x 8192 + ReLU, one launch, timed alone)",
-                         "launch_ms": fc1_ms, "flops_per_launch": flops_fc1, "peak_source": peak_src},
-            "allreduce_bytes_per_rank": M * N2 * 4, "cpu_baseline": None, "e2e": None,
-            "gpu_launches": launches, "clocks": clocks.summary()}))
-    barrier()
+                         "launch_ms": fc1_ms, "flops_per_launch": flops_fc1, "peak_source": pk["source"] + " bf16_tflops_sustained"},
+            "allreduce_bytes_per_rank": M * N2 * 4, "gather_check": check,
+            "gpu_launches": launches, "clocks": clocks.summary()}
+    env.barrier()
     comm.close()
-    if world > 1:
-        dist.destroy_process_group()
+    del prog, x
+    torch.cuda.empty_cache()
+    return rec
 
 
-def run_resstage(args, rank, world, local_rank):
+# ---------------------------------------------------------------------------------------------------------------------
+# ResNet-style conv stage
+
+def run_resstage(env, args):
     """ResNet-style stage (BASELINE configs[4]): [256,56,56,64] bf16 NHWC -> 3 x (Conv3x3+BN+ReLU, Conv3x3+BN+Add+ReLU) ->
     MaxPool 2x2/2, every Conv-BN-[Add]-ReLU chain one tensor-core launch.  The batch is split evenly over the ranks
     (every op is per-image, no collective inside the stage); the pooled outputs are gathered on rank 0 by peer copies."""
-    import torch
-    import torch.distributed as dist
-
+    torch = env.torch
     import swcompiler_b200 as swc
     from swcompiler_b200.programs import ResStageProgram
 
+    world, rank, device = env.world, env.rank, env.device
     N, HW, CH, BLOCKS = 256, 56, 64, 3
-    torch.cuda.set_device(local_rank)
-    device = torch.device("cuda", local_rank)
-    if world > 1:
-        dist.init_process_group("nccl", device_id=device)
     n = N // world
-    be = swc.Backend(local_rank, swc.TC_BF16)
+    be = swc.Backend(env.local_rank, swc.TC_BF16)
     g = torch.Generator(device=device).manual_seed(1005)
     convs = [dict(w=torch.randn((CH, 3, 3, CH), generator=g, device=device) * (2.0 / (9 * CH)) ** 0.5,
                   b=torch.zeros(CH, device=device)) for _ in range(2 * BLOCKS)]
     bns = [dict(scale=torch.rand(CH, generator=g, device=device) + 0.5, bias=torch.randn(CH, generator=g, device=device) * 0.1,
                 mean=torch.randn(CH, generator=g, device=device) * 0.1, var=torch.rand(CH, generator=g, device=device) + 0.5,
                 eps=1e-5) for _ in range(2 * BLOCKS)]
-    gx = torch.Generator(device=device).manual_seed(1005 * 1000 + rank)
-    x = torch.randn((n, HW, HW, CH), generator=gx, device=device).to(torch.bfloat16)
+
+    def images(r):
+        gx = torch.Generator(device=device).manual_seed(1005 * 1000 + r)
+        return torch.randn((n, HW, HW, CH), generator=gx, device=device).to(torch.bfloat16)
+
+    x = images(rank)
     prog = ResStageProgram(be, convs, bns, max_batch=n, hw=HW, ch=CH)
     comm = gathered = None
     if world > 1:
-        from swcompiler_b200 import parallel as par
-
-        def exchange(uid):
-            box = [uid]
-            dist.broadcast_object_list(box, src=0)
-            return box[0]
-
-        comm = par.NcclComm(swc.Backend(local_rank, swc.TC_BF16, stream=torch.cuda.Stream(device)), rank, world, exchange)
+        comm = env.comm(swc)
         if rank == 0:
             gathered = torch.empty((N, HW // 2, HW // 2, CH), dtype=torch.bfloat16, device=device)
         comm.gather_rows_setup(gathered, n * (HW // 2) * (HW // 2) * CH * 2, root=0)
@@ -456,84 +628,82 @@ def run_resstage(args, rank, world, local_rank):
             comm.gather_rows(out)
             main_stream.wait_stream(comm.be.torch_stream)  # one pooled buffer: the next pass may overwrite it
 
-    def barrier():
-        if world > 1:
-            dist.barrier()
-        torch.cuda.synchronize()
-
     for _ in range(max(args.warmup, 3)):
         step()
-    barrier()
+    env.barrier()
+    steps = max(args.steps, 20)  # a step is well under a millisecond
     nl = prog.launches_per_forward
-    ev = [[(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(nl)]
-          for _ in range(args.steps)]
+    ev = [[(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(nl)] for _ in range(steps)]
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     launches0 = be.launches
-    with ClockSampler(local_rank) as clocks:
-        barrier()
+    with ClockSampler(env.local_rank) as clocks:
+        env.barrier()
         e0.record()
-        for s in range(args.steps):
+        for s in range(steps):
             step(on_launch=lambda i, when, s=s: ev[s][i][when].record())
         e1.record()
-        barrier()
+        env.barrier()
     launches = be.launches - launches0
     be.sync()
-    ms = e0.elapsed_time(e1)
-    conv_ms = [ev[s][i][0].elapsed_time(ev[s][i][1]) for s in range(args.steps) for i in range(nl - 1)]
-    conv_avg = sum(conv_ms) / len(conv_ms)
+    per_launch = [sum(ev[s][i][0].elapsed_time(ev[s][i][1]) for s in range(steps)) / steps for i in range(nl)]
+    conv_avg = sum(per_launch[:-1]) / (nl - 1)
+    ms, conv_avg = env.max_over_ranks([e0.elapsed_time(e1), conv_avg])
+
+    # check on rank 0: the first image of every rank through a plain fp32 convolution chain (torch, as the checker),
+    # activations rounded to bf16 where the program stores them, against the gathered pooled tensor
+    check = None
     if world > 1:
-        t = torch.tensor([ms, conv_avg], device=device)
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        ms, conv_avg = float(t[0].item()), float(t[1].item())
-    flops = 2.0 * n * HW * HW * CH * 9 * CH
-    try:
-        peak, peak_src = float(json.load(open(os.path.join(ROOT, "MEASURED_PEAKS.json")))["bf16_tflops"]), \
-            "measured (MEASURED_PEAKS.json bf16_tflops, burst: the launches are short)"
-    except Exception:
-        peak, peak_src = 1590.0, "fallback (burst figure of the profiling recipe)"
+        env.barrier()
     if rank == 0:
-        step_ms = ms / args.steps
+        import torch.nn.functional as F
+        worst, scale = 0.0, 0.0
+        bf = lambda t: t.to(torch.bfloat16).float()
+
+        def conv_bn(h, i):
+            w = bf(convs[i]["w"]).permute(0, 3, 1, 2)  # [oC,kh,kw,iC] -> [oC,iC,kh,kw]
+            y = F.conv2d(h, w, convs[i]["b"], padding=1)
+            b = bns[i]
+            a = b["scale"] / torch.sqrt(b["var"] + b["eps"])
+            return y * a.view(1, -1, 1, 1) + (b["bias"] - b["mean"] * a).view(1, -1, 1, 1)
+
+        prev = torch.backends.cudnn.allow_tf32
+        torch.backends.cudnn.allow_tf32 = False
+        for r in range(world):
+            h = images(r)[:1].float().permute(0, 3, 1, 2)
+            for blk in range(BLOCKS):
+                t = bf(torch.relu(conv_bn(h, 2 * blk)))
+                h = bf(torch.relu(conv_bn(t, 2 * blk + 1) + h))
+            ref = F.max_pool2d(h, 2).permute(0, 2, 3, 1)
+            got = (gathered[r * n] if world > 1 else prog.pooled[0]).float()
+            worst = max(worst, float((got - ref[0]).abs().max().item()))
+            scale = max(scale, float(ref.abs().max().item()))
+        torch.backends.cudnn.allow_tf32 = prev
+        check = {"images": world, "max_abs": worst, "max_activation": scale, "ok": bool(worst <= 0.02 * scale),
+                 "what": "pooled output of each rank's first image vs an fp32 convolution chain with the same rounding points"}
+    flops = 2.0 * n * HW * HW * CH * 9 * CH
+    pk = peaks()
+    rec = None
+    if rank == 0:
+        step_ms = ms / steps
         achieved = flops / (conv_avg * 1e-3) / 1e12
-        print(json.dumps({
-            "metric": METRIC, "value": N / (step_ms * 1e-3), "unit": UNIT, "n_gpus": world, "steps": args.steps,
-            "warmup": max(args.warmup, 3), "ms_per_step": step_ms, "higher_is_better": True, "scaling": "strong",
-            "vs_baseline": None, "dtype": "bf16 (fp32 accumulate)", "data": "synthetic",
+        rec = {
+            "metric": METRIC, "value": N / (step_ms * 1e-3), "unit": UNIT, "n_gpus": world, "steps": steps,
+            "ms_per_step": step_ms, "scaling": "strong", "dtype": "bf16 (fp32 accumulate)", "data": "synthetic",
             "config": {"workload": "ResNet-style conv stage (BASELINE configs[4]): [256,56,56,64] bf16 NHWC, 3 residual blocks "
                                    "of two 3x3 64->64 convolutions with BN / skip / ReLU fused, then MaxPool 2x2/2",
                        "global_batch": N, "images_per_gpu": n, "parallelism": f"dp{world} (batch split; pooled outputs gathered on rank 0)",
                        "l2": "activations (103 MB per tensor at 256 images) larger than L2 at 1 and 2 GPUs; smaller beyond"},
-            "roofline": {"bound": "tensor", "achieved": achieved, "peak": peak, "unit": "TFLOP/s", "frac": achieved / peak,
-                         "traffic": None, "kernel": "conv_tc_kernel (3x3 64->64 + BN [+ skip] + ReLU, one launch)",
-                         "launch_ms": conv_avg, "flops_per_launch": flops, "peak_source": peak_src},
-            "cpu_baseline": None, "e2e": None, "gpu_launches": launches, "clocks": clocks.summary()}))
-    barrier()
+            "roofline": {"bound": "tensor", "achieved": achieved, "peak": pk["burst"], "unit": "TFLOP/s", "frac": achieved / pk["burst"],
+                         "traffic": None, "kernel": "conv_tc_kernel (3x3 64->64 + BN [+ skip] + ReLU, one launch; mean of the stage's six)",
+                         "launch_ms": conv_avg, "flops_per_launch": flops,
+                         "peak_source": pk["source"] + " bf16_tflops (burst: the launches are short)"},
+            "per_launch_ms": per_launch, "gather_check": check, "gpu_launches": launches, "clocks": clocks.summary()}
+    env.barrier()
     if world > 1:
         comm.close()
-        dist.destroy_process_group()
-
-
-def run_e2e(torch, dist, prog, x, probs, world, device, rows, e2e_steps, barrier):
-    """End to end with host buffers (rank-local slice): H2D of X, forward, D2H of the probabilities."""
-    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    x_host = torch.empty((rows, WIDTH), dtype=torch.bfloat16).pin_memory()
-    x_host.copy_(x.cpu())
-    probs_host = torch.empty((rows, CLASSES), dtype=torch.float32).pin_memory()
-    x_dev = torch.empty_like(x)
-    for _ in range(2):
-        prog.forward_host(x_host, probs_host, x_dev, probs)
-    barrier()
-    e0.record()
-    for _ in range(e2e_steps):
-        prog.forward_host(x_host, probs_host, x_dev, probs)  # every rank returns its rows to its own host buffer
-    e1.record()
-    barrier()
-    e2e_ms = e0.elapsed_time(e1)
-    if world > 1:
-        t = torch.tensor([e2e_ms], device=device)
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        e2e_ms = float(t.item())
-    e2e_value = BATCH * e2e_steps / (e2e_ms * 1e-3)
-    return e2e_value, e2e_ms, x_host, probs_host
+    del prog, x, gathered
+    torch.cuda.empty_cache()
+    return rec
 
 
 def main():
@@ -546,9 +716,9 @@ def main():
     ap.add_argument("--batch", type=int, default=BATCH, help="rows in the whole job (smaller only for profiler captures)")
     ap.add_argument("--skip-cpu-baseline", action="store_true", help="leave the CPU sample out (profiler captures)")
     ap.add_argument("--skip-e2e", action="store_true", help="leave the host-buffer pass out (profiler captures)")
-    ap.add_argument("--workload", default="widemlp", choices=["widemlp", "fcpair", "resstage"],
-                    help="widemlp: the data-parallel wide MLP (default, the headline); fcpair: the model-parallel FC pair; "
-                         "resstage: the batch-split ResNet-style conv stage")
+    ap.add_argument("--workload", default="all", choices=["all", "widemlp", "widemlp_split", "fcpair", "resstage", "latency", "ops"],
+                    help="all: the wide-MLP headline with every other workload appended under `workloads` / `ops`; "
+                         "widemlp: the headline alone; the others: that workload's record alone")
     ap.add_argument("--chunks", type=int, default=4, help="fcpair: row chunks per forward (all-reduce overlap)")
     ap.add_argument("--fcpair-rows", type=int, default=8192, help="fcpair: rows of X")
     args = ap.parse_args()
@@ -557,13 +727,55 @@ def main():
     world = int(os.environ.get("WORLD_SIZE", "1"))
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))
     if args.impl == "reference":
-        run_reference(args, rank, world)
-    elif args.workload == "fcpair":
-        run_fcpair(args, rank, world, local_rank)
-    elif args.workload == "resstage":
-        run_resstage(args, rank, world, local_rank)
-    else:
-        run_ours(args, rank, world, local_rank)
+        return run_reference(args, rank, world)
+    env = Env(rank, world, local_rank)
+    w = args.workload
+
+    def guarded(name, fn):
+        """An appended workload must not take the headline down with it: a failure is reported in its place."""
+        try:
+            return fn()
+        except Exception as e:  # noqa: BLE001
+            return {"error": f"{name}: {type(e).__name__}: {e}"[:400]}
+
+    rec = None
+    if w in ("all", "widemlp"):
+        rec = run_widemlp(env, args)
+    elif w == "widemlp_split":
+        rec = run_widemlp(env, args, split=True)
+    elif w == "fcpair":
+        rec = run_fcpair(env, args)
+    elif w == "resstage":
+        rec = run_resstage(env, args)
+    elif w in ("latency", "ops"):
+        if rank == 0:
+            from swcompiler_b200 import opbench
+            rec = {"latency": opbench.latency_rows()} if w == "latency" else {"ops": opbench.op_rows()}
+    if w == "all":
+        extra = {"resstage": guarded("resstage", lambda: run_resstage(env, args))}
+        if world > 1:
+            extra["fcpair"] = guarded("fcpair", lambda: run_fcpair(env, args))
+        extra["widemlp_split"] = guarded("widemlp_split", lambda: _brief(run_widemlp(env, args, split=True)))
+        ops = None
+        if world == 1:
+            from swcompiler_b200 import opbench
+            extra["latency"] = guarded("latency", lambda: opbench.latency_rows())
+            ops = guarded("ops", lambda: opbench.op_rows())
+        if rank == 0:
+            rec["workloads"] = extra
+            if ops is not None:
+                rec["ops"] = ops
+    if rank == 0 and rec is not None:
+        print(json.dumps(rec))
+    env.close()
+
+
+def _brief(rec):
+    """The split-precision run of the wide MLP, reduced to what differs from the headline."""
+    if rec is None:
+        return None
+    keep = ("value", "unit", "ms_per_step", "dtype", "roofline", "per_launch_ms", "gather_check", "gpu_launches")
+    return {k: rec[k] for k in keep if k in rec}
 
 
 if __name__ == "__main__":

@@ -170,6 +170,16 @@ int swcb200_pack_weight_bf16(swcb200_ctx *ctx, const float *w, int k, int n, int
 int swcb200_fc_bf16(swcb200_ctx *ctx, int m, int n, int k, const void *a_bf16, int lda,
                     const void *wp_bf16, int ldw, const float *bias, int act, void *c,
                     int c_dtype, int ldc);
+/* The same layer with SPLIT activations, for networks whose decisions hang on less than a bf16
+ * rounding of a hidden activation (the k-sequential fp32 sum of kernels.h:41-56 is the yardstick).
+ * An activation is carried as two bf16 tensors of the same shape and pitch, hi = bf16(v) and
+ * lo = bf16(v - hi); the layer computes act(A_hi . Wp^T + A_lo . Wp^T + bias) in one fp32
+ * accumulator.  a_lo NULL: the input has one term (an input that is bf16 to begin with).  c_lo
+ * non-NULL (bf16 output only): the output's second term is written there.  About twice the tensor
+ * time of swcb200_fc_bf16 when a_lo is given. */
+int swcb200_fc_bf16_split(swcb200_ctx *ctx, int m, int n, int k, const void *a_hi, const void *a_lo,
+                          int lda, const void *wp_bf16, int ldw, const float *bias, int act,
+                          void *c, void *c_lo, int c_dtype, int ldc);
 
 /* filter fp32 [oC,kh,kw,iC] -> bf16, same index order (K-major for the implicit GEMM). */
 int swcb200_pack_filter_bf16(swcb200_ctx *ctx, const float *filter, const size_t *fdims,

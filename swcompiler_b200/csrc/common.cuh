@@ -27,7 +27,7 @@ struct swcb200_ctx {
     // one word of device memory that kernels with bounded waits write a code into when a wait runs
     // out; read (and cleared) by swcb200_sync
     int *dev_status = nullptr;
-    bool fc_attr_set = false, fc_pair_attr_set = false, conv_attr_set = false;
+    bool conv_attr_set = false;
 };
 
 int swc_fail(swcb200_ctx *ctx, int status, const char *fmt, ...);

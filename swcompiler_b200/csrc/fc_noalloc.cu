@@ -33,8 +33,8 @@
 
 #include "common.cuh"
 
-int swc_fc_tc(swcb200_ctx *ctx, int m, int n, int k, const void *a, int lda, const void *wp, int ldw, const float *bias,
-              int act, void *c, int c_dtype, int ldc);
+int swc_fc_tc(swcb200_ctx *ctx, int m, int n, int k, const void *a, const void *a_lo, int lda, const void *wp, int ldw,
+              const float *bias, int act, void *c, void *c_lo, int c_dtype, int ldc);
 
 namespace {
 
@@ -133,7 +133,7 @@ SWC_EXPORT int swcb200_matrixMatrixMul_f_noalloc(int device, void *cuda_stream, 
     void *a16 = slot->scratch, *b16 = (unsigned char *)slot->scratch + a_bytes;
     rc = swc_cast_pad_rows(&ctx, a, m, k, lda, a16, (int)kp);
     if (!rc) rc = swc_pack_weight_padded(&ctx, b, k, n, ldb, b16, (int)kp);
-    if (!rc) rc = swc_fc_tc(&ctx, m, n, k, a16, (int)kp, b16, (int)kp, nullptr, SWCB200_ACT_NONE, c, SWCB200_F32, ldc);
+    if (!rc) rc = swc_fc_tc(&ctx, m, n, k, a16, nullptr, (int)kp, b16, (int)kp, nullptr, SWCB200_ACT_NONE, c, nullptr, SWCB200_F32, ldc);
     if (rc) {
         fprintf(stderr, "swcb200_matrixMatrixMul_f_noalloc: %s\n", ctx.last_error);
         return rc;

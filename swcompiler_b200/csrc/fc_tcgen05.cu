@@ -16,8 +16,13 @@
 //     128-bit global stores.  Two accumulators (2 x 256 columns = all 512 of the SM) alternate, so the
 //     epilogue of tile i overlaps the main loop of tile i+1.
 //   Out-of-range rows/columns/k are zero-filled by TMA on the way in and masked on the way out.
-#include <stdlib.h>
-
+//
+// Split activations (the SPLIT instantiations).  A bf16 activation keeps 8 bits of mantissa; on a network whose
+// top-two logits are often closer than that rounding, the stored hidden activations -- not the arithmetic --
+// decide the argmax.  In split mode a layer writes its output as TWO bf16 terms, hi = bf16(v) and
+// lo = bf16(v - hi) (together 16 bits of mantissa), and the next layer multiplies both by the same weight tile
+// into the same fp32 accumulator: C = A_hi . Wp^T + A_lo . Wp^T.  Twice the MMAs and twice the A traffic per
+// layer, the weights (bf16 by definition of the workload) unchanged.
 #include <mutex>
 #include <unordered_map>
 
@@ -67,14 +72,18 @@ constexpr int BM = 128;        // UMMA M
 constexpr int BN_MAX = 256;    // UMMA N upper bound
 constexpr int BK = 64;         // one 128-byte swizzle row of bf16
 constexpr int UMMA_K = 16;     // K per tcgen05.mma for 16-bit inputs
-constexpr int kStages = 4;
 constexpr int A_BYTES = BM * BK * 2;                 // 16 KiB
 constexpr int B_BYTES = BN_MAX * BK * 2;             // 32 KiB
-constexpr int STAGE_BYTES = A_BYTES + B_BYTES;       // 48 KiB
+// one stage of the single-CTA kernel: A [, A_lo], Wp tile; 4 stages of 48 KiB, or 3 of 64 KiB with split activations
+template <bool SPLIT> struct Single {
+    static constexpr int kStages = SPLIT ? 3 : 4;
+    static constexpr int A_TOTAL = SPLIT ? 2 * A_BYTES : A_BYTES;
+    static constexpr int STAGE_BYTES = A_TOTAL + B_BYTES;
+    static constexpr size_t kSmemBytes = (size_t)kStages * STAGE_BYTES + 1024 /*alignment slack*/ + 256 /*barriers*/;
+};
 constexpr int kTmemCols = 512;                       // two 256-column accumulators
 constexpr int kThreads = 192;                        // TMA warp, MMA warp, 4 epilogue warps
 constexpr int kEpilogueThreads = 128;
-constexpr size_t kSmemBytes = (size_t)kStages * STAGE_BYTES + 1024 /*alignment slack*/ + 256 /*barriers*/;
 
 struct FcParams {
     int m, n, k;
@@ -87,6 +96,7 @@ struct FcParams {
     int c_is_bf16;
     int ldc;
     int c_vec;  // C base and row pitch are 16-byte aligned: 128-bit stores allowed
+    void *c_lo;  // bf16 outputs only: where the rounding remainder bf16(v - bf16(v)) goes (same pitch), or null
     int *status;
 };
 
@@ -120,6 +130,7 @@ __device__ __forceinline__ void store_row_chunk(const FcParams &p, const uint32_
     }
     if (p.c_is_bf16) {
         __nv_bfloat16 *dst = reinterpret_cast<__nv_bfloat16 *>(p.c) + (size_t)row * p.ldc + col;
+        __nv_bfloat16 *dst_lo = p.c_lo ? reinterpret_cast<__nv_bfloat16 *>(p.c_lo) + (size_t)row * p.ldc + col : nullptr;
 #pragma unroll
         for (int j = 0; j < 32; j += 8) {
             if (p.c_vec && col + j + 8 <= p.n) {
@@ -130,9 +141,23 @@ __device__ __forceinline__ void store_row_chunk(const FcParams &p, const uint32_
                 h[2] = __floats2bfloat162_rn(v[j + 4], v[j + 5]);
                 h[3] = __floats2bfloat162_rn(v[j + 6], v[j + 7]);
                 *reinterpret_cast<uint4 *>(dst + j) = o;
+                if (dst_lo != nullptr) {
+                    uint4 l;
+                    __nv_bfloat162 *g = reinterpret_cast<__nv_bfloat162 *>(&l);
+#pragma unroll
+                    for (int e = 0; e < 4; e++) {
+                        const float2 hi = __bfloat1622float2(h[e]);
+                        g[e] = __floats2bfloat162_rn(v[j + 2 * e] - hi.x, v[j + 2 * e + 1] - hi.y);
+                    }
+                    *reinterpret_cast<uint4 *>(dst_lo + j) = l;
+                }
             } else {
                 for (int e = 0; e < 8; e++)
-                    if (col + j + e < p.n) dst[j + e] = __float2bfloat16_rn(v[j + e]);
+                    if (col + j + e < p.n) {
+                        const __nv_bfloat16 hi = __float2bfloat16_rn(v[j + e]);
+                        dst[j + e] = hi;
+                        if (dst_lo != nullptr) dst_lo[j + e] = __float2bfloat16_rn(v[j + e] - __bfloat162float(hi));
+                    }
             }
         }
     } else {
@@ -149,8 +174,11 @@ __device__ __forceinline__ void store_row_chunk(const FcParams &p, const uint32_
     }
 }
 
+template <bool SPLIT>
 __global__ void __launch_bounds__(kThreads, 1)
-fc_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB, const FcParams p) {
+fc_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmAlo,
+             const __grid_constant__ CUtensorMap tmB, const FcParams p) {
+    constexpr int kStages = Single<SPLIT>::kStages, STAGE_BYTES = Single<SPLIT>::STAGE_BYTES, A_TOTAL = Single<SPLIT>::A_TOTAL;
     extern __shared__ uint8_t smem_raw[];
     uint8_t *smem = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
     uint64_t *full = reinterpret_cast<uint64_t *>(smem + (size_t)kStages * STAGE_BYTES);
@@ -165,6 +193,7 @@ fc_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CU
 
     if (threadIdx.x == 0) {
         tma_prefetch_desc(&tmA);
+        if (SPLIT) tma_prefetch_desc(&tmAlo);
         tma_prefetch_desc(&tmB);
         for (int s = 0; s < kStages; s++) {
             mbar_init(&full[s], 1);
@@ -189,7 +218,7 @@ fc_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CU
     if (warp == 0) {
         // ------------------------------------------------------------ TMA producer
         if (lane == 0) {
-            const uint32_t tx_bytes = (uint32_t)(A_BYTES + p.bn * BK * 2);
+            const uint32_t tx_bytes = (uint32_t)(A_TOTAL + p.bn * BK * 2);
             uint32_t g = 0;  // k blocks issued so far (ring position)
             bool ok = true;
             for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x) {
@@ -205,7 +234,8 @@ fc_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CU
                     mbar_expect_tx(&full[s], tx_bytes);
                     uint8_t *sa = smem + (size_t)s * STAGE_BYTES;
                     tma_load_2d(sa, &tmA, &full[s], kb * BK, tm * BM);
-                    tma_load_2d(sa + A_BYTES, &tmB, &full[s], kb * BK, tn * p.bn);
+                    if (SPLIT) tma_load_2d(sa + A_BYTES, &tmAlo, &full[s], kb * BK, tm * BM);
+                    tma_load_2d(sa + A_TOTAL, &tmB, &full[s], kb * BK, tn * p.bn);
                 }
             }
             // Drain: do not leave the CTA while copies may still be landing in its shared memory.
@@ -237,11 +267,12 @@ fc_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CU
                     }
                     tc_fence_after();
                     const uint32_t sa = smem_u32(smem + (size_t)s * STAGE_BYTES);
-                    const uint64_t da = smem_desc_sw128(sa), db = smem_desc_sw128(sa + A_BYTES);
+                    const uint64_t da = smem_desc_sw128(sa), db = smem_desc_sw128(sa + A_TOTAL);
 #pragma unroll
                     for (int j = 0; j < BK / UMMA_K; j++) {
                         // advancing K by 16 elements = 32 bytes inside the swizzle row: +2 in the >>4 address field
                         umma_bf16(d_tmem, da + 2 * j, db + 2 * j, idesc, (uint32_t)((kb | j) != 0));
+                        if (SPLIT) umma_bf16(d_tmem, da + (A_BYTES >> 4) + 2 * j, db + 2 * j, idesc, 1u);  // the lo term, same weights
                     }
                     umma_commit(&empty[s]);  // stage reusable once these MMAs have read it
                 }
@@ -297,13 +328,20 @@ fc_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CU
 //   barriers: full[s] lives in the leader and counts the bytes of BOTH CTAs' loads; empty[s] and
 //   tmem_full[b] exist in both CTAs and are signalled together by one tcgen05.commit; tmem_empty[b] lives in
 //   the leader and collects the epilogue warps of both CTAs.
-constexpr int kStages2 = 6;
 constexpr int B2_BYTES = (BN_MAX / 2) * BK * 2;       // 16 KiB: this CTA's half of the Wp tile
-constexpr int STAGE2_BYTES = A_BYTES + B2_BYTES;      // 32 KiB
-constexpr size_t kSmemBytes2 = (size_t)kStages2 * STAGE2_BYTES + 1024 + 256;
+// one stage of the pair kernel: A [, A_lo], half Wp tile; 6 stages of 32 KiB, or 4 of 48 KiB with split activations
+template <bool SPLIT> struct Pair {
+    static constexpr int kStages = SPLIT ? 4 : 6;
+    static constexpr int A_TOTAL = SPLIT ? 2 * A_BYTES : A_BYTES;
+    static constexpr int STAGE_BYTES = A_TOTAL + B2_BYTES;
+    static constexpr size_t kSmemBytes = (size_t)kStages * STAGE_BYTES + 1024 + 256;
+};
 
+template <bool SPLIT>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads, 1)
-fc_tc_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB, const FcParams p) {
+fc_tc_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmAlo,
+                  const __grid_constant__ CUtensorMap tmB, const FcParams p) {
+    constexpr int kStages2 = Pair<SPLIT>::kStages, STAGE2_BYTES = Pair<SPLIT>::STAGE_BYTES, A_TOTAL = Pair<SPLIT>::A_TOTAL;
     extern __shared__ uint8_t smem_raw[];
     uint8_t *smem = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
     uint64_t *full = reinterpret_cast<uint64_t *>(smem + (size_t)kStages2 * STAGE2_BYTES);
@@ -322,6 +360,7 @@ fc_tc_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
 
     if (threadIdx.x == 0) {
         tma_prefetch_desc(&tmA);
+        if (SPLIT) tma_prefetch_desc(&tmAlo);
         tma_prefetch_desc(&tmB);
         for (int s = 0; s < kStages2; s++) {
             mbar_init(&full[s], 1);
@@ -348,7 +387,7 @@ fc_tc_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
     if (warp == 0) {
         // ------------------------------------------------------------ TMA producer (one per CTA)
         if (lane == 0) {
-            const uint32_t tx_bytes = 2u * (uint32_t)(A_BYTES + half_bn * BK * 2);  // both CTAs' boxes
+            const uint32_t tx_bytes = 2u * (uint32_t)(A_TOTAL + half_bn * BK * 2);  // both CTAs' boxes
             int st = 0;
             uint32_t ph = 0;
             for (int t = cluster_id; t < num_tiles && !failed; t += num_clusters) {
@@ -364,7 +403,8 @@ fc_tc_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
                     if (leader) mbar_expect_tx(&full[st], tx_bytes);
                     uint8_t *sa = smem + (size_t)st * STAGE2_BYTES;
                     tma_load_2d_pair(sa, &tmA, full_leader, kb * BK, row_a);
-                    tma_load_2d_pair(sa + A_BYTES, &tmB, full_leader, kb * BK, row_b);
+                    if (SPLIT) tma_load_2d_pair(sa + A_BYTES, &tmAlo, full_leader, kb * BK, row_a);
+                    tma_load_2d_pair(sa + A_TOTAL, &tmB, full_leader, kb * BK, row_b);
                     if (++st == kStages2) {
                         st = 0;
                         ph ^= 1;
@@ -376,7 +416,7 @@ fc_tc_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
         // ------------------------------------------------------------ MMA issuer (leader CTA only)
         if (leader && lane == 0) {
             const uint32_t idesc = idesc_bf16_f32(2 * BM, p.bn);
-            const uint64_t da0 = smem_desc_sw128(smem_u32(smem)), db0 = smem_desc_sw128(smem_u32(smem + A_BYTES));
+            const uint64_t da0 = smem_desc_sw128(smem_u32(smem)), db0 = smem_desc_sw128(smem_u32(smem + A_TOTAL));
             int st = 0;
             uint32_t ph = 0, it = 0;
             for (int t = cluster_id; t < num_tiles && !failed; t += num_clusters, it++) {
@@ -396,9 +436,13 @@ fc_tc_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
                     const uint64_t off = (uint64_t)st * (STAGE2_BYTES >> 4);
                     const uint64_t da = da0 + off, db = db0 + off;
                     umma_bf16_pair(d_tmem, da, db, idesc, (uint32_t)(kb != 0));
+                    if (SPLIT) umma_bf16_pair(d_tmem, da + (A_BYTES >> 4), db, idesc, 1u);  // the lo term, same weights
                     umma_bf16_pair(d_tmem, da + 2, db + 2, idesc, 1u);
+                    if (SPLIT) umma_bf16_pair(d_tmem, da + (A_BYTES >> 4) + 2, db + 2, idesc, 1u);
                     umma_bf16_pair(d_tmem, da + 4, db + 4, idesc, 1u);
+                    if (SPLIT) umma_bf16_pair(d_tmem, da + (A_BYTES >> 4) + 4, db + 4, idesc, 1u);
                     umma_bf16_pair(d_tmem, da + 6, db + 6, idesc, 1u);
+                    if (SPLIT) umma_bf16_pair(d_tmem, da + (A_BYTES >> 4) + 6, db + 6, idesc, 1u);
                     umma_commit_pair(&empty[st], 3);  // both CTAs' stage `st` may be refilled once these have read it
                     if (++st == kStages2) {
                         st = 0;
@@ -501,20 +545,42 @@ int tmap_2d(swcb200_ctx *ctx, const void *base, uint64_t rows, uint64_t cols, ui
 
 }  // namespace
 
-// SWCB200_FC_SINGLE_CTA=1 in the environment keeps every launch on the single-CTA kernel (for A/B timing).
-static bool swc_fc_force_single() {
-    static int v = -1;
-    if (v < 0) {
-        const char *e = getenv("SWCB200_FC_SINGLE_CTA");
-        v = (e && e[0] == '1') ? 1 : 0;
+template <bool SPLIT>
+static int launch_fc(swcb200_ctx *ctx, bool pair, const CUtensorMap &tmA, const CUtensorMap &tmAlo, const CUtensorMap &tmB,
+                     FcParams &p, int m) {
+    static bool attr_single[64] = {false}, attr_pair[64] = {false};  // per device: the opt-in to large dynamic shared memory
+    const int dev = ctx->device & 63;
+    if (pair) {
+        p.tiles_m = (m + 2 * BM - 1) / (2 * BM);
+        if (!attr_pair[dev]) {
+            SWC_CUDA(ctx, cudaFuncSetAttribute(fc_tc_pair_kernel<SPLIT>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                               (int)Pair<SPLIT>::kSmemBytes));
+            attr_pair[dev] = true;
+        }
+        const long long tiles2 = (long long)p.tiles_m * p.tiles_n;
+        const long long max_clusters = ctx->sm_count / 2;
+        unsigned grid2 = 2u * (unsigned)(tiles2 < max_clusters ? tiles2 : max_clusters);
+        fc_tc_pair_kernel<SPLIT><<<grid2, kThreads, Pair<SPLIT>::kSmemBytes, ctx->stream>>>(tmA, tmAlo, tmB, p);
+        return swc_check_launch(ctx, "fc_bf16");
     }
-    return v == 1;
+    if (!attr_single[dev]) {
+        SWC_CUDA(ctx, cudaFuncSetAttribute(fc_tc_kernel<SPLIT>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                           (int)Single<SPLIT>::kSmemBytes));
+        attr_single[dev] = true;
+    }
+    const long long tiles = (long long)p.tiles_m * p.tiles_n;
+    unsigned grid = (unsigned)(tiles < ctx->sm_count ? tiles : ctx->sm_count);
+    fc_tc_kernel<SPLIT><<<grid, kThreads, Single<SPLIT>::kSmemBytes, ctx->stream>>>(tmA, tmAlo, tmB, p);
+    return swc_check_launch(ctx, "fc_bf16");
 }
 
-int swc_fc_tc(swcb200_ctx *ctx, int m, int n, int k, const void *a, int lda, const void *wp, int ldw, const float *bias,
-              int act, void *c, int c_dtype, int ldc) {
-    SWC_REQUIRE(ctx, swc_aligned16(a) && swc_aligned16(wp), SWCB200_ERR_MISALIGNED,
+// a_lo / c_lo: the second term of a split activation (see the top of the file), or null
+int swc_fc_tc(swcb200_ctx *ctx, int m, int n, int k, const void *a, const void *a_lo, int lda, const void *wp, int ldw,
+              const float *bias, int act, void *c, void *c_lo, int c_dtype, int ldc) {
+    SWC_REQUIRE(ctx, swc_aligned16(a) && swc_aligned16(wp) && swc_aligned16(a_lo), SWCB200_ERR_MISALIGNED,
                 "fc_bf16: A and Wp must be 16-byte aligned");
+    SWC_REQUIRE(ctx, c_lo == nullptr || c_dtype == SWCB200_BF16, SWCB200_ERR_BAD_ARG,
+                "fc_bf16: a remainder output only goes with a bf16 output");
     SWC_REQUIRE(ctx, lda % 8 == 0 && ldw % 8 == 0, SWCB200_ERR_MISALIGNED,
                 "fc_bf16: lda (%d) and ldw (%d) must be multiples of 8 elements", lda, ldw);
     SWC_REQUIRE(ctx, lda >= k && ldw >= k && ldc >= n, SWCB200_ERR_BAD_SHAPE, "fc_bf16: leading dimension too small");
@@ -535,35 +601,22 @@ int swc_fc_tc(swcb200_ctx *ctx, int m, int n, int k, const void *a, int lda, con
     p.c = c;
     p.c_is_bf16 = c_dtype == SWCB200_BF16;
     p.ldc = ldc;
-    p.c_vec = swc_aligned16(c) && ((size_t)ldc * celem) % 16 == 0;
+    p.c_vec = swc_aligned16(c) && swc_aligned16(c_lo) && ((size_t)ldc * celem) % 16 == 0;
+    p.c_lo = c_lo;
     p.status = ctx->dev_status;
     // CTA pairs whenever there is more than one 128-row panel and the tile is wide enough to halve
-    const bool pair = m > BM && bn >= 64 && ctx->sm_count >= 2 && !swc_fc_force_single();
-    CUtensorMap tmA, tmB;
+    const bool pair = m > BM && bn >= 64 && ctx->sm_count >= 2;
+    CUtensorMap tmA, tmAlo, tmB;
     int rc = tmap_2d(ctx, a, (uint64_t)m, (uint64_t)k, (uint64_t)lda, BM, &tmA);
     if (rc) return rc;
+    tmAlo = tmA;
+    if (a_lo != nullptr) {
+        rc = tmap_2d(ctx, a_lo, (uint64_t)m, (uint64_t)k, (uint64_t)lda, BM, &tmAlo);
+        if (rc) return rc;
+    }
     rc = tmap_2d(ctx, wp, (uint64_t)n, (uint64_t)k, (uint64_t)ldw, (uint32_t)(pair ? bn / 2 : bn), &tmB);
     if (rc) return rc;
-    if (pair) {
-        p.tiles_m = (m + 2 * BM - 1) / (2 * BM);
-        if (!ctx->fc_pair_attr_set) {
-            SWC_CUDA(ctx, cudaFuncSetAttribute(fc_tc_pair_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSmemBytes2));
-            ctx->fc_pair_attr_set = true;
-        }
-        const long long tiles2 = (long long)p.tiles_m * p.tiles_n;
-        const long long max_clusters = ctx->sm_count / 2;
-        unsigned grid2 = 2u * (unsigned)(tiles2 < max_clusters ? tiles2 : max_clusters);
-        fc_tc_pair_kernel<<<grid2, kThreads, kSmemBytes2, ctx->stream>>>(tmA, tmB, p);
-        return swc_check_launch(ctx, "fc_bf16");
-    }
-    if (!ctx->fc_attr_set) {
-        SWC_CUDA(ctx, cudaFuncSetAttribute(fc_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSmemBytes));
-        ctx->fc_attr_set = true;
-    }
-    const long long tiles = (long long)p.tiles_m * p.tiles_n;
-    unsigned grid = (unsigned)(tiles < ctx->sm_count ? tiles : ctx->sm_count);
-    fc_tc_kernel<<<grid, kThreads, kSmemBytes, ctx->stream>>>(tmA, tmB, p);
-    return swc_check_launch(ctx, "fc_bf16");
+    return a_lo != nullptr ? launch_fc<true>(ctx, pair, tmA, tmAlo, tmB, p, m) : launch_fc<false>(ctx, pair, tmA, tmAlo, tmB, p, m);
 }
 
 SWC_EXPORT int swcb200_fc_bf16(swcb200_ctx *ctx, int m, int n, int k, const void *a_bf16, int lda, const void *wp_bf16,
@@ -574,7 +627,19 @@ SWC_EXPORT int swcb200_fc_bf16(swcb200_ctx *ctx, int m, int n, int k, const void
     SWC_REQUIRE(ctx, c_dtype == SWCB200_F32 || c_dtype == SWCB200_BF16, SWCB200_ERR_BAD_ARG, "fc_bf16: unknown output dtype");
     if (m == 0 || n == 0) return SWCB200_OK;
     SWC_REQUIRE(ctx, a_bf16 && wp_bf16 && c, SWCB200_ERR_BAD_ARG, "fc_bf16: null tensor");
-    return swc_fc_tc(ctx, m, n, k, a_bf16, lda, wp_bf16, ldw, bias, act, c, c_dtype, ldc);
+    return swc_fc_tc(ctx, m, n, k, a_bf16, nullptr, lda, wp_bf16, ldw, bias, act, c, nullptr, c_dtype, ldc);
+}
+
+SWC_EXPORT int swcb200_fc_bf16_split(swcb200_ctx *ctx, int m, int n, int k, const void *a_hi, const void *a_lo, int lda,
+                                     const void *wp_bf16, int ldw, const float *bias, int act, void *c, void *c_lo,
+                                     int c_dtype, int ldc) {
+    SWC_CTX(ctx);
+    SWC_REQUIRE(ctx, m >= 0 && n >= 0 && k > 0, SWCB200_ERR_BAD_ARG, "fc_bf16_split: bad shape %d x %d x %d", m, n, k);
+    SWC_REQUIRE(ctx, act >= SWCB200_ACT_NONE && act <= SWCB200_ACT_TANH, SWCB200_ERR_BAD_ARG, "fc_bf16_split: unknown activation");
+    SWC_REQUIRE(ctx, c_dtype == SWCB200_F32 || c_dtype == SWCB200_BF16, SWCB200_ERR_BAD_ARG, "fc_bf16_split: unknown output dtype");
+    if (m == 0 || n == 0) return SWCB200_OK;
+    SWC_REQUIRE(ctx, a_hi && wp_bf16 && c, SWCB200_ERR_BAD_ARG, "fc_bf16_split: null tensor");
+    return swc_fc_tc(ctx, m, n, k, a_hi, a_lo, lda, wp_bf16, ldw, bias, act, c, c_lo, c_dtype, ldc);
 }
 
 int swc_fc_strict(swcb200_ctx *ctx, int m, int n, int k, const float *a, int lda, const float *b, int ldb, float *c,
@@ -603,5 +668,5 @@ SWC_EXPORT int swcb200_matrixMatrixMul_f(swcb200_ctx *ctx, int m, int n, int k, 
     if (rc) return rc;
     rc = swc_pack_weight_padded(ctx, b, k, n, ldb, b16, (int)kp);
     if (rc) return rc;
-    return swc_fc_tc(ctx, m, n, k, a16, (int)kp, b16, (int)kp, nullptr, SWCB200_ACT_NONE, c, SWCB200_F32, ldc);
+    return swc_fc_tc(ctx, m, n, k, a16, nullptr, (int)kp, b16, (int)kp, nullptr, SWCB200_ACT_NONE, c, nullptr, SWCB200_F32, ldc);
 }

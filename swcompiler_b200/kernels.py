@@ -236,16 +236,27 @@ class Backend:
         self._call("pack_weight_bf16", _p(w), C.c_int(k), C.c_int(n), C.c_int(n), _p(wp))
         return wp
 
-    def fc_bf16(self, a, wp, bias=None, act=L.ACT_NONE, out_dtype=torch.bfloat16, out=None):
-        """act(A[m,k] . Wp[n,k]^T + bias) in one launch; A, Wp bf16."""
+    def fc_bf16(self, a, wp, bias=None, act=L.ACT_NONE, out_dtype=torch.bfloat16, out=None, a_lo=None, out_lo=None):
+        """act(A[m,k] . Wp[n,k]^T + bias) in one launch; A, Wp bf16.  With `a_lo` the input is a split activation
+        (A = a + a_lo, two bf16 terms); with `out_lo` (bf16 outputs) the output's second term is written there."""
         if a.dtype != torch.bfloat16 or wp.dtype != torch.bfloat16 or not (a.is_contiguous() and wp.is_contiguous()):
             raise ValueError("fc_bf16 wants contiguous bf16 operands")
         (m, k), (n, k2) = a.shape, wp.shape
         if k != k2:
             raise ValueError("inner dimensions differ")
         out = out if out is not None else self._new((m, n), out_dtype)
-        self._call("fc_bf16", C.c_int(m), C.c_int(n), C.c_int(k), _p(a), C.c_int(k), _p(wp), C.c_int(k), _p(bias),
-                   C.c_int(act), _p(out), C.c_int(L.BF16 if out.dtype == torch.bfloat16 else L.F32), C.c_int(n))
+        dt = C.c_int(L.BF16 if out.dtype == torch.bfloat16 else L.F32)
+        if a_lo is None and out_lo is None:
+            self._call("fc_bf16", C.c_int(m), C.c_int(n), C.c_int(k), _p(a), C.c_int(k), _p(wp), C.c_int(k), _p(bias),
+                       C.c_int(act), _p(out), dt, C.c_int(n))
+            return out
+        for t in (a_lo, out_lo):
+            if t is not None and not (t.dtype == torch.bfloat16 and t.is_contiguous()):
+                raise ValueError("the second term of a split activation is a contiguous bf16 tensor")
+        if (a_lo is not None and a_lo.shape != a.shape) or (out_lo is not None and out_lo.shape != out.shape):
+            raise ValueError("the two terms of a split activation have the same shape")
+        self._call("fc_bf16_split", C.c_int(m), C.c_int(n), C.c_int(k), _p(a), _p(a_lo), C.c_int(k), _p(wp), C.c_int(k),
+                   _p(bias), C.c_int(act), _p(out), _p(out_lo), dt, C.c_int(n))
         return out
 
     def pack_filter_bf16(self, filt):

@@ -39,12 +39,13 @@ def _time(fn, iters):
     return e0.elapsed_time(e1) / iters * 1e-3
 
 
-def latency(iters):
+def latency_rows(iters=50):
     """The two configurations that are bound by launch latency, not by any roofline (52 and 182 MFLOP per forward):
     X[64,784] -> FC 784->512 -> Tanh -> FC 512->10 -> Softmax, and [32,28,28,1] -> Conv5x5 1->16 -> ReLU -> MaxPool ->
     Conv5x5 16->32 -> ReLU -> MaxPool -> FC 1568->10 -> Softmax.  One table call per op node, strict fp32 kernels and
-    the tensor-core mode of the same entry points; microseconds per forward pass and samples per second."""
-    dev = torch.device("cuda", 0)
+    the tensor-core mode of the same entry points; microseconds per forward pass and samples per second, launched call
+    by call and replayed as a CUDA graph (the form the generator prints with graph_replays)."""
+    dev = torch.device("cuda", torch.cuda.current_device())
     g = torch.Generator(device=dev).manual_seed(1001)
     rn = lambda *shape, s=1.0: torch.randn(shape, generator=g, device=dev) * s
     x1, w0, b0, w1, b1 = torch.rand((64, 784), generator=g, device=dev), rn(784, 512, s=0.05), torch.zeros(512, device=dev), \
@@ -54,25 +55,41 @@ def latency(iters):
     cw1, cb1 = rn(32, 5, 5, 16, s=(2 / 400) ** 0.5), torch.zeros(32, device=dev)
     fw, fb = rn(1568, 10, s=0.02), torch.zeros(10, device=dev)
     k5, s1, p2, k2, s2, p0 = (5, 5), (1, 1), (2, 2, 2, 2), (2, 2), (2, 2), (0, 0, 0, 0)
+    rows = []
+    stream = torch.cuda.Stream(dev)
     for mode, name in ((swc.STRICT_F32, "strict fp32"), (swc.TC_BF16, "tensor-core mode")):
-        be = swc.Backend(0, mode)
+        with torch.cuda.stream(stream):
+            be = swc.Backend(dev.index, mode, stream=stream)
 
-        def mlp():
-            return be.mlp_forward(x1, w0, b0, w1, b1)
+            def mlp():
+                return be.mlp_forward(x1, w0, b0, w1, b1)
 
-        def lenet():
-            h = be.maxpool_f(be.relu_f(be.conv2d_f(x2, cw0, cb0, k5, s1, p2)), k2, s2, p0)
-            h = be.maxpool_f(be.relu_f(be.conv2d_f(h, cw1, cb1, k5, s1, p2)), k2, s2, p0)
-            return be.matrixSoftmax_f(be.fc(h, fw, fb))
+            def lenet():
+                h = be.maxpool_f(be.relu_f(be.conv2d_f(x2, cw0, cb0, k5, s1, p2)), k2, s2, p0)
+                h = be.maxpool_f(be.relu_f(be.conv2d_f(h, cw1, cb1, k5, s1, p2)), k2, s2, p0)
+                return be.matrixSoftmax_f(be.fc(h, fw, fb))
 
-        for label, fn, batch in (("MLP 784-512-10, batch 64", mlp, 64), ("LeNet-style conv net, batch 32", lenet, 32)):
-            n0 = be.launches
-            fn()
-            per_forward = be.launches - n0
-            t = _time(fn, iters)
-            print(json.dumps({"config": label, "mode": name, "us_per_forward": t * 1e6, "samples_per_s": batch / t,
-                              "launches_per_forward": per_forward}))
-        be.sync()
+            for label, fn, batch in (("MLP 784-512-10, batch 64", mlp, 64), ("LeNet-style conv net, batch 32", lenet, 32)):
+                n0 = be.launches
+                fn()
+                per_forward = be.launches - n0
+                t = _time(fn, iters)
+                # the same calls captured once and replayed: what remains is the kernels' own time
+                stream.synchronize()
+                graph = torch.cuda.CUDAGraph()
+                with torch.cuda.graph(graph, stream=stream):
+                    fn()
+                tg = _time(graph.replay, iters)
+                rows.append({"config": label, "mode": name, "us_per_forward": t * 1e6, "samples_per_s": batch / t,
+                             "graph_us_per_forward": tg * 1e6, "graph_samples_per_s": batch / tg,
+                             "launches_per_forward": per_forward})
+            be.sync()
+    return rows
+
+
+def latency(iters):
+    for r in latency_rows(iters):
+        print(json.dumps(r))
 
 
 def conv_roles():
@@ -107,21 +124,12 @@ def conv_roles():
                           "cta0_cycles": t[7], "cta0_ns": t[8], "ghz": t[7] / max(1, t[8]), "marks": {"prologue_done": t[9], "filter_ready": t[10], "issuer_done": t[11], "epi_loop_done": t[12], "stores_done": t[13]}}))
 
 
-def main():
-    ap = argparse.ArgumentParser()
-    ap.add_argument("--only", default=None)
-    ap.add_argument("--iters", type=int, default=20)
-    ap.add_argument("--latency", action="store_true",
-                    help="the two small configurations (MLP batch 64, LeNet-style net batch 32): microseconds per forward")
-    ap.add_argument("--conv-roles", action="store_true",
-                    help="per-role cycle counters of the convolution kernel (library built with --conv-timing)")
-    args = ap.parse_args()
-    if args.conv_roles:
-        return conv_roles()
-    if args.latency:
-        return latency(args.iters)
+def op_rows(iters=20, only=None):
+    """One row per kernel at the benchmark configurations' sizes: achieved GB/s or TFLOP/s and the fraction of the
+    measured peak (see the module docstring)."""
+    rows = []
     hbm, tflops, src = _peaks()
-    be = swc.Backend(0, swc.STRICT_F32)
+    be = swc.Backend(torch.cuda.current_device(), swc.STRICT_F32)
     dev = be.device
     g = torch.Generator(device=dev).manual_seed(0)
     stage = (256, 56, 56, 64)
@@ -153,39 +161,39 @@ def main():
         ("cast_f32_to_bf16", 6 * E, lambda: be.cast_f32_to_bf16(x, out=xb)),
     ]
     for name, nbytes, fn in mem_ops:
-        if args.only and args.only not in name:
+        if only and only not in name:
             continue
-        t = _time(fn, args.iters)
-        print(json.dumps({"kernel": name, "bound": "hbm", "us": t * 1e6, "achieved": nbytes / t / 1e9, "unit": "GB/s",
+        t = _time(fn, iters)
+        rows.append(({"kernel": name, "bound": "hbm", "us": t * 1e6, "achieved": nbytes / t / 1e9, "unit": "GB/s",
                           "peak": hbm, "frac": nbytes / t / 1e9 / hbm, "peak_source": src, "bytes": nbytes}))
     be.set_precision(swc.TC_BF16)
     for name, nbytes, fn in [
         ("matrixTanh_f fast [32768,4096]", 8 * act.numel(), lambda: be.matrixTanh_f(act, out=act_out)),
         ("matrixSoftmax_f fast [65536,1000]", 8 * logits.numel(), lambda: be.matrixSoftmax_f(logits, out=probs)),
     ]:
-        if args.only and args.only not in name:
+        if only and only not in name:
             continue
-        t = _time(fn, args.iters)
-        print(json.dumps({"kernel": name, "bound": "hbm", "us": t * 1e6, "achieved": nbytes / t / 1e9, "unit": "GB/s",
+        t = _time(fn, iters)
+        rows.append(({"kernel": name, "bound": "hbm", "us": t * 1e6, "achieved": nbytes / t / 1e9, "unit": "GB/s",
                           "peak": hbm, "frac": nbytes / t / 1e9 / hbm, "peak_source": src, "bytes": nbytes}))
     del act, act_out, logits, probs
 
     # tensor-core FC shapes (bf16, fp32 accumulate): config 3 hidden layer and last layer, config 4 per-GPU shards at p = 8
     for (m, n, k) in [(65536, 4096, 4096), (65536, 1000, 4096), (8192, 4096, 8192), (8192, 8192, 4096)]:
         name = f"fc_bf16 {m}x{n}x{k}"
-        if args.only and args.only not in name:
+        if only and only not in name:
             continue
         a = torch.randn((m, k), generator=g, device=dev).to(torch.bfloat16)
         wp = (torch.randn((n, k), generator=g, device=dev) / k ** 0.5).to(torch.bfloat16)
         b = torch.randn(n, generator=g, device=dev)
         o = torch.empty((m, n), device=dev, dtype=torch.bfloat16)
-        t = _time(lambda: be.fc_bf16(a, wp, b, swc.ACT_RELU, out=o), args.iters)
+        t = _time(lambda: be.fc_bf16(a, wp, b, swc.ACT_RELU, out=o), iters)
         fl = 2.0 * m * n * k
-        print(json.dumps({"kernel": name, "bound": "tensor", "us": t * 1e6, "achieved": fl / t / 1e12, "unit": "TFLOP/s",
+        rows.append(({"kernel": name, "bound": "tensor", "us": t * 1e6, "achieved": fl / t / 1e12, "unit": "TFLOP/s",
                           "peak": tflops, "frac": fl / t / 1e12 / tflops, "peak_source": src + " (burst)", "flops": fl}))
         del a, wp, o
     # config 5: 3x3 64->64 convolution on [256,56,56,64] with the fused epilogue, and the whole stage
-    if not args.only or "conv" in args.only or "stage" in args.only:
+    if not only or "conv" in only or "stage" in only:
         from .programs import ResStageProgram
         n, hw, ch = 256, 56, 64
         xin = torch.randn((n, hw, hw, ch), generator=g, device=dev).to(torch.bfloat16)
@@ -204,16 +212,34 @@ def main():
              lambda: be.conv2d_bf16(xin, prog.fp[1], prog.cb[1], (3, 3), (1, 1), (1, 1, 1, 1), bn=prog.bn[1], residual=xin,
                                     relu=True, out=o)),
         ]:
-            t = _time(fn, args.iters)
-            print(json.dumps({"kernel": name, "bound": "tensor", "us": t * 1e6, "achieved": fl / t / 1e12, "unit": "TFLOP/s",
+            t = _time(fn, iters)
+            rows.append(({"kernel": name, "bound": "tensor", "us": t * 1e6, "achieved": fl / t / 1e12, "unit": "TFLOP/s",
                               "peak": tflops, "frac": fl / t / 1e12 / tflops, "peak_source": src + " (burst)", "flops": fl,
                               "hbm_GBps": (2 * xin.numel() * 2) / t / 1e9}))
-        t = _time(lambda: prog.forward(xin), args.iters)
-        print(json.dumps({"kernel": "res stage forward (config 5): 6 fused convs + maxpool, batch 256", "bound": "tensor",
+        t = _time(lambda: prog.forward(xin), iters)
+        rows.append(({"kernel": "res stage forward (config 5): 6 fused convs + maxpool, batch 256", "bound": "tensor",
                           "us": t * 1e6, "achieved": prog.flops(n) / t / 1e12, "unit": "TFLOP/s", "peak": tflops,
                           "frac": prog.flops(n) / t / 1e12 / tflops, "peak_source": src + " (burst)",
                           "samples_per_s": n / t, "launches": prog.launches_per_forward}))
     be.sync()
+    return rows
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--only", default=None)
+    ap.add_argument("--iters", type=int, default=20)
+    ap.add_argument("--latency", action="store_true",
+                    help="the two small configurations (MLP batch 64, LeNet-style net batch 32): microseconds per forward")
+    ap.add_argument("--conv-roles", action="store_true",
+                    help="per-role cycle counters of the convolution kernel (library built with --conv-timing)")
+    args = ap.parse_args()
+    if args.conv_roles:
+        return conv_roles()
+    if args.latency:
+        return latency(args.iters)
+    for r in op_rows(args.iters, args.only):
+        print(json.dumps(r))
 
 
 if __name__ == "__main__":

@@ -106,6 +106,49 @@ def test_config3_slice_logits_and_argmax(be, oracle):
     assert raw >= 0.99, raw
 
 
+def test_split_activation_layer_against_oracle(be, oracle):
+    """One layer with a two-term (hi + lo) input and a two-term output, shapes that take the CTA-pair kernel and the
+    single-CTA kernel: the product of the fp32 activation hi + lo with the bf16-rounded weights, and hi + lo of the
+    output, agree with the oracle far below one bf16 rounding."""
+    r = np.random.default_rng(12)
+    for (m, k, n) in ((384, 512, 320), (100, 264, 72), (1024, 4096, 1000)):
+        a = r.standard_normal((m, k)).astype(np.float32)
+        w = cases.bf16_round((r.standard_normal((k, n)) / np.sqrt(k)).astype(np.float32))
+        bias = (r.standard_normal(n) * 0.1).astype(np.float32)
+        a_hi = cases.bf16_round(a)
+        a_lo = cases.bf16_round(a - a_hi)
+        want = np.maximum(oracle.batchedadd_f(oracle.matrixMatrixMul_f(a_hi + a_lo, w), bias), 0)
+        wp = be.pack_weight_bf16(torch.from_numpy(w).cuda())
+        out_lo = torch.empty((m, n), dtype=torch.bfloat16, device="cuda")
+        out = be.fc_bf16(_bf16(a_hi), wp, torch.from_numpy(bias).cuda(), swc.ACT_RELU, torch.bfloat16, a_lo=_bf16(a_lo), out_lo=out_lo)
+        f32 = be.fc_bf16(_bf16(a_hi), wp, torch.from_numpy(bias).cuda(), swc.ACT_RELU, torch.float32, a_lo=_bf16(a_lo))
+        be.sync()
+        scale = float(np.abs(want).max())
+        assert np.abs(f32.cpu().numpy() - want).max() <= 2e-5 * scale + 1e-5, (m, k, n)
+        two_terms = out.float().cpu().numpy() + out_lo.float().cpu().numpy()
+        assert np.abs(two_terms - want).max() <= 4e-5 * scale + 1e-5, (m, k, n)      # 16 bits of mantissa
+        assert np.array_equal(out.float().cpu().numpy(), cases.bf16_round(f32.cpu().numpy()))   # hi is the plain rounding
+
+
+def test_config3_slice_argmax_with_split_activations(be, oracle):
+    """The same 1024 rows with hidden activations carried as two bf16 terms: the stored activations no longer decide
+    the winner, and the argmax agrees with the fp32 oracle on at least 99.9 % of the rows."""
+    from swcompiler_b200.programs import WideMlpProgram
+    c = cases.config3_wide_mlp(batch=1024)
+    want_logits = cases.wide_mlp_forward(oracle, c, softmax=False)
+    prog = WideMlpProgram(be, [torch.from_numpy(w).cuda() for w in c["w"]], [torch.from_numpy(b).cuda() for b in c["b"]],
+                          max_rows=1024, split=True)
+    probs = torch.empty((1024, 1000), dtype=torch.float32, device="cuda")
+    prog.forward(_bf16(c["x"]), probs)
+    top = be.argMax_i(probs, 1).cpu().numpy()[:, 0]
+    be.sync()
+    err = float(np.abs(prog.logits.cpu().numpy() - want_logits).max())
+    raw = float(np.mean(top == oracle.argMax_i(want_logits, 1)[:, 0]))
+    print(f"config3 slice, split activations: logits max-abs err {err:.2e}; raw argmax agreement {raw:.4f}")
+    assert err <= 2e-3, err
+    assert raw >= 0.999, raw
+
+
 def test_fc_bf16_at_full_config3_size_sampled_rows(be, oracle):
     """One 65536 x 4096 x 4096 layer; 96 sampled rows are checked against the oracle run on those rows alone."""
     g = torch.Generator(device="cuda").manual_seed(7)
