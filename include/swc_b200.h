@@ -106,14 +106,18 @@ int swcb200_accuracy_i(swcb200_ctx *ctx, const int *pred, const int *label, int 
  * fixed memory budget, code running between the collectives of a multi-GPU job).  It has no counterpart
  * in the reference.  The bf16 operand copies live in a fixed 40 MiB array inside the library, held by every
  * GPU that loads the library until the process exits; sizes with 2*roundup(k,8)*(m+n) beyond 40 MiB return
- * SWCB200_ERR_TOO_LARGE.  No context is needed: kernels go on `cuda_stream` of `device`, and the call
- * returns after that stream has drained.  The first call on a device caches the array's device address;
- * make it outside stream capture.  All calls on a device share the array (its old contents are
- * overwritten where they matter; nothing needs clearing), so calls that overlap on one GPU race: serialise
- * them.  Calls no cudaMalloc / cudaFree or allocating library routine. */
+ * SWCB200_ERR_TOO_LARGE.  No context is needed: kernels go on `cuda_stream` of `device`, and EVERY call waits
+ * for that stream before it returns (C is complete on return, the host thread blocks).  So no call may be made
+ * while the stream is being captured; the first call on a device, which also caches the array's device
+ * address, least of all.  The calling thread's current device is left as it was.  All calls on a device
+ * share the array (its old contents are overwritten where they matter; nothing needs clearing), so calls
+ * that overlap on one GPU race: serialise them.  Calls no cudaMalloc / cudaFree or allocating library
+ * routine, and prints nothing: the calling thread's last failure is described by
+ * swcb200_matrixMatrixMul_f_noalloc_last_error(). */
 int swcb200_matrixMatrixMul_f_noalloc(int device, void *cuda_stream, int m, int n, int k,
                                       const float *a, int lda, const float *b, int ldb, float *c,
                                       int ldc);
+const char *swcb200_matrixMatrixMul_f_noalloc_last_error(void);
 
 /* ------------------------------------------------------- flat elementwise */
 

@@ -19,10 +19,15 @@
 //
 // Rules for callers
 //   * The first call on each device looks up the device address of the array (and of the status word)
-//     and caches it.  Make that first call outside any stream capture.
+//     and caches it.
 //   * The function needs no context.  It issues its kernels on the stream it is given, then waits for
 //     that stream before it returns, so on return C is complete and a device-side timeout has been
-//     turned into a status.
+//     turned into a status.  Because EVERY call ends with that wait (and a small blocking read-back of
+//     the status word), no call -- not only the first -- may be made while the stream is being
+//     captured, and the call blocks the host thread.
+//   * The calling thread's current device is the same after the call as before it.
+//   * Nothing is printed.  What went wrong with the calling thread's last failed call can be read with
+//     swcb200_matrixMatrixMul_f_noalloc_last_error().
 //   * All calls on one device share the one array, and it keeps whatever the previous call left there.
 //     Nothing in it has to start at zero: each call overwrites exactly the part it later reads (the
 //     padding columns k..roundup(k,8) are outside the tensor maps and are never read), and the status
@@ -54,6 +59,21 @@ struct DeviceSlot {
 };
 DeviceSlot g_slots[kMaxDevices];
 std::mutex g_slots_mutex;
+thread_local char t_last_error[512] = {0};
+
+// puts the caller's current device back on every way out
+struct DeviceGuard {
+    int prev = -1;
+    DeviceGuard() {
+        if (cudaGetDevice(&prev) != cudaSuccess) {
+            prev = -1;
+            cudaGetLastError();
+        }
+    }
+    ~DeviceGuard() {
+        if (prev >= 0) cudaSetDevice(prev);
+    }
+};
 
 // once per device, with that device current
 int setup_device(int device, DeviceSlot **out, char *err, size_t errlen) {
@@ -99,24 +119,22 @@ SWC_EXPORT int swcb200_matrixMatrixMul_f_noalloc(int device, void *cuda_stream, 
     if (!a || !b || !c) return SWCB200_ERR_BAD_ARG;
     const size_t kp = ((size_t)k + 7) & ~(size_t)7;
     const size_t a_bytes = ((size_t)m * kp * 2 + 255) & ~(size_t)255, b_bytes = (size_t)n * kp * 2;
+    t_last_error[0] = 0;
     if (a_bytes + b_bytes > kScratchBytes) {
-        fprintf(stderr,
-                "swcb200_matrixMatrixMul_f_noalloc: %d x %d x %d needs %zu bytes of bf16 operand copies; the fixed "
-                "scratch holds %zu (limit: 2*roundup(k,8)*(m+n) <= 40 MiB)\n",
-                m, n, k, a_bytes + b_bytes, kScratchBytes);
+        snprintf(t_last_error, sizeof(t_last_error),
+                 "%d x %d x %d needs %zu bytes of bf16 operand copies; the fixed scratch holds %zu (limit: "
+                 "2*roundup(k,8)*(m+n) <= 40 MiB)", m, n, k, a_bytes + b_bytes, kScratchBytes);
         return SWCB200_ERR_TOO_LARGE;
     }
+    DeviceGuard guard;
     if (cudaSetDevice(device) != cudaSuccess) {
+        snprintf(t_last_error, sizeof(t_last_error), "cudaSetDevice(%d) failed", device);
         cudaGetLastError();
         return SWCB200_ERR_CUDA;
     }
-    char err[256] = {0};
     DeviceSlot *slot = nullptr;
-    int rc = setup_device(device, &slot, err, sizeof(err));
-    if (rc) {
-        if (err[0]) fprintf(stderr, "swcb200_matrixMatrixMul_f_noalloc: %s\n", err);
-        return rc;
-    }
+    int rc = setup_device(device, &slot, t_last_error, sizeof(t_last_error));
+    if (rc) return rc;
     // A context object on the host stack: plain data describing where to launch, owning nothing.
     swcb200_ctx ctx;
     ctx.device = device;
@@ -127,7 +145,7 @@ SWC_EXPORT int swcb200_matrixMatrixMul_f_noalloc(int device, void *cuda_stream, 
     ctx.dev_status = slot->status;
     cudaError_t e = cudaMemsetAsync(slot->status, 0, sizeof(int), ctx.stream);
     if (e != cudaSuccess) {
-        fprintf(stderr, "swcb200_matrixMatrixMul_f_noalloc: clearing the status word: %s\n", cudaGetErrorString(e));
+        snprintf(t_last_error, sizeof(t_last_error), "clearing the status word: %s", cudaGetErrorString(e));
         return SWCB200_ERR_CUDA;
     }
     void *a16 = slot->scratch, *b16 = (unsigned char *)slot->scratch + a_bytes;
@@ -135,15 +153,18 @@ SWC_EXPORT int swcb200_matrixMatrixMul_f_noalloc(int device, void *cuda_stream, 
     if (!rc) rc = swc_pack_weight_padded(&ctx, b, k, n, ldb, b16, (int)kp);
     if (!rc) rc = swc_fc_tc(&ctx, m, n, k, a16, nullptr, (int)kp, b16, (int)kp, nullptr, SWCB200_ACT_NONE, c, nullptr, SWCB200_F32, ldc);
     if (rc) {
-        fprintf(stderr, "swcb200_matrixMatrixMul_f_noalloc: %s\n", ctx.last_error);
+        snprintf(t_last_error, sizeof(t_last_error), "%s", ctx.last_error);
         return rc;
     }
     e = cudaStreamSynchronize(ctx.stream);
     int code = 0;
     if (e == cudaSuccess) e = cudaMemcpy(&code, slot->status, sizeof(int), cudaMemcpyDeviceToHost);
     if (e != cudaSuccess) {
-        fprintf(stderr, "swcb200_matrixMatrixMul_f_noalloc: %s\n", cudaGetErrorString(e));
+        snprintf(t_last_error, sizeof(t_last_error), "%s", cudaGetErrorString(e));
         return SWCB200_ERR_CUDA;
     }
+    if (code != 0) snprintf(t_last_error, sizeof(t_last_error), "a device-side wait ran out (code %d)", code);
     return code == 0 ? SWCB200_OK : SWCB200_ERR_TIMEOUT;
 }
+
+SWC_EXPORT const char *swcb200_matrixMatrixMul_f_noalloc_last_error(void) { return t_last_error; }

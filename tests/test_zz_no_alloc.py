@@ -23,10 +23,10 @@ from swcompiler_b200 import _lib as L
 pytestmark = pytest.mark.gpu
 
 
-def _noalloc(m, n, k, a, b, c):
+def _noalloc(m, n, k, a, b, c, device=0):
     lib = L.lib()
-    stream = torch.cuda.current_stream().cuda_stream
-    return lib.swcb200_matrixMatrixMul_f_noalloc(C.c_int(0), C.c_void_p(stream), C.c_int(m), C.c_int(n), C.c_int(k),
+    stream = torch.cuda.current_stream(device).cuda_stream
+    return lib.swcb200_matrixMatrixMul_f_noalloc(C.c_int(device), C.c_void_p(stream), C.c_int(m), C.c_int(n), C.c_int(k),
                                                  C.c_void_p(a.data_ptr()), C.c_int(k), C.c_void_p(b.data_ptr()),
                                                  C.c_int(n), C.c_void_p(c.data_ptr()), C.c_int(n))
 
@@ -60,4 +60,25 @@ def test_noalloc_refuses_what_does_not_fit():
     # 2 * 8192 * (4096 + 4096) bytes = 128 MiB of operand copies: beyond the 40 MiB array; nothing is launched
     rc = _noalloc(4096, 4096, 8192, a, a, a)
     assert rc == L.ERR_TOO_LARGE
+    lib = L.lib()
+    lib.swcb200_matrixMatrixMul_f_noalloc_last_error.restype = C.c_char_p
+    assert b"40 MiB" in lib.swcb200_matrixMatrixMul_f_noalloc_last_error()    # said through the accessor, not printed
     assert _noalloc(4, 4, 0, a, a, a) == L.ERR_BAD_ARG
+
+
+def test_noalloc_on_another_device_leaves_the_current_device_alone():
+    """A call for the last GPU of the box made while GPU 0 is the thread's current device: same result as on GPU 0,
+    and GPU 0 is still current afterwards.  (On a one-GPU box this is the same device and only the second half holds.)"""
+    last = torch.cuda.device_count() - 1
+    torch.cuda.set_device(0)
+    g = torch.Generator(device="cuda:0").manual_seed(5)
+    a0 = torch.randn((130, 264), generator=g, device="cuda:0")
+    b0 = torch.randn((264, 96), generator=g, device="cuda:0") / 16
+    want = torch.empty((130, 96), device="cuda:0")
+    assert _noalloc(130, 96, 264, a0, b0, want, device=0) == L.OK
+    a1, b1 = a0.to(f"cuda:{last}"), b0.to(f"cuda:{last}")
+    got = torch.full((130, 96), float("nan"), device=f"cuda:{last}")
+    torch.cuda.synchronize(last)
+    assert _noalloc(130, 96, 264, a1, b1, got, device=last) == L.OK
+    assert torch.cuda.current_device() == 0
+    assert torch.equal(got.cpu(), want.cpu())
