@@ -66,6 +66,15 @@ int swcb200_init_on_stream(int device, int precision, void *cuda_stream, swcb200
 int swcb200_destroy(swcb200_ctx *ctx);
 int swcb200_sync(swcb200_ctx *ctx);
 int swcb200_set_precision(swcb200_ctx *ctx, int precision);
+/* Every wait inside the tensor-core kernels (on an operand tile, a pipeline stage, an accumulator) is
+ * bounded: when it runs out the kernel unwinds normally and the next swcb200_sync returns
+ * SWCB200_ERR_TIMEOUT; the context stays usable.  The limit is counted in SM clock cycles, 4e9 by
+ * default (2 to 3 seconds).  The reference has no counterpart (its kernels cannot wait). */
+int swcb200_set_wait_limit(swcb200_ctx *ctx, long long cycles);
+/* Self-test of that path: launches one thread that waits, with the same bounded wait, on a barrier
+ * nothing arrives at.  After the context's limit the kernel returns and swcb200_sync reports
+ * SWCB200_ERR_TIMEOUT.  Set a short limit first (a million cycles is half a millisecond). */
+int swcb200_selftest_wait_timeout(swcb200_ctx *ctx);
 void *swcb200_stream(swcb200_ctx *ctx);
 const char *swcb200_status_string(int status);
 const char *swcb200_last_error(swcb200_ctx *ctx);
@@ -227,6 +236,15 @@ int swcb200_comm_unique_id(void *id_out /* SWCB200_UNIQUE_ID_BYTES */);
 int swcb200_comm_init(swcb200_ctx *ctx, const void *unique_id, int nranks, int rank);
 int swcb200_comm_destroy(swcb200_ctx *ctx);
 int swcb200_comm_rank(swcb200_ctx *ctx, int *rank, int *nranks);
+/* Bounded wait for the collectives queued on the context's stream.  Polls the stream and the communicator's
+ * asynchronous error state; returns SWCB200_OK once the stream is idle, SWCB200_ERR_NCCL if NCCL reports an
+ * error, SWCB200_ERR_TIMEOUT after timeout_ms of wall-clock time.  In both failure cases the communicator has
+ * been aborted and removed from the context (a peer has died or hangs): the process does not hang with it.
+ * The reference ignores MPI's return codes and has nothing of the kind. */
+int swcb200_comm_watch(swcb200_ctx *ctx, int timeout_ms);
+/* The same polling loop run against the NCCL library at `libnccl_path` and a stream that never becomes idle;
+ * needs no GPU.  For testing the loop with a stand-in library. */
+int swcb200_comm_watch_selftest(const char *libnccl_path, int timeout_ms);
 /* Scatter node (ParallelCodegen.cpp:457-575): axis -1 = MPI_Bcast; axis >= 0 = each rank gets
  * its slice of `src` (read on root only) packed contiguously into `dst`. */
 int swcb200_scatter(swcb200_ctx *ctx, const void *src, void *dst, const size_t *dims, int ndim,

@@ -14,6 +14,7 @@
 // staging block (the context's scratch) packed and unpacked with strided device copies.
 #include <cuda.h>
 #include <dlfcn.h>
+#include <time.h>
 
 #include <mutex>
 
@@ -102,6 +103,24 @@ namespace {
         if (r__ != ncclSuccess)                                                                          \
             return swc_fail((ctx), SWCB200_ERR_NCCL, "%s: %s", #call, g_nccl.GetErrorString(r__));       \
     } while (0)
+
+// An NCCL group that is closed on every way out of the scope: a Send or Recv that fails returns from the
+// middle of the group, and a group left open would swallow every later collective of the thread.
+struct NcclGroup {
+    bool open = false;
+    int start() {
+        int r = g_nccl.GroupStart();
+        open = r == ncclSuccess;
+        return r;
+    }
+    int end() {
+        open = false;
+        return g_nccl.GroupEnd();
+    }
+    ~NcclGroup() {
+        if (open) g_nccl.GroupEnd();
+    }
+};
 
 int nccl_type(int dtype, size_t *elem) {
     switch (dtype) {
@@ -197,6 +216,95 @@ SWC_EXPORT int swcb200_comm_destroy(swcb200_ctx *ctx) {
     return r == ncclSuccess ? SWCB200_OK : SWCB200_ERR_NCCL;
 }
 
+// ---------------------------------------------------------------------------------------------------
+// Failure detection on the host.  A collective whose peer has died never completes, and a host thread that
+// synchronises its stream behind it waits for ever.  swcb200_comm_watch is the bounded form of that
+// synchronisation: it polls the stream and the communicator's asynchronous error state until the stream is
+// idle (OK), NCCL reports an error (ERR_NCCL) or the wall-clock limit has passed (ERR_TIMEOUT); in the two
+// failure cases the communicator is aborted, which takes its kernels off the GPU, and dropped, so that the
+// process can carry on (or exit) instead of hanging.  The reference has no counterpart: its MPI return
+// codes are ignored (src/codegen/ParallelCodegen.cpp:457-896).
+namespace {
+
+struct WatchFns {
+    int (*stream_idle)(void *stream);                 // 1 idle, 0 busy, < 0 error
+    int (*async_error)(void *comm, int *state);       // NCCL's convention: returns ncclSuccess, state = ncclSuccess / ncclInProgress / error
+    int (*abort)(void *comm);
+};
+
+int watch_loop(const WatchFns &f, void *comm, void *stream, int timeout_ms, char *err, size_t errlen) {
+    timespec t0;
+    clock_gettime(CLOCK_MONOTONIC, &t0);
+    for (unsigned spin = 0;; spin++) {
+        const int idle = f.stream_idle(stream);
+        if (idle > 0) return SWCB200_OK;
+        if (idle < 0) {
+            snprintf(err, errlen, "comm_watch: the stream reported an error");
+            return SWCB200_ERR_CUDA;
+        }
+        int state = ncclSuccess;
+        if (f.async_error(comm, &state) != ncclSuccess || (state != ncclSuccess && state != ncclInProgress)) {
+            f.abort(comm);
+            snprintf(err, errlen, "comm_watch: the communicator reported an asynchronous error (state %d); aborted", state);
+            return SWCB200_ERR_NCCL;
+        }
+        timespec t1;
+        clock_gettime(CLOCK_MONOTONIC, &t1);
+        const long long ms = (t1.tv_sec - t0.tv_sec) * 1000ll + (t1.tv_nsec - t0.tv_nsec) / 1000000ll;
+        if (ms > timeout_ms) {
+            f.abort(comm);
+            snprintf(err, errlen, "comm_watch: collectives still pending after %d ms; communicator aborted", timeout_ms);
+            return SWCB200_ERR_TIMEOUT;
+        }
+        if (spin > 64) {  // a short sleep once the quick polls have not sufficed
+            timespec nap = {0, 200000};
+            nanosleep(&nap, nullptr);
+        }
+    }
+}
+
+int real_stream_idle(void *stream) {
+    cudaError_t e = cudaStreamQuery((cudaStream_t)stream);
+    if (e == cudaSuccess) return 1;
+    if (e == cudaErrorNotReady) return 0;
+    cudaGetLastError();
+    return -1;
+}
+int real_async_error(void *comm, int *state) { return g_nccl.CommGetAsyncError((ncclComm_t)comm, state); }
+int real_abort(void *comm) { return g_nccl.CommAbort((ncclComm_t)comm); }
+
+}  // namespace
+
+SWC_EXPORT int swcb200_comm_watch(swcb200_ctx *ctx, int timeout_ms) {
+    SWC_CTX(ctx);
+    SWC_REQUIRE(ctx, ctx->comm != nullptr, SWCB200_ERR_NCCL, "comm_watch: no communicator");
+    SWC_REQUIRE(ctx, timeout_ms > 0, SWCB200_ERR_BAD_ARG, "comm_watch: the limit must be positive");
+    const WatchFns f = {real_stream_idle, real_async_error, real_abort};
+    int rc = watch_loop(f, ctx->comm->comm, ctx->stream, timeout_ms, ctx->last_error, sizeof(ctx->last_error));
+    if (rc == SWCB200_ERR_NCCL || rc == SWCB200_ERR_TIMEOUT) {
+        // the communicator is gone (ncclCommAbort frees it); peer mappings of the row gather go with it
+        swcb200_gather_rows_release(ctx);
+        delete ctx->comm;
+        ctx->comm = nullptr;
+    }
+    return rc;
+}
+
+// The watch loop against an NCCL library given by path and a stream that never becomes idle, without any GPU:
+// for a stand-in library whose asynchronous error state stays "in progress" (expected: SWCB200_ERR_TIMEOUT after
+// timeout_ms, one abort) or turns into an error (expected: SWCB200_ERR_NCCL, one abort).
+SWC_EXPORT int swcb200_comm_watch_selftest(const char *libnccl_path, int timeout_ms) {
+    int rc = load_nccl(libnccl_path);
+    if (rc) return rc;
+    ncclUniqueId id;
+    if (g_nccl.GetUniqueId(&id) != ncclSuccess) return SWCB200_ERR_NCCL;
+    ncclComm_t comm = nullptr;
+    if (g_nccl.CommInitRank(&comm, 1, id, 0) != ncclSuccess) return SWCB200_ERR_NCCL;
+    const WatchFns f = {[](void *) { return 0; }, real_async_error, real_abort};
+    char err[256];
+    return watch_loop(f, comm, nullptr, timeout_ms, err, sizeof(err));
+}
+
 SWC_EXPORT int swcb200_comm_rank(swcb200_ctx *ctx, int *rank, int *nranks) {
     if (!ctx || !ctx->comm) return SWCB200_ERR_BAD_ARG;
     if (rank) *rank = ctx->comm->rank;
@@ -233,7 +341,8 @@ SWC_EXPORT int swcb200_scatter(swcb200_ctx *ctx, const void *src, void *dst, con
         }
         send_base = (const uint8_t *)stage;
     }
-    SWC_NCCL(ctx, g_nccl.GroupStart());
+    NcclGroup group;
+    SWC_NCCL(ctx, group.start());
     if (c->rank == root) {
         for (int r = 0; r < c->nranks; r++)
             if (r != root)
@@ -241,7 +350,7 @@ SWC_EXPORT int swcb200_scatter(swcb200_ctx *ctx, const void *src, void *dst, con
     } else {
         SWC_NCCL(ctx, g_nccl.Recv(dst, shard, t.type, root, c->comm, ctx->stream));
     }
-    SWC_NCCL(ctx, g_nccl.GroupEnd());
+    SWC_NCCL(ctx, group.end());
     if (c->rank == root)  // root's own shard: a local copy
         return copy_window(ctx, dst, t.blk, (const uint8_t *)src + (size_t)root * t.blk * t.elem, t.inner, t.blk, t.outer,
                            t.elem);
@@ -272,7 +381,8 @@ SWC_EXPORT int swcb200_gather(swcb200_ctx *ctx, const void *src, void *dst, cons
         if (rc) return rc;
         recv_base = (uint8_t *)stage;
     }
-    SWC_NCCL(ctx, g_nccl.GroupStart());
+    NcclGroup group;
+    SWC_NCCL(ctx, group.start());
     if (c->rank == root) {
         for (int r = 0; r < c->nranks; r++)
             if (r != root)
@@ -280,7 +390,7 @@ SWC_EXPORT int swcb200_gather(swcb200_ctx *ctx, const void *src, void *dst, cons
     } else {
         SWC_NCCL(ctx, g_nccl.Send(src, shard, t.type, root, c->comm, ctx->stream));
     }
-    SWC_NCCL(ctx, g_nccl.GroupEnd());
+    SWC_NCCL(ctx, group.end());
     if (c->rank == root) {
         rc = copy_window(ctx, (uint8_t *)dst + (size_t)root * t.blk * t.elem, t.inner, src, t.blk, t.blk, t.outer, t.elem);
         if (rc) return rc;
@@ -505,12 +615,13 @@ int transform_nd(swcb200_ctx *ctx, const void *src, void *dst, const size_t *dim
         rc = copy_window(ctx, st_send + q * box * elem, sblk, s + q * sblk * elem, si, sblk, so, elem);
         if (rc) return rc;
     }
-    SWC_NCCL(ctx, g_nccl.GroupStart());
+    NcclGroup group;
+    SWC_NCCL(ctx, group.start());
     for (size_t q = 0; q < p; q++) {
         SWC_NCCL(ctx, g_nccl.Send(st_send + q * box * elem, box, type, (int)q, c->comm, ctx->stream));
         SWC_NCCL(ctx, g_nccl.Recv(st_recv + q * box * elem, box, type, (int)q, c->comm, ctx->stream));
     }
-    SWC_NCCL(ctx, g_nccl.GroupEnd());
+    SWC_NCCL(ctx, group.end());
     for (size_t q = 0; q < p; q++) {
         rc = copy_window(ctx, d + q * rblk * elem, ri, st_recv + q * box * elem, rblk, rblk, ro, elem);
         if (rc) return rc;
@@ -596,22 +707,24 @@ SWC_EXPORT int swcb200_transform(swcb200_ctx *ctx, const void *src, void *dst, c
             rc = copy_window(ctx, st + q * blk * elem, Cp, s + q * Cp * elem, C, Cp, Rp, elem);
             if (rc) return rc;
         }
-        SWC_NCCL(ctx, g_nccl.GroupStart());
+        NcclGroup group;
+        SWC_NCCL(ctx, group.start());
         for (size_t q = 0; q < p; q++) {
             SWC_NCCL(ctx, g_nccl.Send(st + q * blk * elem, blk, type, (int)q, c->comm, ctx->stream));
             SWC_NCCL(ctx, g_nccl.Recv(d + q * blk * elem, blk, type, (int)q, c->comm, ctx->stream));
         }
-        SWC_NCCL(ctx, g_nccl.GroupEnd());
+        SWC_NCCL(ctx, group.end());
         return SWCB200_OK;
     }
     // pre 1 -> post 0: local [R, C/p]: block for rank q is rows [q*Rp, (q+1)*Rp), contiguous; the block received
     // from q becomes columns [q*Cp, (q+1)*Cp) of the result [R/p, C] -> unpack
-    SWC_NCCL(ctx, g_nccl.GroupStart());
+    NcclGroup group;
+    SWC_NCCL(ctx, group.start());
     for (size_t q = 0; q < p; q++) {
         SWC_NCCL(ctx, g_nccl.Send(s + q * blk * elem, blk, type, (int)q, c->comm, ctx->stream));
         SWC_NCCL(ctx, g_nccl.Recv(st + q * blk * elem, blk, type, (int)q, c->comm, ctx->stream));
     }
-    SWC_NCCL(ctx, g_nccl.GroupEnd());
+    SWC_NCCL(ctx, group.end());
     for (size_t q = 0; q < p; q++) {
         rc = copy_window(ctx, d + q * Cp * elem, C, st + q * blk * elem, Cp, Cp, Rp, elem);
         if (rc) return rc;

@@ -24,8 +24,9 @@ struct swcb200_ctx {
     void *scratch = nullptr;
     size_t scratch_bytes = 0;
     swcb200_comm *comm = nullptr;
-    // one word of device memory that kernels with bounded waits write a code into when a wait runs
-    // out; read (and cleared) by swcb200_sync
+    // the status block in device memory, {int code; int pad; long long wait_limit_cycles}: kernels with
+    // bounded waits read the limit from it and write a code into it when a wait runs out; the code is
+    // read (and cleared) by swcb200_sync
     int *dev_status = nullptr;
     bool conv_attr_set = false;
 };

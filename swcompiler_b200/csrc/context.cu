@@ -1,7 +1,7 @@
 // Context life-cycle and status strings.
 #include <stdarg.h>
 
-#include "common.cuh"
+#include "tc_common.cuh"
 
 int swc_fail(swcb200_ctx *ctx, int status, const char *fmt, ...) {
     if (ctx) {
@@ -68,8 +68,9 @@ static int init_common(int device, int precision, void *stream, bool own, swcb20
     } else {
         ctx->stream = (cudaStream_t)stream;
     }
-    if (cudaMalloc(&ctx->dev_status, sizeof(int)) != cudaSuccess ||
-        cudaMemset(ctx->dev_status, 0, sizeof(int)) != cudaSuccess) {
+    const long long block[2] = {0, 4000000000ll};  // code 0; the default limit of the device-side waits, in SM cycles
+    if (cudaMalloc(&ctx->dev_status, sizeof(block)) != cudaSuccess ||
+        cudaMemcpy(ctx->dev_status, block, sizeof(block), cudaMemcpyHostToDevice) != cudaSuccess) {
         if (ctx->own_stream) cudaStreamDestroy(ctx->stream);
         delete ctx;
         return SWCB200_ERR_CUDA;
@@ -113,6 +114,32 @@ SWC_EXPORT int swcb200_sync(swcb200_ctx *ctx) {
                         (code >= 1 && code <= 5) ? where[code] : "?", code);
     }
     return SWCB200_OK;
+}
+
+SWC_EXPORT int swcb200_set_wait_limit(swcb200_ctx *ctx, long long cycles) {
+    SWC_CTX(ctx);
+    SWC_REQUIRE(ctx, cycles > 0, SWCB200_ERR_BAD_ARG, "set_wait_limit: the limit must be positive");
+    // ordered with the kernels of the stream: launches made before this call keep the old limit
+    SWC_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
+    SWC_CUDA(ctx, cudaMemcpy((long long *)ctx->dev_status + 1, &cycles, sizeof(cycles), cudaMemcpyHostToDevice));
+    return SWCB200_OK;
+}
+
+namespace {
+// One thread waits, with the library's bounded wait, on a barrier nobody will ever arrive at: the wait runs out
+// after the context's limit, records its code and the kernel returns normally.
+__global__ void selftest_wait_kernel(int *status) {
+    __shared__ uint64_t bar;
+    tc::mbar_init(&bar, 1);
+    tc::fence_barrier_init();
+    tc::mbar_wait(&bar, 0, status, tc::kWaitFull);
+}
+}  // namespace
+
+SWC_EXPORT int swcb200_selftest_wait_timeout(swcb200_ctx *ctx) {
+    SWC_CTX(ctx);
+    selftest_wait_kernel<<<1, 1, 0, ctx->stream>>>(ctx->dev_status);
+    return swc_check_launch(ctx, "selftest_wait_timeout");
 }
 
 SWC_EXPORT int swcb200_set_precision(swcb200_ctx *ctx, int precision) {

@@ -49,7 +49,8 @@ constexpr int kMaxDevices = 64;
 // The scratch itself.  In host code these names are only handles for the runtime; the addresses the
 // kernels use are obtained with cudaGetSymbolAddress below.
 static __device__ __align__(256) unsigned char g_noalloc_scratch[kScratchBytes];
-static __device__ __align__(16) int g_noalloc_status;
+// the status block of the bounded waits: {code, pad} and the wait limit in SM cycles (see tc_common.cuh)
+static __device__ __align__(16) long long g_noalloc_status[2] = {0, 4000000000ll};
 
 struct DeviceSlot {
     bool ready = false;

@@ -63,16 +63,18 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t *bar, uint32_t parity) {
 // Bounded wait: false (and `code` stored to *status) once the limit has passed.  The limit is counted in
 // SM clock cycles (clock64 is a cheap per-SM counter; the nanosecond %globaltimer is served by a remote
 // unit and costs on the order of a microsecond per read, which would tax every wait that is not
-// satisfied at the first probe).  4e9 cycles is 2 s at 2 GHz and 3 s at the 1.3 GHz a power-capped GEMM
-// settles at.
+// satisfied at the first probe).  `status` points at the context's status block {int code; int pad;
+// long long limit_cycles}: the limit is read from there only on the slow path.  The default, 4e9 cycles,
+// is 2 s at 2 GHz and 3 s at the 1.3 GHz a power-capped GEMM settles at (swcb200_set_wait_limit changes it).
 constexpr long long kWaitLimitCycles = 4000000000ll;
 __device__ __forceinline__ bool mbar_wait(uint64_t *bar, uint32_t parity, int *status, int code) {
     if (mbar_try_wait(bar, parity)) return true;
     const long long t0 = clock64();
+    const long long limit = *reinterpret_cast<const volatile long long *>(status + 2);
     uint32_t spins = 0;
     while (!mbar_try_wait(bar, parity)) {
         if ((++spins & 0x3f) == 0) {
-            if (clock64() - t0 > kWaitLimitCycles) {
+            if (clock64() - t0 > limit) {
                 atomicCAS(status, 0, code);
                 return false;
             }

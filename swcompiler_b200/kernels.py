@@ -80,6 +80,14 @@ class Backend:
     def sync(self):
         self._call("sync")
 
+    def set_wait_limit(self, cycles: int):
+        """Limit, in SM clock cycles, of every wait inside the tensor-core kernels launched through this context."""
+        self._call("set_wait_limit", C.c_longlong(cycles))
+
+    def selftest_wait_timeout(self):
+        """Launches a kernel whose bounded wait can only run out; `sync()` then raises with status ERR_TIMEOUT."""
+        self._call("selftest_wait_timeout")
+
     def set_precision(self, precision: int):
         self._call("set_precision", C.c_int(precision))
         self.precision = precision
