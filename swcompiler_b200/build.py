@@ -1,10 +1,6 @@
 """Builds libswc_b200.so (the C-ABI kernel library) in-tree with nvcc for sm_100a.
 
-    python -m swcompiler_b200.build [--force] [--conv-timing]
-
---conv-timing compiles the convolution kernel with per-role cycle counters (-DSWC_CONV_TIMING) and exports
-swcb200_debug_conv_timing to read them (`python -m swcompiler_b200.opbench --conv-roles`); a measuring build,
-not the one to ship: rebuild without the flag afterwards.
+    python -m swcompiler_b200.build [--force] [-v]
 
 nvcc cross-compiles without a GPU.  Objects are compiled in parallel, one per .cu file, and
 re-used while they are newer than every source and header.
@@ -42,7 +38,7 @@ def _newest_header() -> float:
     return max(os.path.getmtime(h) for h in hs)
 
 
-def build_library(force: bool = False, verbose: bool = False, conv_timing: bool = False) -> str:
+def build_library(force: bool = False, verbose: bool = False) -> str:
     nvcc = _nvcc()
     os.makedirs(OBJ, exist_ok=True)
     srcs = sorted(glob.glob(os.path.join(CSRC, "*.cu")))
@@ -52,16 +48,8 @@ def build_library(force: bool = False, verbose: bool = False, conv_timing: bool 
     for s in srcs:
         o = os.path.join(OBJ, os.path.basename(s)[:-3] + ".o")
         objs.append(o)
-        timing = os.path.basename(s) == "conv_tcgen05.cu" and (conv_timing or os.path.exists(o + ".timing"))
-        if force or timing or not os.path.exists(o) or os.path.getmtime(o) < max(os.path.getmtime(s), hdr):
-            jobs.append([nvcc, *NVCC_FLAGS, "-c", s, "-o", o] + (["-Xptxas", "-v"] if verbose else []) +
-                        (["-DSWC_CONV_TIMING"] if timing and conv_timing else []))
-        if timing:  # a marker beside the object: the next plain build recompiles it without the counters
-            marker = o + ".timing"
-            if conv_timing:
-                open(marker, "w").close()
-            elif os.path.exists(marker):
-                os.remove(marker)
+        if force or not os.path.exists(o) or os.path.getmtime(o) < max(os.path.getmtime(s), hdr):
+            jobs.append([nvcc, *NVCC_FLAGS, "-c", s, "-o", o] + (["-Xptxas", "-v"] if verbose else []))
 
     def run(cmd):
         r = subprocess.run(cmd, capture_output=True, text=True)
@@ -79,4 +67,4 @@ def build_library(force: bool = False, verbose: bool = False, conv_timing: bool 
 
 
 if __name__ == "__main__":
-    print(build_library(force="--force" in sys.argv, verbose="-v" in sys.argv, conv_timing="--conv-timing" in sys.argv))
+    print(build_library(force="--force" in sys.argv, verbose="-v" in sys.argv))

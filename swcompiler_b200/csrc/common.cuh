@@ -28,7 +28,6 @@ struct swcb200_ctx {
     // bounded waits read the limit from it and write a code into it when a wait runs out; the code is
     // read (and cleared) by swcb200_sync
     int *dev_status = nullptr;
-    bool conv_attr_set = false;
 };
 
 int swc_fail(swcb200_ctx *ctx, int status, const char *fmt, ...);

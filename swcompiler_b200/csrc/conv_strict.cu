@@ -62,6 +62,47 @@ __global__ void __launch_bounds__(256) conv_strict_kernel(float *__restrict__ ou
     if (pix_ok && co_ok) out[pix * g.OC + co] = acc;
 }
 
+// The same arithmetic with the CTA's whole filter slice (32 output channels x kh*kw*C) resident in shared memory:
+// staged once per CTA, then no barrier inside the tap loops, and a CTA walks many groups of 8 pixels.  For the
+// filters that fit (kh*kw*C <= kMaxResidentK); the kernel above takes the rest.
+constexpr int kMaxResidentK = 1536;  // 1536 x 33 floats = 198 KiB
+
+__global__ void __launch_bounds__(256) conv_strict_resident_kernel(float *__restrict__ out, const float *__restrict__ in,
+                                                                   const float *__restrict__ filt,
+                                                                   const float *__restrict__ bias, ConvGeom g) {
+    extern __shared__ float fr[];  // fr[q][co], pitch kCo + 1, q = (kx * kw + ky) * C + ci
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int K = g.kh * g.kw * g.C;
+    const int co0 = blockIdx.y * kCo, co = co0 + lane;
+    for (int idx = threadIdx.x; idx < K * kCo; idx += blockDim.x) {
+        const int r = idx / K, q = idx - r * K;  // consecutive threads read consecutive words of one filter row
+        fr[q * (kCo + 1) + r] = (co0 + r < g.OC) ? filt[(size_t)(co0 + r) * K + q] : 0.f;
+    }
+    __syncthreads();
+    const bool co_ok = co < g.OC;
+    const float b = co_ok ? bias[co] : 0.f;
+    const size_t npix = (size_t)g.N * g.OH * g.OW;
+    for (size_t pix = (size_t)blockIdx.x * kPix + warp; pix < npix; pix += (size_t)gridDim.x * kPix) {
+        size_t p = pix;
+        const int ow = (int)(p % g.OW);
+        p /= g.OW;
+        const int oh = (int)(p % g.OH), n = (int)(p / g.OH);
+        float acc = b;
+        for (int kx = 0; kx < g.kh; kx++) {
+            const int ih = oh * g.sh - g.pt + kx;
+            if (ih < 0 || ih >= g.H) continue;  // uniform within the warp: one pixel per warp
+            for (int ky = 0; ky < g.kw; ky++) {
+                const int iw = ow * g.sw - g.pl + ky;
+                if (iw < 0 || iw >= g.W) continue;
+                const float *ip = in + (((size_t)n * g.H + ih) * g.W + iw) * g.C;
+                const float *fq = fr + (size_t)((kx * g.kw + ky) * g.C) * (kCo + 1) + lane;
+                for (int ci = 0; ci < g.C; ci++) acc = __fadd_rn(acc, __fmul_rn(__ldg(ip + ci), fq[ci * (kCo + 1)]));
+            }
+        }
+        if (co_ok) out[pix * g.OC + co] = acc;
+    }
+}
+
 }  // namespace
 
 int swc_conv_tc_from_f32(swcb200_ctx *ctx, float *output, const float *input, const float *filter, const float *bias,
@@ -96,6 +137,23 @@ SWC_EXPORT int swcb200_conv2d_f(swcb200_ctx *ctx, float *output, const float *in
     }
     dim3 grid((unsigned)((npix + kPix - 1) / kPix), (g.OC + kCo - 1) / kCo);
     SWC_REQUIRE(ctx, grid.y <= 65535, SWCB200_ERR_TOO_LARGE, "conv2d_f: too many output channels");
+    const long long K = (long long)g.kh * g.kw * g.C;
+    if (K <= kMaxResidentK) {
+        static bool attr_set[64] = {false};  // per device: the opt-in to large dynamic shared memory
+        if (!attr_set[ctx->device & 63]) {
+            SWC_CUDA(ctx, cudaFuncSetAttribute(conv_strict_resident_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                               kMaxResidentK * (kCo + 1) * (int)sizeof(float)));
+            attr_set[ctx->device & 63] = true;
+        }
+        const size_t smem = (size_t)K * (kCo + 1) * sizeof(float);
+        // as many CTAs as keep every SM busy for this filter's shared-memory footprint; each walks its share of the pixels
+        const unsigned per_sm = (unsigned)(smem > 100 * 1024 ? 1 : (smem > 48 * 1024 ? 2 : 4));
+        unsigned cap = (unsigned)ctx->sm_count * per_sm / grid.y;
+        if (cap < 1) cap = 1;
+        dim3 gr(grid.x < cap ? grid.x : cap, grid.y);
+        conv_strict_resident_kernel<<<gr, 256, smem, ctx->stream>>>(output, input, filter, bias, g);
+        return swc_check_launch(ctx, "conv2d_f(strict)");
+    }
     conv_strict_kernel<<<grid, 256, 0, ctx->stream>>>(output, input, filter, bias, g);
     return swc_check_launch(ctx, "conv2d_f(strict)");
 }

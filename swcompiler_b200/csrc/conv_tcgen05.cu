@@ -36,6 +36,11 @@
 // branch issues tcgen05.mma at 75 cycles apiece on this part, the uniform form at the 48 cycles the
 // shared-memory reads allow.
 //
+// A CTA-pair form (cta_group::2, M = 256, half the filter per CTA: 5 KiB of operand reads per MMA instead of 6) was
+// built and measured: correct, but a cta_group::2 MMA does not issue faster than about every 155 cycles whatever its
+// N, so at N = 64 the pair ran the layer in 91 us against 65 us for this kernel.  It pays from N = 256 up, which is
+// where the FC kernel uses it.
+//
 // Restrictions: stride 1, group 1, iC a multiple of 64, oC a multiple of 32 and <= 256, kw <= 9, filter at
 // most 96 KiB in bf16, two windows fitting beside it.  Other shapes return SWCB200_ERR_UNSUPPORTED (the
 // strict kernel takes them).
@@ -83,13 +88,6 @@ struct ConvParams {
     int out_is_f32, res_is_f32;
     int *status;
 };
-
-#ifdef SWC_CONV_TIMING
-__device__ long long g_conv_timing[16];
-#define TIMING(x) x
-#else
-#define TIMING(x)
-#endif
 
 // v[j] = acc[j] * alpha[c0+j] + beta[c0+j], coefficients read as 128-bit broadcasts
 __device__ __forceinline__ void apply_affine(const uint32_t (&acc)[32], const float *s_alpha, const float *s_beta, int c0,
@@ -233,7 +231,6 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap tmIn, const __grid_constant__
     uint32_t *tmem_holder = reinterpret_cast<uint32_t *>(res_empty + 2);
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    TIMING(const long long tk0 = clock64(); const unsigned long long tn0 = globaltimer_ns();)
     const int taps = p.kh * p.kw;
     const int ochunks = p.OC >> 6;  // 64-channel chunks of the output (staged epilogue only)
 
@@ -278,7 +275,6 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap tmIn, const __grid_constant__
     __syncthreads();
     tc_fence_after();
     const uint32_t tmem_base = *tmem_holder;
-    TIMING(if (blockIdx.x == 0 && threadIdx.x == 0) g_conv_timing[9] += clock64() - tk0;)
 
     if (warp == 0) {
         // ------------------------------------------------------------ TMA producer (warp-uniform loop, one elected lane issues)
@@ -296,10 +292,8 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap tmIn, const __grid_constant__
         TileWalk tw(blockIdx.x, gridDim.x, p.row_blocks, p.col_blocks);
         for (long long tile = blockIdx.x; tile < p.num_tiles; tile += gridDim.x, tw.advance()) {
             const int n = tw.n, oh0 = tw.rb * 2, ow0 = tw.cb * p.cw;
-            TIMING(const long long tw0 = clock64();)
             bool ok = mbar_wait(&empty[st], ph ^ 1, p.status, kWaitEmpty);
             ok = __all_sync(0xffffffffu, ok);
-            TIMING(if (blockIdx.x == 0 && lane == 0) g_conv_timing[0] += clock64() - tw0;)
             if (!ok) break;
             if (leader) {
                 mbar_expect_tx(&full[st], (uint32_t)p.stage_bytes);
@@ -376,7 +370,6 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap tmIn, const __grid_constant__
         bool ok = mbar_wait(filter_bar, 0, p.status, kWaitFull);
         ok = __all_sync(0xffffffffu, ok);
         tc_fence_after();
-        TIMING(if (blockIdx.x == 0 && lane == 0 && iw == 0) g_conv_timing[10] += clock64() - tk0;)
         uint32_t it = iw, ph = (iw / (uint32_t)p.stages) & 1;
         int st = (int)(iw % (uint32_t)p.stages);
         uint32_t buf = iw % (uint32_t)p.num_acc, aph = (iw / (uint32_t)p.num_acc) & 1;
@@ -389,12 +382,9 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap tmIn, const __grid_constant__
         auto desc = [desc_hi](uint32_t lo) { return ((uint64_t)desc_hi << 32) | lo; };
         for (long long tile = blockIdx.x + (long long)iw * gridDim.x; tile < p.num_tiles && ok;
              tile += (long long)kIssuers * gridDim.x, it += kIssuers) {
-            TIMING(const long long tm0 = clock64();)
             ok = mbar_wait(&tmem_empty[buf], aph ^ 1, p.status, kWaitTmemEmpty);
-            TIMING(const long long tm1 = clock64();)
             if (ok) ok = mbar_wait(&full[st], ph, p.status, kWaitFull);
             ok = __all_sync(0xffffffffu, ok);
-            TIMING(const long long tm2 = clock64();)
             if (!ok) break;
             tc_fence_after();
             const uint32_t d_tmem = tmem_base + buf * p.acc_stride;
@@ -422,9 +412,6 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap tmIn, const __grid_constant__
                 umma_commit(&tmem_full[buf]);  // and the accumulator is complete
             }
             __syncwarp();
-            TIMING(if (blockIdx.x == 0 && lane == 0 && iw == 0) {
-                g_conv_timing[1] += tm1 - tm0; g_conv_timing[2] += tm2 - tm1; g_conv_timing[3] += clock64() - tm2; g_conv_timing[4] += 1;
-            })
             // this warp's next tile is kIssuers further on (stages >= 2 and num_acc >= 2, so one wrap at most)
             st += kIssuers;
             if (st >= p.stages) {
@@ -437,7 +424,6 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap tmIn, const __grid_constant__
                 aph ^= 1;
             }
         }
-        TIMING(if (blockIdx.x == 0 && lane == 0 && iw == 0) g_conv_timing[11] += clock64() - tk0;)
     } else if (warp >= kFirstEpilogueWarp) {
         // ------------------------------------------------------------ epilogue: two groups of four warps, alternate tiles
         // A thread owns one output pixel (one tensor-memory lane) and walks its channels 64 at a time.  One tile's
@@ -466,7 +452,6 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap tmIn, const __grid_constant__
             const bool skip = p.out_tma ? tcol >= p.bw : !valid;  // staged tiles are clipped by the TMA store
             const size_t pix = ((size_t)n * p.OH + oh) * p.OW + ow;
             bool ok = true;
-            TIMING(const long long te0 = clock64();)
             if (p.out_tma) {
                 // the group's previous store must have finished reading the staging buffer before anyone refills it
                 if (issuer) bulk_wait_read_all();
@@ -477,7 +462,6 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap tmIn, const __grid_constant__
                 if (ok && p.res_tma) ok = mbar_wait(&res_full[group], sph, p.status, kWaitFull);
             }
             ok = __shfl_sync(0xffffffffu, ok, 0);
-            TIMING(const long long te1 = clock64();)
             if (!ok) break;
             tc_fence_after();
 
@@ -529,7 +513,6 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap tmIn, const __grid_constant__
                 if (two) pass(acc1, c0 + 32);
             }
             __syncwarp();
-            TIMING(if (blockIdx.x == 0 && lane == 0 && warp == kFirstEpilogueWarp) { g_conv_timing[5] += te1 - te0; g_conv_timing[6] += clock64() - te1; })
             if (p.res_tma && lane == 0) mbar_arrive(&res_empty[group]);
             if (p.out_tma) {
                 // the staged tile leaves by TMA once the whole group has written its part
@@ -547,9 +530,7 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap tmIn, const __grid_constant__
             }
             sph ^= 1;
         }
-        TIMING(if (blockIdx.x == 0 && warp == kFirstEpilogueWarp && lane == 0) g_conv_timing[12] += clock64() - tk0;)
         if (p.out_tma && issuer) bulk_wait_all();  // shared memory stays valid until the last store has read it
-        TIMING(if (blockIdx.x == 0 && warp == kFirstEpilogueWarp && lane == 0) g_conv_timing[13] += clock64() - tk0;)
     }
 
     __syncwarp();
@@ -559,21 +540,9 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap tmIn, const __grid_constant__
         tc_fence_after();
         tmem_dealloc(tmem_base, (uint32_t)p.tmem_cols);
     }
-    TIMING(if (blockIdx.x == 0 && threadIdx.x == 0) { g_conv_timing[7] += clock64() - tk0; g_conv_timing[8] += (long long)(globaltimer_ns() - tn0); })
 }
 
 }  // namespace
-
-#ifdef SWC_CONV_TIMING
-// working builds only: cycle counters of CTA 0 {producer wait, issuer wait accumulator, issuer wait window, issuer
-// issue, tiles, epilogue wait, epilogue work}; reading clears them
-SWC_EXPORT int swcb200_debug_conv_timing(long long *out16) {
-    long long zero[16] = {0};
-    if (cudaMemcpyFromSymbol(out16, g_conv_timing, sizeof(zero)) != cudaSuccess) return SWCB200_ERR_CUDA;
-    if (cudaMemcpyToSymbol(g_conv_timing, zero, sizeof(zero)) != cudaSuccess) return SWCB200_ERR_CUDA;
-    return SWCB200_OK;
-}
-#endif
 
 // input/filter bf16; output and residual bf16 or fp32
 int swc_conv_tc(swcb200_ctx *ctx, void *output, int out_dtype, const void *input, const void *filt, const float *bias,
@@ -679,9 +648,10 @@ int swc_conv_tc(swcb200_ctx *ctx, void *output, int out_dtype, const void *input
             if (rc) return rc;
         }
     }
-    if (!ctx->conv_attr_set) {
+    static bool attr_set[64] = {false};  // per device: the opt-in to large dynamic shared memory
+    if (!attr_set[ctx->device & 63]) {
         SWC_CUDA(ctx, cudaFuncSetAttribute(conv_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kMaxSmem));
-        ctx->conv_attr_set = true;
+        attr_set[ctx->device & 63] = true;
     }
     const size_t smem = (size_t)smem_for(p.stages, p.out_tma, p.res_tma);
     unsigned grid = (unsigned)(p.num_tiles < ctx->sm_count ? p.num_tiles : ctx->sm_count);

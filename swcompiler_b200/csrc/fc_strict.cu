@@ -73,11 +73,49 @@ __global__ void __launch_bounds__(256) fc_strict_kernel(int m, int n, int k, con
     }
 }
 
+// The same arithmetic for shapes whose 64 x 64 tiles would occupy only a few SMs (a batch of 64 rows, a 10-column
+// classifier): 8 x 32 output tiles, one output element per thread, 32-deep k slices.  The order of the additions
+// per element is unchanged (k ascending), so the result is the same bit for bit.
+constexpr int SM_ROWS = 8, SM_COLS = 32, SM_K = 32;
+
+__global__ void __launch_bounds__(256) fc_strict_small_kernel(int m, int n, int k, const float *__restrict__ a, int lda,
+                                                              const float *__restrict__ b, int ldb, float *__restrict__ c,
+                                                              int ldc) {
+    __shared__ float As[SM_ROWS][SM_K];       // As[i][p]: read as a broadcast by the 32 threads of a row
+    __shared__ float Bs[SM_K][SM_COLS + 1];   // Bs[p][j]
+    const int tx = threadIdx.x & 31, ty = threadIdx.x >> 5;
+    const int row = blockIdx.y * SM_ROWS + ty, col = blockIdx.x * SM_COLS + tx;
+    float acc = 0.f;
+    for (int k0 = 0; k0 < k; k0 += SM_K) {
+        As[ty][tx] = (row < m && k0 + tx < k) ? a[(size_t)row * lda + k0 + tx] : 0.f;
+#pragma unroll
+        for (int u = 0; u < SM_K / SM_ROWS; u++) {
+            const int kk = ty + SM_ROWS * u;
+            Bs[kk][tx] = (k0 + kk < k && col < n) ? b[(size_t)(k0 + kk) * ldb + col] : 0.f;
+        }
+        __syncthreads();
+        const int kmax = min(SM_K, k - k0);
+        if (kmax == SM_K) {
+#pragma unroll
+            for (int p = 0; p < SM_K; p++) acc = __fadd_rn(acc, __fmul_rn(As[ty][p], Bs[p][tx]));
+        } else {
+            for (int p = 0; p < kmax; p++) acc = __fadd_rn(acc, __fmul_rn(As[ty][p], Bs[p][tx]));
+        }
+        __syncthreads();
+    }
+    if (row < m && col < n) c[(size_t)row * ldc + col] = acc;
+}
+
 }  // namespace
 
 int swc_fc_strict(swcb200_ctx *ctx, int m, int n, int k, const float *a, int lda, const float *b, int ldb, float *c,
                   int ldc) {
     dim3 grid((n + BN - 1) / BN, (m + BM - 1) / BM);
+    if ((long long)grid.x * grid.y < ctx->sm_count / 2) {  // too few 64 x 64 tiles to fill the GPU: small tiles
+        dim3 gs((n + SM_COLS - 1) / SM_COLS, (m + SM_ROWS - 1) / SM_ROWS);
+        fc_strict_small_kernel<<<gs, 256, 0, ctx->stream>>>(m, n, k, a, lda, b, ldb, c, ldc);
+        return swc_check_launch(ctx, "matrixMatrixMul_f(strict)");
+    }
     SWC_REQUIRE(ctx, grid.y <= 65535, SWCB200_ERR_TOO_LARGE, "matrixMatrixMul_f: m beyond 4M rows in strict mode");
     fc_strict_kernel<<<grid, 256, 0, ctx->stream>>>(m, n, k, a, lda, b, ldb, c, ldc);
     return swc_check_launch(ctx, "matrixMatrixMul_f(strict)");

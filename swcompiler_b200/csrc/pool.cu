@@ -110,6 +110,51 @@ __global__ void __launch_bounds__(256) maxpool_bf16_kernel(const __nv_bfloat16 *
     }
 }
 
+// The common window, 2x2 stride 2 without padding and with every tap inside the image, on bf16 storage: the four
+// 16-byte loads of a thread are issued back to back (the general kernel's bounds checks keep them apart), two
+// output pixels per thread, and the comparisons then run in the reference's tap order (kx, then ky; a later
+// tap replaces only when strictly greater).  128 bytes in flight per thread.
+__global__ void __launch_bounds__(256) maxpool_bf16_2x2_kernel(const uint4 *__restrict__ in, uint4 *__restrict__ out,
+                                                               int rows, int H, int W, int OH, int OW, int cg) {
+    const int rowlen = OW * cg;           // uint4 per output row
+    const int half = (rowlen + 1) >> 1;   // a thread takes positions pos and pos + half of the row
+    const int pos = blockIdx.y * blockDim.x + threadIdx.x;
+    if (pos >= half) return;
+    const bool two = pos + half < rowlen;
+    const int p0 = pos, p1 = two ? pos + half : pos;
+    const int ow0 = p0 / cg, c0 = p0 - ow0 * cg, ow1 = p1 / cg, c1 = p1 - ow1 * cg;
+    const size_t in_row = (size_t)W * cg;
+    auto pick = [](uint32_t a, uint32_t b, uint32_t c, uint32_t d) {
+        // per 16-bit half: first tap, then strictly-greater replacements, compared as the fp32 values they stand for
+        uint32_t r = 0;
+#pragma unroll
+        for (int h = 0; h < 2; h++) {
+            const uint32_t sh = h ? 0u : 16u, mask = h ? 0xffff0000u : 0xffffu;
+            float v = __uint_as_float(h ? (a & mask) : (a << 16));
+            const float tb = __uint_as_float(h ? (b & mask) : (b << 16)), tc = __uint_as_float(h ? (c & mask) : (c << 16)),
+                        td = __uint_as_float(h ? (d & mask) : (d << 16));
+            v = tb > v ? tb : v;
+            v = tc > v ? tc : v;
+            v = td > v ? td : v;
+            r |= h ? (__float_as_uint(v) & mask) : (__float_as_uint(v) >> sh);
+        }
+        return r;
+    };
+    for (int row = blockIdx.x; row < rows; row += gridDim.x) {
+        const int n = row / OH, oh = row - n * OH;
+        const uint4 *top = in + ((size_t)n * H + 2 * oh) * in_row, *bot = top + in_row;
+        const size_t i0 = (size_t)(2 * ow0) * cg + c0, i1 = (size_t)(2 * ow1) * cg + c1;
+        const uint4 a0 = __ldcs(top + i0), b0 = __ldcs(top + i0 + cg), c0v = __ldcs(bot + i0), d0 = __ldcs(bot + i0 + cg);
+        const uint4 a1 = __ldcs(top + i1), b1 = __ldcs(top + i1 + cg), c1v = __ldcs(bot + i1), d1 = __ldcs(bot + i1 + cg);
+        uint4 *dst = out + (size_t)row * rowlen;
+        __stcs(dst + p0, make_uint4(pick(a0.x, b0.x, c0v.x, d0.x), pick(a0.y, b0.y, c0v.y, d0.y), pick(a0.z, b0.z, c0v.z, d0.z),
+                                    pick(a0.w, b0.w, c0v.w, d0.w)));
+        if (two)
+            __stcs(dst + p1, make_uint4(pick(a1.x, b1.x, c1v.x, d1.x), pick(a1.y, b1.y, c1v.y, d1.y),
+                                        pick(a1.z, b1.z, c1v.z, d1.z), pick(a1.w, b1.w, c1v.w, d1.w)));
+    }
+}
+
 // avgpool_f (kernels.h:444-493): in-range taps summed kx then ky, divided by kh*kw regardless of padding
 __global__ void __launch_bounds__(256) avgpool_f32_kernel(const float *__restrict__ in, float *__restrict__ out,
                                                           PoolGeom g) {
@@ -201,6 +246,18 @@ SWC_EXPORT int swcb200_maxpool_bf16(swcb200_ctx *ctx, const void *input, void *o
     SWC_REQUIRE(ctx, input && output, SWCB200_ERR_BAD_ARG, "maxpool_bf16: null tensor");
     bool vec = (g.C % 8 == 0) && swc_aligned16(input) && swc_aligned16(output);
     dim3 grid, block;
+    if (vec && g.kh == 2 && g.kw == 2 && g.sh == 2 && g.sw == 2 && g.pt == 0 && g.pl == 0 && 2 * g.OH <= g.H && 2 * g.OW <= g.W) {
+        const int cg = g.C / 8;
+        const long long rowlen = (long long)g.OW * cg, half = (rowlen + 1) / 2, rows = (long long)g.N * g.OH;
+        SWC_REQUIRE(ctx, rowlen <= 0x7fffffffLL && rows <= 0x7fffffffLL, SWCB200_ERR_TOO_LARGE,
+                    "maxpool_bf16: output row or row count beyond 2^31");
+        const int threads = half >= 256 ? 256 : (int)((half + 31) / 32 * 32);
+        const long long by = (half + threads - 1) / threads, cap = (long long)ctx->sm_count * 16;
+        SWC_REQUIRE(ctx, by <= 65535, SWCB200_ERR_TOO_LARGE, "maxpool_bf16: output row too long");
+        maxpool_bf16_2x2_kernel<<<dim3((unsigned)(rows < cap ? rows : cap), (unsigned)by), threads, 0, ctx->stream>>>(
+            (const uint4 *)input, (uint4 *)output, (int)rows, g.H, g.W, g.OH, g.OW, cg);
+        return swc_check_launch(ctx, "maxpool_bf16");
+    }
     rc = pool_launch_geom(ctx, g, vec ? 8 : 1, &grid, &block);
     if (rc) return rc;
     if (vec)

@@ -214,6 +214,50 @@ __global__ void __launch_bounds__(256) argmax_kernel(const float *__restrict__ i
     }
 }
 
+// top_k = 1 on rows of 16-byte aligned float4: the whole row of a warp's lanes is requested before the first
+// comparison (P float4 per lane, n <= 128 * P), scanned in index order so that `>=` leaves the HIGHEST index among
+// equal maxima, the same winner as the pair ordering above.
+template <int P>
+__global__ void __launch_bounds__(256) argmax_top1_vec_kernel(const float *__restrict__ in, int *__restrict__ idx, int m, int n) {
+    const int lane = threadIdx.x & 31;
+    const int warps_per_cta = blockDim.x >> 5;
+    const int n4 = n >> 2;
+    for (long long row = (long long)blockIdx.x * warps_per_cta + (threadIdx.x >> 5); row < m;
+         row += (long long)gridDim.x * warps_per_cta) {
+        const float4 *r = reinterpret_cast<const float4 *>(in + (size_t)row * n);
+        float4 v[P];
+#pragma unroll
+        for (int u = 0; u < P; u++) {
+            const int j4 = lane + 32 * u;
+            v[u] = j4 < n4 ? __ldcs(r + j4) : make_float4(0.f, 0.f, 0.f, 0.f);
+        }
+        float bv = 0.f;
+        int bi = -1;
+#pragma unroll
+        for (int u = 0; u < P; u++) {
+            const int j4 = lane + 32 * u;
+            if (j4 >= n4) continue;
+            const float e[4] = {v[u].x, v[u].y, v[u].z, v[u].w};
+#pragma unroll
+            for (int k = 0; k < 4; k++)
+                if (bi < 0 || e[k] >= bv) {
+                    bv = e[k];
+                    bi = 4 * j4 + k;
+                }
+        }
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) {
+            float ov = __shfl_xor_sync(kFull, bv, o);
+            int oi = __shfl_xor_sync(kFull, bi, o);
+            if (oi >= 0 && (bi < 0 || beats(ov, oi, bv, bi))) {
+                bv = ov;
+                bi = oi;
+            }
+        }
+        if (lane == 0) idx[row] = bi;
+    }
+}
+
 // accum[0] += rows whose label is among their n predictions, accum[1] += rows; integer counters, so the result does
 // not depend on the order of the atomic additions
 __global__ void __launch_bounds__(256) accuracy_kernel(const int *__restrict__ pred, const int *__restrict__ label,
@@ -286,6 +330,15 @@ SWC_EXPORT int swcb200_argMax_i(swcb200_ctx *ctx, const float *input, int *idx, 
     if (m == 0 || top_k == 0) return SWCB200_OK;
     SWC_REQUIRE(ctx, input && idx, SWCB200_ERR_BAD_ARG, "argMax_i: null tensor");
     unsigned grid = swc_grid(ctx, (size_t)m, 8, 8);
+    if (top_k == 1 && n % 4 == 0 && n >= 128 && n <= 128 * 8 && swc_aligned16(input)) {
+        if (n <= 128 * 2)
+            argmax_top1_vec_kernel<2><<<grid, 256, 0, ctx->stream>>>(input, idx, m, n);
+        else if (n <= 128 * 4)
+            argmax_top1_vec_kernel<4><<<grid, 256, 0, ctx->stream>>>(input, idx, m, n);
+        else
+            argmax_top1_vec_kernel<8><<<grid, 256, 0, ctx->stream>>>(input, idx, m, n);
+        return swc_check_launch(ctx, "argMax_i");
+    }
     argmax_kernel<<<grid, 256, 0, ctx->stream>>>(input, idx, m, n, top_k);
     return swc_check_launch(ctx, "argMax_i");
 }

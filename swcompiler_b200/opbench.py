@@ -92,38 +92,6 @@ def latency(iters):
         print(json.dumps(r))
 
 
-def conv_roles():
-    """Cycle counters of CTA 0 of the convolution kernel on the config-5 layer, per tile: where the producer, the
-    MMA-issuing warp and one epilogue warp spend their time.  Needs `python -m swcompiler_b200.build --conv-timing`."""
-    import ctypes as C
-    be = swc.Backend(0, swc.TC_BF16)
-    if not hasattr(be.lib, "swcb200_debug_conv_timing"):
-        raise SystemExit("the library was built without --conv-timing")
-    dev = be.device
-    g = torch.Generator(device=dev).manual_seed(0)
-    n, hw, ch = 256, 56, 64
-    x = torch.randn((n, hw, hw, ch), generator=g, device=dev).to(torch.bfloat16)
-    fp = be.pack_filter_bf16(torch.randn((ch, 3, 3, ch), generator=g, device=dev) * (2.0 / (9 * ch)) ** 0.5)
-    b = torch.zeros(ch, device=dev)
-    o = torch.empty_like(x)
-    buf = (C.c_longlong * 16)()
-    for res in (None, x):
-        for _ in range(3):
-            be.conv2d_bf16(x, fp, b, (3, 3), (1, 1), (1, 1, 1, 1), relu=True, residual=res, out=o)
-        torch.cuda.synchronize()
-        be.lib.swcb200_debug_conv_timing(buf)  # clears the counters
-        be.conv2d_bf16(x, fp, b, (3, 3), (1, 1), (1, 1, 1, 1), relu=True, residual=res, out=o)
-        torch.cuda.synchronize()
-        be.lib.swcb200_debug_conv_timing(buf)
-        t = list(buf)
-        tiles = max(1, t[4])
-        print(json.dumps({"kernel": "conv2d_bf16 3x3 64->64 [256,56,56,64]", "residual": res is not None, "tiles_cta0": tiles,
-                          "cycles_per_tile": {"producer_wait_window_free": t[0] / tiles, "issuer_wait_accumulator": t[1] / tiles,
-                                              "issuer_wait_window": t[2] / tiles, "issuer_issue": t[3] / tiles,
-                                              "epilogue_wait": t[5] / tiles, "epilogue_work": t[6] / tiles},
-                          "cta0_cycles": t[7], "cta0_ns": t[8], "ghz": t[7] / max(1, t[8]), "marks": {"prologue_done": t[9], "filter_ready": t[10], "issuer_done": t[11], "epi_loop_done": t[12], "stores_done": t[13]}}))
-
-
 def op_rows(iters=20, only=None):
     """One row per kernel at the benchmark configurations' sizes: achieved GB/s or TFLOP/s and the fraction of the
     measured peak (see the module docstring)."""
@@ -231,11 +199,7 @@ def main():
     ap.add_argument("--iters", type=int, default=20)
     ap.add_argument("--latency", action="store_true",
                     help="the two small configurations (MLP batch 64, LeNet-style net batch 32): microseconds per forward")
-    ap.add_argument("--conv-roles", action="store_true",
-                    help="per-role cycle counters of the convolution kernel (library built with --conv-timing)")
     args = ap.parse_args()
-    if args.conv_roles:
-        return conv_roles()
     if args.latency:
         return latency(args.iters)
     for r in op_rows(args.iters, args.only):

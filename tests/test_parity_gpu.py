@@ -166,3 +166,39 @@ def test_bandwidth_kernels_at_size(gpu, n):
     b = r.standard_normal(n).astype(np.float32)
     assert np.array_equal(gpu.relu_f(a), np.where(a > 0, a, np.float32(0)))
     assert np.array_equal(gpu.vecAdd_f(a, b), a + b)
+
+
+def test_top1_argmax_fast_path_against_oracle(gpu, oracle):
+    """top_k = 1 on rows of whole float4 (the vectorised kernel): random rows at the three register budgets, and rows of
+    quantised values where equal maxima are the rule, so that 'the higher index wins' is exercised in every lane."""
+    r = np.random.default_rng(41)
+    for (m, n) in [(300, 1000), (64, 512), (17, 256), (9, 128), (5, 1024)]:
+        x = r.standard_normal((m, n)).astype(np.float32)
+        assert np.array_equal(gpu.argMax_i(x, 1), oracle.argMax_i(x, 1)), (m, n)
+        q = np.round(r.random((m, n)) * 3).astype(np.float32)
+        q[0, :] = 2.0                    # a whole row of equal values: the last index
+        q[m - 1, ::7] = -0.0
+        assert np.array_equal(gpu.argMax_i(q, 1), oracle.argMax_i(q, 1)), (m, n)
+    assert gpu.argMax_i(np.full((2, 128), 2.0, np.float32), 1).tolist() == [[127], [127]]
+
+
+def test_maxpool_on_bf16_storage_against_oracle(gpu, oracle):
+    """MaxPool on bf16 tensors: the maxima of bf16 values are bf16 values, so the result must equal the oracle's
+    maxpool_f on the same (bf16-representable) numbers bit for bit -- the 2x2/2 fast path (even and odd extents,
+    ties, signed zeros, all-negative windows) and the general kernel (padding, 3x3, stride 1)."""
+    r = np.random.default_rng(43)
+    spec = [((2, 56, 56, 64), (2, 2), (2, 2), (0, 0, 0, 0)), ((1, 8, 8, 64), (2, 2), (2, 2), (0, 0, 0, 0)),
+            ((3, 7, 9, 8), (2, 2), (2, 2), (0, 0, 0, 0)), ((1, 6, 6, 24), (2, 2), (2, 2), (0, 0, 0, 0)),
+            ((2, 9, 7, 16), (3, 3), (2, 2), (1, 1, 1, 1)), ((1, 5, 6, 8), (3, 2), (1, 1), (1, 0, 1, 0)),
+            ((1, 6, 6, 5), (2, 2), (2, 2), (0, 0, 0, 0))]
+    for idims, k, s, p in spec:
+        for kind in ("normal", "ties"):
+            x = r.standard_normal(idims) if kind == "normal" else np.round(r.random(idims) * 3) - 4
+            x = cases.bf16_round(x.astype(np.float32))
+            if kind == "ties":
+                x[0, 0, :2, :] = np.float32(-0.0)
+                x[0, 1, :2, :] = np.float32(0.0)
+            want = oracle.maxpool_f(x, k, s, p)
+            got = gpu.be.maxpool_bf16(torch.from_numpy(x).cuda().to(torch.bfloat16), k, s, p)
+            gpu.be.sync()
+            assert np.array_equal(bits(got.float().cpu().numpy()), bits(want)), (idims, k, s, p, kind)
