@@ -385,67 +385,47 @@ def check_gather_widemlp(env, prog, gathered, rows, samples=48):
 
 def run_e2e(env, args, prog, x, probs2, comm, gathered, rows):
     """End to end with host buffers: every rank copies its rows of X in from pinned host memory while earlier chunks
-    compute; with more than one GPU the probabilities are gathered on rank 0, which copies the whole result out
-    (the copy-out of step s overlaps step s+1); with one GPU the copy-out is chunked like the copy-in."""
+    compute, and copies its probabilities out, chunk by chunk, into its rows of ONE result array in host memory.  With
+    more than one GPU that array is a shared-memory segment every rank has mapped and registered with CUDA: the Gather
+    of the results on the host is carried by all the GPUs' copy engines at once instead of funnelling through rank 0's
+    link."""
     torch = env.torch
     world, rank, device = env.world, env.rank, env.device
     steps = max(3, min(args.steps, 10))
     x_host = torch.empty((rows, WIDTH), dtype=torch.bfloat16).pin_memory()
     x_host.copy_(x.cpu())
     x_dev = torch.empty_like(x)
-    chunk = min(8192, max(2048, rows // 4))
+    chunk = min(4096, max(1024, rows // 8))  # short first copy-in and last copy-out; the copies, not the GEMMs, set the pace
     main = torch.cuda.current_stream(device)
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    shm_path = None
     if world == 1:
-        probs_host = torch.empty((rows, CLASSES), dtype=torch.float32).pin_memory()
-
-        def one():
-            prog.forward_host(x_host, probs_host, x_dev, probs2[0], chunk_rows=chunk)
-        out_bytes = probs_host.numel() * 4
+        result = torch.empty((BATCH, CLASSES), dtype=torch.float32).pin_memory()
     else:
-        out_host = [torch.empty((BATCH, CLASSES), dtype=torch.float32).pin_memory() for _ in range(2)] if rank == 0 else None
-        s_out = torch.cuda.Stream(device)
-        cs = comm.be.torch_stream
-        sync_word = torch.zeros(1, device=device)
-        state = {"s": 0, "gdone": [None, None]}
+        # the result array: a file in /dev/shm created by rank 0, mapped by everyone, page-locked for CUDA by everyone
+        nbytes = BATCH * CLASSES * 4
+        if rank == 0:
+            import tempfile
+            st = os.statvfs("/dev/shm") if os.path.isdir("/dev/shm") else None
+            where = "/dev/shm" if st and st.f_bavail * st.f_frsize > 2 * nbytes else tempfile.gettempdir()
+            shm_path = os.path.join(where, f"swcb200_bench_{os.getpid()}")
+        shm_path = env.exchange(shm_path)
+        if rank == 0:
+            with open(shm_path, "wb") as f:
+                f.truncate(nbytes)
+        env.barrier()
+        result = torch.from_file(shm_path, shared=True, size=BATCH * CLASSES, dtype=torch.float32).view(BATCH, CLASSES)
+        err = torch.cuda.cudart().cudaHostRegister(result.data_ptr(), nbytes, 0)
+        if int(err) != 0:
+            raise RuntimeError(f"cudaHostRegister of the shared result array failed ({err})")
+    mine = result[rank * rows:(rank + 1) * rows]
 
-        def one():
-            # One gathered buffer on rank 0, so the steps hand it over in turn: the Gather of step s (every rank's
-            # peer copy, then a one-word all-reduce that completes on rank 0 only when all copies are in), rank 0's
-            # copy-out of it, and a second one-word all-reduce that rank 0 joins after that copy-out, which tells
-            # the other ranks that the buffer may be overwritten by step s+1.  Copy-in and compute of step s+1 run
-            # on the main stream meanwhile.
-            s = state["s"]
-            state["s"] += 1
-            out = probs2[s % 2]
-            if state["gdone"][s % 2] is not None:
-                main.wait_event(state["gdone"][s % 2])  # the Gather of step s-2 has read this buffer
-            prog.forward_host(x_host, None, x_dev, out, chunk_rows=chunk)
-            ready = torch.cuda.Event()
-            ready.record(main)
-            cs.wait_event(ready)
-            comm.gather_rows(out)
-            gd = torch.cuda.Event()
-            gd.record(cs)
-            state["gdone"][s % 2] = gd
-            comm.allreduce_sum(sync_word, out=sync_word)
-            if rank == 0:
-                arrived = torch.cuda.Event()
-                arrived.record(cs)
-                s_out.wait_event(arrived)
-                with torch.cuda.stream(s_out):
-                    out_host[s % 2].copy_(gathered, non_blocking=True)
-                    od = torch.cuda.Event()
-                    od.record(s_out)
-                cs.wait_event(od)
-            comm.allreduce_sum(sync_word, out=sync_word)
-        out_bytes = BATCH * CLASSES * 4
+    def one():
+        prog.forward_host(x_host, mine, x_dev, probs2[0], chunk_rows=chunk)
+    out_bytes = BATCH * CLASSES * 4
 
     def finish():
-        if world > 1:
-            main.wait_stream(comm.be.torch_stream)
-            if rank == 0:
-                main.wait_stream(s_out)
+        pass  # forward_host has made the main stream wait for the last copy-out
 
     for _ in range(2):
         one()
@@ -473,12 +453,24 @@ def run_e2e(env, args, prog, x, probs2, comm, gathered, rows):
     probe_host = torch.empty((rows, CLASSES), dtype=torch.float32).pin_memory()
     d2h = copy_gbs(probe_host, probs2[0], rows * CLASSES * 4)
     links = env.gather_floats([h2d, d2h])
+    # the gathered result on the host against this rank's probabilities on the device (every rank checks its rows)
+    torch.cuda.synchronize()
+    same = bool(torch.equal(mine, probs2[0].cpu()))
+    all_same = env.max_over_ranks([0.0 if same else 1.0])[0] == 0.0
+    env.barrier()
+    if world > 1:
+        torch.cuda.cudart().cudaHostUnregister(result.data_ptr())
+        del mine, result
+        env.barrier()
+        if rank == 0:
+            os.unlink(shm_path)
     if rank != 0:
         return None
     return {"value": BATCH * steps / (e2e_ms * 1e-3), "unit": UNIT, "h2d_bytes_per_step": x_host.numel() * 2 * world,
             "d2h_bytes_per_step": out_bytes, "ms_per_step": e2e_ms / steps, "steps": steps, "chunk_rows": chunk,
-            "program": "H2D of each rank's rows in chunks overlapped with compute" +
-                       ("; chunked D2H" if world == 1 else "; Gather on rank 0 (peer copies); D2H of the gathered result by rank 0, overlapped with the next step"),
+            "program": "H2D of each rank's rows in chunks overlapped with compute; chunked D2H of its probabilities into its rows of "
+                       "one result array in host memory" + ("" if world == 1 else " (a shared-memory segment all ranks map: the Gather happens over every GPU's host link at once)"),
+            "result_on_host_matches_device": all_same,
             "host_link_GBps_all_ranks_copying": {"h2d_per_rank": [l[0] for l in links], "d2h_per_rank": [l[1] for l in links],
                                                   "h2d_sum": sum(l[0] for l in links), "d2h_sum": sum(l[1] for l in links)}}
 
