@@ -41,6 +41,13 @@
 // N, so at N = 64 the pair ran the layer in 91 us against 65 us for this kernel.  It pays from N = 256 up, which is
 // where the FC kernel uses it.
 //
+// A fused-row form was built and measured too: the three taps of a filter row share their window rows, so one MMA
+// with N = 3 * oC = 192 over the row's three (contiguous) filter slices replaces three N = 64 MMAs -- 12 MMAs of 96
+// cycles per tile instead of 36 of 48 -- and the epilogue adds the three column blocks shifted by one and two pixels
+// with warp shuffles (tiles of 4 rows x 32 window columns, so that a warp is one row).  Correct, but 69.5 us against
+// 62.6 us on the same run: the epilogue then reads three times the tensor memory and shuffles 128 values per thread
+// and tile, and even with its arithmetic switched off the kernel took 53.7 us (58 us for this kernel in that state).
+//
 // Restrictions: stride 1, group 1, iC a multiple of 64, oC a multiple of 32 and <= 256, kw <= 9, filter at
 // most 96 KiB in bf16, two windows fitting beside it.  Other shapes return SWCB200_ERR_UNSUPPORTED (the
 // strict kernel takes them).
