@@ -30,7 +30,7 @@ def reference_root() -> str:
 
 # the sample programs: <graph>[_dp<N> | _mp<N>][_fused], see gen_driver.cpp
 PROGRAMS = ("mlp8", "convnet", "resblock", "mlp8_fused", "convnet_fused", "resblock_fused",
-            "resproj", "resproj_fused", "convact", "convact_fused",
+            "resproj", "resproj_fused", "convact", "convact_fused", "c2lenet", "c2resnet", "c2resnet_fused",
             "mlp8_dp2", "mlp8_dp2_fused", "fcpair_mp2", "mlp8_mp2", "resblock_dp2", "mlp_eval", "mlp_eval_fused",
             "mlp8_graph", "resblock_fused_graph")
 
@@ -53,10 +53,12 @@ def build(ref: str = None, quiet: bool = True) -> str:
     os.makedirs(EMITTED, exist_ok=True)
     flags = ["-std=c++11", "-O1", "-w", "-I" + os.path.join(ref, "src"), "-I" + os.path.join(ref, "include"), "-I" + HERE]
     jobs, objs = [], []
-    for s in reference_sources(ref) + [os.path.join(HERE, "B200Codegen.cpp"), os.path.join(HERE, "gen_driver.cpp")]:
+    ours = [os.path.join(HERE, f) for f in ("B200Codegen.cpp", "Caffe2Import.cpp", "gen_driver.cpp")]
+    for s in reference_sources(ref) + ours:
         o = os.path.join(BUILD, os.path.relpath(s, "/").replace(os.sep, "_")[:-4] + ".o")
         objs.append(o)
-        if not os.path.exists(o) or os.path.getmtime(o) < max(os.path.getmtime(s), os.path.getmtime(os.path.join(HERE, "B200Codegen.h"))):
+        hdr = max(os.path.getmtime(os.path.join(HERE, h)) for h in ("B200Codegen.h", "Caffe2Import.h"))
+        if not os.path.exists(o) or os.path.getmtime(o) < max(os.path.getmtime(s), hdr):
             jobs.append(["g++", *flags, "-c", s, "-o", o])
 
     def run(cmd):
@@ -71,8 +73,21 @@ def build(ref: str = None, quiet: bool = True) -> str:
     return exe
 
 
+def write_caffe2_models(where: str):
+    """The serialized nets of the two synthetic Caffe2 models (tests/golden/caffe2_models.py), for gen_driver's import."""
+    import importlib.util
+    spec = importlib.util.spec_from_file_location("caffe2_models", os.path.join(ROOT, "tests", "golden", "caffe2_models.py"))
+    mod = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(mod)
+    for name in ("c2lenet", "c2resnet"):
+        predict, init, _, _ = mod.model(name)
+        open(os.path.join(where, name + "_predict.pb"), "wb").write(predict)
+        open(os.path.join(where, name + "_init.pb"), "wb").write(init)
+
+
 def emit(exe: str, out_dir: str = EMITTED):
     os.makedirs(out_dir, exist_ok=True)
+    write_caffe2_models(BUILD)
     for which in PROGRAMS:
         # the generator also drops Graph.cpp / G_Makefile / SW_Makefile and *.dot in its working directory
         r = subprocess.run([exe, which, out_dir, "$(abspath ../../..)"], cwd=BUILD, capture_output=True, text=True)

@@ -18,6 +18,9 @@
 //   gen_driver convact  <out_dir> <repo_root>  [2,8,8,64] -> Conv2dWithActivation(3x3, ReLU) -> MaxPool -> FC -> Softmax -> top-1
 //   gen_driver badop    <out_dir> <repo_root>  a graph with an op outside the kernel table (ElementMul): the generator
 //                                              must refuse it (exit code 3, #error in the text)
+//   gen_driver c2lenet  <out_dir> <repo_root>  a Caffe2 model read by Caffe2Import from c2lenet_predict.pb / c2lenet_init.pb in
+//   gen_driver c2resnet <out_dir> <repo_root>  the working directory (tests/golden/caffe2_models.py writes them); the weight
+//                                              files the import produces go to the working directory too
 //   A name with _dp<N> (mlp8_dp2) partitions the graph over N ranks by the batch: config.mpi, config.mpi_size = N,
 //   config.force_data_parallel, the reference's ParallelLabeling / ParallelLowering passes unchanged.
 //   A name with _mp<N> (fcpair_mp2, mlp8_mp2) sets the model-parallel strategies by hand -- first FC split by output
@@ -38,6 +41,7 @@
 #include <vector>
 
 #include "B200Codegen.h"
+#include "Caffe2Import.h"
 #include "SWC.h"
 #include "pass/EliminationPass.h"
 #include "pass/ParallelLoweringPass.h"
@@ -280,6 +284,26 @@ IRGraph *build_convact() {
     return g;
 }
 
+// A Caffe2 model: predict and init net from the working directory, top-1 behind the model's softmax.
+IRGraph *build_caffe2(const std::string &model) {
+    auto *g = new IRGraph();
+    auto *data = model == "c2lenet" ? new TensorNode("data", {4, 28, 28, 1}) : new TensorNode("data", {2, 8, 8, 64});
+    data->getTensor()->setTensorInit(TensorInitType::FILE, model + "_input.bin");
+    swcb200::Caffe2Import imp(g, model + "_predict.pb", model + "_init.pb", {data}, ".", model + "_");
+    if (!imp.ok()) {
+        std::cerr << "import of " << model << " failed: " << imp.error() << "\n";
+        exit(4);
+    }
+    TensorNode *probs = imp.output();
+    const size_t rows = probs->getDims()[0];
+    auto *am = op(g, "argmax", new ArgMaxOp(1), probs);
+    auto *top1 = result(g, "top1", {rows, 1}, am, DataType::Int32_t);
+    g->findInOut();
+    g->updateTopology();
+    g->addDisplayTensorNodes(probs, top1);
+    return g;
+}
+
 // an op the kernel table has no entry for, in the middle of a forward pass
 IRGraph *build_badop() {
     auto *g = new IRGraph();
@@ -331,6 +355,7 @@ int main(int argc, char **argv) {
                  : base == "mlp_eval" ? build_mlp_eval()
                  : base == "resproj" ? build_resproj()
                  : base == "convact" ? build_convact()
+                 : (base == "c2lenet" || base == "c2resnet") ? build_caffe2(base)
                  : base == "badop" ? build_badop() : nullptr;
     if (!g) {
         std::cerr << "unknown graph " << base << "\n";

@@ -183,6 +183,10 @@ class Interp:
         self.t[out] = y.reshape(-1)
 
     # ---- bf16 storage entry points: bf16-rounded operands, fp32 arithmetic
+    def op_avgpool_f(self, x, out, idm, od, kd, sd, pd):
+        xv = self._get(x).reshape(self.dims[idm.strip()])
+        self.t[out.strip()] = self.o.avgpool_f(xv, self.dims[kd.strip()], self.dims[sd.strip()], self.dims[pd.strip()]).reshape(-1)
+
     def op_cast_f32_to_bf16(self, src, dst, count):
         self.t[dst] = cases.bf16_round(self._get(src)[:int(count)])
 
