@@ -339,7 +339,7 @@ def run_widemlp(env, args, split=False):
     rec = None
     if rank == 0:
         # DRAM traffic of one hidden-layer launch by its operands: A and C once (rows x 4096 bf16 each), the packed
-        # weight once (32 MiB); the ncu capture of an 8192-row launch agrees within 5 % (profiles/).  Not measured here.
+        # weight once (32 MiB); an ncu capture of an 8192-row launch measured 3 % less than this count.  Not measured here.
         traffic_model = 2.0 * rows * WIDTH * 2 + WIDTH * WIDTH * 2
         rec = {
             "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps, "warmup": max(args.warmup, 3),

@@ -83,6 +83,27 @@ def latency_rows(iters=50):
                 rows.append({"config": label, "mode": name, "us_per_forward": t * 1e6, "samples_per_s": batch / t,
                              "graph_us_per_forward": tg * 1e6, "graph_samples_per_s": batch / tg,
                              "launches_per_forward": per_forward})
+            if mode == swc.TC_BF16:
+                # the program the fusion planner prints for the MLP: weights packed once at load, one launch per FC layer
+                # (matmul + bias + tanh), bf16 between them
+                wp0, wp1 = be.pack_weight_bf16(w0), be.pack_weight_bf16(w1)
+
+                def mlp_fused():
+                    h = be.fc_bf16(be.cast_f32_to_bf16(x1), wp0, b0, swc.ACT_TANH)
+                    return be.matrixSoftmax_f(be.fc_bf16(h, wp1, b1, swc.ACT_NONE, torch.float32))
+
+                n0 = be.launches
+                mlp_fused()
+                per_forward = be.launches - n0
+                t = _time(mlp_fused, iters)
+                stream.synchronize()
+                graph = torch.cuda.CUDAGraph()
+                with torch.cuda.graph(graph, stream=stream):
+                    mlp_fused()
+                tg = _time(graph.replay, iters)
+                rows.append({"config": "MLP 784-512-10, batch 64", "mode": "fused bf16 program (packed weights, one launch per FC layer)",
+                             "us_per_forward": t * 1e6, "samples_per_s": 64 / t, "graph_us_per_forward": tg * 1e6,
+                             "graph_samples_per_s": 64 / tg, "launches_per_forward": per_forward})
             be.sync()
     return rows
 

@@ -23,7 +23,7 @@ from oracle import oracle as orc  # noqa: E402
 
 
 def main():
-    ref_root = sys.argv[1] if len(sys.argv) > 1 else "/root/reference"
+    ref_root = sys.argv[1] if len(sys.argv) > 1 else (os.environ.get("REFERENCE_ROOT") or os.path.join(os.path.dirname(ROOT), "reference"))
     os.environ["REFERENCE_ROOT"] = ref_root
     orc.build()
     ref = orc.Reference()
