@@ -71,6 +71,10 @@ int swcb200_set_precision(swcb200_ctx *ctx, int precision);
  * SWCB200_ERR_TIMEOUT; the context stays usable.  The limit is counted in SM clock cycles, 4e9 by
  * default (2 to 3 seconds).  The reference has no counterpart (its kernels cannot wait). */
 int swcb200_set_wait_limit(swcb200_ctx *ctx, long long cycles);
+/* The persistent tensor-core kernels (swcb200_fc_bf16*, swcb200_conv2d_bf16) launched through this context take at
+ * most `sms` SMs (0 = all, the default).  They hold nearly all of an SM's shared memory, so a kernel of another
+ * stream -- a collective that should run BESIDE a GEMM -- only finds room on SMs left free this way. */
+int swcb200_set_sm_limit(swcb200_ctx *ctx, int sms);
 /* Self-test of that path: launches one thread that waits, with the same bounded wait, on a barrier
  * nothing arrives at.  After the context's limit the kernel returns and swcb200_sync reports
  * SWCB200_ERR_TIMEOUT.  Set a short limit first (a million cycles is half a millisecond). */
@@ -229,6 +233,7 @@ int swcb200_maxpool_bf16(swcb200_ctx *ctx, const void *input, void *output, cons
  * parameter here. */
 
 #define SWCB200_UNIQUE_ID_BYTES 128
+#define SWCB200_MAX_PEERS 8 /* ranks whose memory one kernel addresses directly (one NVSwitch box) */
 /* Path of libnccl.so.2 to dlopen (NULL: the loader's default search). Call before comm_init. */
 int swcb200_comm_load(const char *libnccl_path);
 int swcb200_comm_unique_id(void *id_out /* SWCB200_UNIQUE_ID_BYTES */);
@@ -245,6 +250,26 @@ int swcb200_comm_watch(swcb200_ctx *ctx, int timeout_ms);
 /* The same polling loop run against the NCCL library at `libnccl_path` and a stream that never becomes idle;
  * needs no GPU.  For testing the loop with a stand-in library. */
 int swcb200_comm_watch_selftest(const char *libnccl_path, int timeout_ms);
+/* The Reduce join of a model-parallel layer (ParallelCodegen.cpp:873-896: MPI_Reduce of the partial sums) done by
+ * the producing GEMM itself, over peer memory instead of a collective kernel.  Every rank owns m/p rows of the output
+ * and holds a slot array of p slots [m/p, ld_slot] fp32, slot r for rank r's partial block.
+ *   swcb200_peer_slots_setup      collective, once: exchanges CUDA-IPC handles of the ranks' slot arrays (each must
+ *                                 come from the CUDA allocator); all_slots_out[r] = rank r's array as this rank
+ *                                 addresses it (SWCB200_MAX_PEERS entries at most).
+ *   swcb200_fc_bf16_scatter_rows  C = A . Wp^T (bf16 in, fp32 out, no bias) whose epilogue stores row i into slot
+ *                                 `rank` of the array of the rank that owns it, owner_slots[i / (m/p)]: plain 128-bit
+ *                                 stores over NVLink, overlapped with the tensor-core work of the other tiles.
+ *   swcb200_sum_slots             out[i] = ((s_0[i] + s_1[i]) + ...): the owner adds its p slots in rank order
+ *                                 (a result that does not depend on timing), after the ranks have met (e.g. a
+ *                                 one-word swcb200_allreduce_sum on the same streams).
+ * No waiting on a peer happens inside any kernel. */
+int swcb200_peer_slots_setup(swcb200_ctx *ctx, void *local_slots, void **all_slots_out);
+int swcb200_peer_slots_release(swcb200_ctx *ctx);
+int swcb200_fc_bf16_scatter_rows(swcb200_ctx *ctx, int m, int n, int k, const void *a_bf16, int lda,
+                                 const void *wp_bf16, int ldw, void *const *owner_slots, int nranks,
+                                 int rank, int ld_slot);
+int swcb200_sum_slots(swcb200_ctx *ctx, const float *slots, size_t slot_stride, int nslots, float *out,
+                      size_t count);
 /* Scatter node (ParallelCodegen.cpp:457-575): axis -1 = MPI_Bcast; axis >= 0 = each rank gets
  * its slice of `src` (read on root only) packed contiguously into `dst`. */
 int swcb200_scatter(swcb200_ctx *ctx, const void *src, void *dst, const size_t *dims, int ndim,

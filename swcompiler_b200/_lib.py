@@ -14,6 +14,7 @@ OK, ERR_BAD_ARG, ERR_BAD_SHAPE, ERR_MISALIGNED, ERR_UNSUPPORTED, ERR_CUDA, ERR_N
 STRICT_F32, TC_BF16 = 0, 1
 F32, BF16, I32 = 0, 1, 2
 ACT_NONE, ACT_RELU, ACT_TANH = 0, 1, 2
+MAX_PEERS = 8
 
 _lib = None
 

@@ -93,6 +93,10 @@ struct swcb200_comm {
     void *rows_ipc_base = nullptr; // what cudaIpcOpenMemHandle returned (non-root), to close later
     size_t rows_bytes = 0;
     int rows_root = -1;
+    // peer slots (swcb200_peer_slots_*): every rank's slot array as this rank can address it
+    void *slots[SWCB200_MAX_PEERS] = {nullptr};      // [rank]: own array, or IPC mapping + offset
+    void *slots_ipc_base[SWCB200_MAX_PEERS] = {nullptr};
+    int slots_ready = 0;
 };
 
 namespace {
@@ -208,6 +212,7 @@ SWC_EXPORT int swcb200_comm_destroy(swcb200_ctx *ctx) {
     if (!ctx) return SWCB200_ERR_BAD_ARG;
     if (!ctx->comm) return SWCB200_OK;
     swcb200_gather_rows_release(ctx);
+    swcb200_peer_slots_release(ctx);
     cudaSetDevice(ctx->device);
     cudaStreamSynchronize(ctx->stream);
     int r = g_nccl.CommDestroy(ctx->comm->comm);
@@ -284,6 +289,7 @@ SWC_EXPORT int swcb200_comm_watch(swcb200_ctx *ctx, int timeout_ms) {
     if (rc == SWCB200_ERR_NCCL || rc == SWCB200_ERR_TIMEOUT) {
         // the communicator is gone (ncclCommAbort frees it); peer mappings of the row gather go with it
         swcb200_gather_rows_release(ctx);
+        swcb200_peer_slots_release(ctx);
         delete ctx->comm;
         ctx->comm = nullptr;
     }
@@ -489,6 +495,65 @@ SWC_EXPORT int swcb200_gather_rows_release(swcb200_ctx *ctx) {
     if (ctx->comm->rows_ipc_base) cudaIpcCloseMemHandle(ctx->comm->rows_ipc_base);
     ctx->comm->rows_ipc_base = ctx->comm->rows_dst = nullptr;
     ctx->comm->rows_root = -1;
+    return SWCB200_OK;
+}
+
+// Peer slots: the join of a model-parallel layer without a collective kernel.  Every rank owns a block of the
+// output rows and keeps, for each rank, a slot that rank's partial block is written into -- by the producing GEMM's
+// own epilogue, straight over NVLink (swcb200_fc_bf16_scatter_rows).  Here the ranks exchange CUDA-IPC handles of
+// their slot arrays once, so that each can address all of them.
+SWC_EXPORT int swcb200_peer_slots_setup(swcb200_ctx *ctx, void *local_slots, void **all_slots_out) {
+    SWC_CTX(ctx);
+    SWC_REQUIRE(ctx, ctx->comm != nullptr, SWCB200_ERR_NCCL, "peer_slots_setup: no communicator");
+    swcb200_comm *c = ctx->comm;
+    SWC_REQUIRE(ctx, c->nranks <= SWCB200_MAX_PEERS, SWCB200_ERR_UNSUPPORTED, "peer_slots_setup: at most %d ranks", SWCB200_MAX_PEERS);
+    SWC_REQUIRE(ctx, local_slots && all_slots_out, SWCB200_ERR_BAD_ARG, "peer_slots_setup: null argument");
+    SWC_REQUIRE(ctx, !c->slots_ready, SWCB200_ERR_BAD_ARG, "peer_slots_setup: already set up (release first)");
+    GetRangeFn range = get_range_fn();
+    SWC_REQUIRE(ctx, range != nullptr, SWCB200_ERR_CUDA, "peer_slots_setup: cuMemGetAddressRange not found");
+    RowsExport mine;
+    memset(&mine, 0, sizeof(mine));
+    CUdeviceptr base = 0;
+    size_t size = 0;
+    SWC_REQUIRE(ctx, range(&base, &size, (CUdeviceptr)local_slots) == CUDA_SUCCESS, SWCB200_ERR_CUDA,
+                "peer_slots_setup: the slot array is not a device allocation");
+    SWC_CUDA(ctx, cudaIpcGetMemHandle(&mine.handle, (void *)base));
+    mine.offset = (unsigned long long)((CUdeviceptr)local_slots - base);
+    // every rank's export to every rank: an all-gather of a few bytes through the communicator
+    void *dev = nullptr;
+    int rc = swc_scratch(ctx, sizeof(mine) * (size_t)(c->nranks + 1), &dev);
+    if (rc) return rc;
+    RowsExport all[SWCB200_MAX_PEERS];
+    uint8_t *send = (uint8_t *)dev, *recv = send + sizeof(mine);
+    SWC_CUDA(ctx, cudaMemcpyAsync(send, &mine, sizeof(mine), cudaMemcpyHostToDevice, ctx->stream));
+    SWC_NCCL(ctx, g_nccl.AllGather(send, recv, sizeof(mine), /*ncclInt8*/ 0, c->comm, ctx->stream));
+    SWC_CUDA(ctx, cudaMemcpyAsync(all, recv, sizeof(mine) * (size_t)c->nranks, cudaMemcpyDeviceToHost, ctx->stream));
+    SWC_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
+    for (int r = 0; r < c->nranks; r++) {
+        if (r == c->rank) {
+            c->slots[r] = local_slots;
+            continue;
+        }
+        void *mapped = nullptr;
+        SWC_CUDA(ctx, cudaIpcOpenMemHandle(&mapped, all[r].handle, cudaIpcMemLazyEnablePeerAccess));
+        c->slots_ipc_base[r] = mapped;
+        c->slots[r] = (uint8_t *)mapped + all[r].offset;
+    }
+    c->slots_ready = 1;
+    for (int r = 0; r < c->nranks; r++) all_slots_out[r] = c->slots[r];
+    return SWCB200_OK;
+}
+
+SWC_EXPORT int swcb200_peer_slots_release(swcb200_ctx *ctx) {
+    if (!ctx) return SWCB200_ERR_BAD_ARG;
+    if (!ctx->comm || !ctx->comm->slots_ready) return SWCB200_OK;
+    cudaSetDevice(ctx->device);
+    cudaStreamSynchronize(ctx->stream);
+    for (int r = 0; r < SWCB200_MAX_PEERS; r++) {
+        if (ctx->comm->slots_ipc_base[r]) cudaIpcCloseMemHandle(ctx->comm->slots_ipc_base[r]);
+        ctx->comm->slots_ipc_base[r] = ctx->comm->slots[r] = nullptr;
+    }
+    ctx->comm->slots_ready = 0;
     return SWCB200_OK;
 }
 

@@ -17,6 +17,7 @@ struct swcb200_ctx {
     cudaStream_t stream = nullptr;
     bool own_stream = false;
     int sm_count = 148;
+    int tc_sm_limit = 0;  // persistent tensor-core kernels take at most this many SMs (0 = all of them)
     uint64_t launches = 0;
     char last_error[512] = {0};
     // private scratch for the fp32 entry points in tensor-core mode (bf16 copies of operands);
@@ -57,6 +58,11 @@ int swc_pack_weight_padded(swcb200_ctx *ctx, const float *w, int k, int n, int l
         if (e__ != cudaSuccess)                                                                \
             return swc_fail((ctx), SWCB200_ERR_CUDA, "%s: %s", #call, cudaGetErrorString(e__)); \
     } while (0)
+
+// SMs a persistent tensor-core kernel of this context may occupy
+static inline int swc_tc_sms(const swcb200_ctx *ctx) {
+    return (ctx->tc_sm_limit > 0 && ctx->tc_sm_limit < ctx->sm_count) ? ctx->tc_sm_limit : ctx->sm_count;
+}
 
 static inline bool swc_aligned16(const void *p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
 

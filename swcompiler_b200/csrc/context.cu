@@ -142,6 +142,13 @@ SWC_EXPORT int swcb200_selftest_wait_timeout(swcb200_ctx *ctx) {
     return swc_check_launch(ctx, "selftest_wait_timeout");
 }
 
+SWC_EXPORT int swcb200_set_sm_limit(swcb200_ctx *ctx, int sms) {
+    if (!ctx) return SWCB200_ERR_BAD_ARG;
+    SWC_REQUIRE(ctx, sms >= 0, SWCB200_ERR_BAD_ARG, "set_sm_limit: negative count");
+    ctx->tc_sm_limit = sms;
+    return SWCB200_OK;
+}
+
 SWC_EXPORT int swcb200_set_precision(swcb200_ctx *ctx, int precision) {
     if (!ctx) return SWCB200_ERR_BAD_ARG;
     SWC_REQUIRE(ctx, precision == SWCB200_STRICT_F32 || precision == SWCB200_TC_BF16, SWCB200_ERR_BAD_ARG,

@@ -661,7 +661,7 @@ int swc_conv_tc(swcb200_ctx *ctx, void *output, int out_dtype, const void *input
         attr_set[ctx->device & 63] = true;
     }
     const size_t smem = (size_t)smem_for(p.stages, p.out_tma, p.res_tma);
-    unsigned grid = (unsigned)(p.num_tiles < ctx->sm_count ? p.num_tiles : ctx->sm_count);
+    unsigned grid = (unsigned)(p.num_tiles < swc_tc_sms(ctx) ? p.num_tiles : swc_tc_sms(ctx));
     conv_tc_kernel<<<grid, kThreads, smem, ctx->stream>>>(tmIn, tmF, tmOut, tmRes, p);
     return swc_check_launch(ctx, "conv2d_bf16");
 }

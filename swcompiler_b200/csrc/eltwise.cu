@@ -218,12 +218,53 @@ int launch_map1(swcb200_ctx *ctx, const float *in, float *out, size_t n, Op op, 
     return swc_check_launch(ctx, what);
 }
 
+// out[i] = ((s_0[i] + s_1[i]) + s_2[i]) + ... over `nslots` arrays of `n` floats lying `stride` floats apart: the join
+// of the partial sums of a model-parallel layer, always in rank order so that the result does not depend on timing.
+__global__ void __launch_bounds__(kThreads) sum_slots_kernel(const float *__restrict__ slots, size_t stride, int nslots,
+                                                             float *__restrict__ out, size_t n, bool vec) {
+    const size_t tid = (size_t)blockIdx.x * kThreads + threadIdx.x;
+    const size_t nthreads = (size_t)gridDim.x * kThreads;
+    if (vec) {
+        const size_t n4 = n >> 2;
+        for (size_t i = tid; i < n4; i += nthreads) {
+            float4 acc = ld4(slots + 4 * i);
+            for (int r = 1; r < nslots; r++) {
+                const float4 v = ld4(slots + (size_t)r * stride + 4 * i);
+                acc = make_float4(__fadd_rn(acc.x, v.x), __fadd_rn(acc.y, v.y), __fadd_rn(acc.z, v.z), __fadd_rn(acc.w, v.w));
+            }
+            st4(out + 4 * i, acc);
+        }
+        for (size_t i = (n4 << 2) + tid; i < n; i += nthreads) {
+            float acc = slots[i];
+            for (int r = 1; r < nslots; r++) acc = __fadd_rn(acc, slots[(size_t)r * stride + i]);
+            out[i] = acc;
+        }
+    } else {
+        for (size_t i = tid; i < n; i += nthreads) {
+            float acc = slots[i];
+            for (int r = 1; r < nslots; r++) acc = __fadd_rn(acc, slots[(size_t)r * stride + i]);
+            out[i] = acc;
+        }
+    }
+}
+
 }  // namespace
 
 SWC_EXPORT int swcb200_relu_f(swcb200_ctx *ctx, const float *src, float *dest, size_t size) {
     SWC_CTX(ctx);
     SWC_REQUIRE(ctx, size == 0 || (src && dest), SWCB200_ERR_BAD_ARG, "relu_f: null tensor");
     return launch_map1(ctx, src, dest, size, ReluOp(), "relu_f");
+}
+
+SWC_EXPORT int swcb200_sum_slots(swcb200_ctx *ctx, const float *slots, size_t slot_stride, int nslots, float *out, size_t count) {
+    SWC_CTX(ctx);
+    SWC_REQUIRE(ctx, nslots >= 1 && slot_stride >= count, SWCB200_ERR_BAD_ARG, "sum_slots: bad slot count or stride");
+    if (count == 0) return SWCB200_OK;
+    SWC_REQUIRE(ctx, slots && out, SWCB200_ERR_BAD_ARG, "sum_slots: null tensor");
+    const bool vec = swc_aligned16(slots) && swc_aligned16(out) && slot_stride % 4 == 0;
+    unsigned grid = swc_grid(ctx, count, (size_t)kThreads * 4, kCtasPerSm);
+    sum_slots_kernel<<<grid, kThreads, 0, ctx->stream>>>(slots, slot_stride, nslots, out, count, vec);
+    return swc_check_launch(ctx, "sum_slots");
 }
 
 SWC_EXPORT int swcb200_vecAdd_f(swcb200_ctx *ctx, int size, const float *a, const float *b, float *c) {

@@ -72,6 +72,9 @@ constexpr int BM = 128;        // UMMA M
 constexpr int BN_MAX = 256;    // UMMA N upper bound
 constexpr int BK = 64;         // one 128-byte swizzle row of bf16
 constexpr int UMMA_K = 16;     // K per tcgen05.mma for 16-bit inputs
+// scattered-rows epilogue: a 32 x 32 fp32 chunk per epilogue warp, rows 36 floats apart (16-byte aligned rows)
+constexpr int kXposePitch = 36;
+constexpr int kXposeBytes = 4 * 32 * kXposePitch * 4;
 constexpr int A_BYTES = BM * BK * 2;                 // 16 KiB
 constexpr int B_BYTES = BN_MAX * BK * 2;             // 32 KiB
 // one stage of the single-CTA kernel: A [, A_lo], Wp tile; 4 stages of 48 KiB, or 3 of 64 KiB with split activations
@@ -79,7 +82,7 @@ template <bool SPLIT> struct Single {
     static constexpr int kStages = SPLIT ? 3 : 4;
     static constexpr int A_TOTAL = SPLIT ? 2 * A_BYTES : A_BYTES;
     static constexpr int STAGE_BYTES = A_TOTAL + B_BYTES;
-    static constexpr size_t kSmemBytes = (size_t)kStages * STAGE_BYTES + 1024 /*alignment slack*/ + 256 /*barriers*/;
+    static constexpr size_t kSmemBytes = (size_t)kStages * STAGE_BYTES + 1024 /*alignment slack*/ + 256 /*barriers*/ + kXposeBytes;
 };
 constexpr int kTmemCols = 512;                       // two 256-column accumulators
 constexpr int kThreads = 192;                        // TMA warp, MMA warp, 4 epilogue warps
@@ -97,6 +100,11 @@ struct FcParams {
     int ldc;
     int c_vec;  // C base and row pitch are 16-byte aligned: 128-bit stores allowed
     void *c_lo;  // bf16 outputs only: where the rounding remainder bf16(v - bf16(v)) goes (same pitch), or null
+    // Rows scattered to their owners (fp32 output only, owners > 0): row i belongs to rank o = i / owner_rows and is
+    // written to that rank's memory, owner_base[o] + ((owner_rank * owner_rows) + i % owner_rows) * ldc -- slot
+    // `owner_rank` of the owner's slot array.  owner_base[] are peer mappings (plain stores over NVLink).
+    float *owner_base[SWCB200_MAX_PEERS];
+    int owners, owner_rows, owner_rank;
     int *status;
 };
 
@@ -174,6 +182,32 @@ __device__ __forceinline__ void store_row_chunk(const FcParams &p, const uint32_
     }
 }
 
+// Scattered rows (FcParams::owners > 0): the warp's 32 x 32 chunk goes to other GPUs' memory.  A thread holds 32
+// columns of ONE row, so storing straight from registers would send 16-byte pieces of 32 different lines per
+// instruction, which NVLink carries badly (measured: 130 GB/s).  The chunk is turned through shared memory instead and
+// leaves as whole 128-byte lines, four rows per instruction.
+__device__ __forceinline__ void store_chunk_to_owners(const FcParams &p, const uint32_t (&r)[32], int row_base, int lane, int col,
+                                                      float *sx) {
+    float4 *mine = reinterpret_cast<float4 *>(sx + lane * kXposePitch);
+#pragma unroll
+    for (int j = 0; j < 8; j++)
+        mine[j] = make_float4(__uint_as_float(r[4 * j]), __uint_as_float(r[4 * j + 1]), __uint_as_float(r[4 * j + 2]),
+                              __uint_as_float(r[4 * j + 3]));
+    __syncwarp();
+    const int sub = lane >> 3, c4 = (lane & 7) * 4;
+#pragma unroll
+    for (int r0 = 0; r0 < 32; r0 += 4) {
+        const int rr = r0 + sub, row = row_base + rr;
+        const float4 v = *reinterpret_cast<const float4 *>(sx + rr * kXposePitch + c4);
+        if (row < p.m && col + c4 < p.n) {  // n is a multiple of 4 in this mode
+            const int o = row / p.owner_rows;
+            float *dst = p.owner_base[o] + ((size_t)p.owner_rank * p.owner_rows + (size_t)(row - o * p.owner_rows)) * p.ldc + col + c4;
+            *reinterpret_cast<float4 *>(dst) = v;
+        }
+    }
+    __syncwarp();
+}
+
 template <bool SPLIT>
 __global__ void __launch_bounds__(kThreads, 1)
 fc_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmAlo,
@@ -186,6 +220,7 @@ fc_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CU
     uint64_t *tmem_full = empty + kStages;
     uint64_t *tmem_empty = tmem_full + 2;
     uint32_t *tmem_holder = reinterpret_cast<uint32_t *>(tmem_empty + 2);
+    float *s_xpose = reinterpret_cast<float *>(smem + (size_t)kStages * STAGE_BYTES + 256);
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int num_tiles = p.tiles_m * p.tiles_n;
@@ -300,6 +335,10 @@ fc_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CU
                 tmem_ld_32x32(tmem_base + ((uint32_t)(quarter * 32) << 16) + buf * BN_MAX + c0, r);
                 tmem_ld_wait();
                 const int col = col_base + c0;
+                if (p.owners > 0) {  // warp-uniform
+                    if (col < p.n) store_chunk_to_owners(p, r, tm * BM + quarter * 32, lane, col, s_xpose + (warp - 2) * 32 * kXposePitch);
+                    continue;
+                }
                 if (!row_ok || col >= p.n) continue;
                 store_row_chunk(p, r, row, col);
             }
@@ -334,7 +373,7 @@ template <bool SPLIT> struct Pair {
     static constexpr int kStages = SPLIT ? 4 : 6;
     static constexpr int A_TOTAL = SPLIT ? 2 * A_BYTES : A_BYTES;
     static constexpr int STAGE_BYTES = A_TOTAL + B2_BYTES;
-    static constexpr size_t kSmemBytes = (size_t)kStages * STAGE_BYTES + 1024 + 256;
+    static constexpr size_t kSmemBytes = (size_t)kStages * STAGE_BYTES + 1024 + 256 + kXposeBytes;
 };
 
 template <bool SPLIT>
@@ -349,6 +388,7 @@ fc_tc_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
     uint64_t *tmem_full = empty + kStages2;
     uint64_t *tmem_empty = tmem_full + 2;
     uint32_t *tmem_holder = reinterpret_cast<uint32_t *>(tmem_empty + 2);
+    float *s_xpose = reinterpret_cast<float *>(smem + (size_t)kStages2 * STAGE2_BYTES + 256);
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const uint32_t rank = cluster_ctarank();
@@ -477,6 +517,12 @@ fc_tc_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
                 tmem_ld_32x32(tmem_base + ((uint32_t)(quarter * 32) << 16) + buf * BN_MAX + c0, r);
                 tmem_ld_wait();
                 const int col = col_base + c0;
+                if (p.owners > 0) {  // warp-uniform
+                    if (col < p.n)
+                        store_chunk_to_owners(p, r, tm * (2 * BM) + (int)rank * BM + quarter * 32, lane, col,
+                                              s_xpose + (warp - 2) * 32 * kXposePitch);
+                    continue;
+                }
                 if (!row_ok || col >= p.n) continue;
                 store_row_chunk(p, r, row, col);
             }
@@ -558,7 +604,7 @@ static int launch_fc(swcb200_ctx *ctx, bool pair, const CUtensorMap &tmA, const 
             attr_pair[dev] = true;
         }
         const long long tiles2 = (long long)p.tiles_m * p.tiles_n;
-        const long long max_clusters = ctx->sm_count / 2;
+        const long long max_clusters = swc_tc_sms(ctx) / 2;
         unsigned grid2 = 2u * (unsigned)(tiles2 < max_clusters ? tiles2 : max_clusters);
         fc_tc_pair_kernel<SPLIT><<<grid2, kThreads, Pair<SPLIT>::kSmemBytes, ctx->stream>>>(tmA, tmAlo, tmB, p);
         return swc_check_launch(ctx, "fc_bf16");
@@ -569,14 +615,28 @@ static int launch_fc(swcb200_ctx *ctx, bool pair, const CUtensorMap &tmA, const 
         attr_single[dev] = true;
     }
     const long long tiles = (long long)p.tiles_m * p.tiles_n;
-    unsigned grid = (unsigned)(tiles < ctx->sm_count ? tiles : ctx->sm_count);
+    unsigned grid = (unsigned)(tiles < swc_tc_sms(ctx) ? tiles : swc_tc_sms(ctx));
     fc_tc_kernel<SPLIT><<<grid, kThreads, Single<SPLIT>::kSmemBytes, ctx->stream>>>(tmA, tmAlo, tmB, p);
     return swc_check_launch(ctx, "fc_bf16");
 }
 
+// rows of an fp32 output scattered over the ranks that own them (see FcParams); null: one local output
+struct FcOwners {
+    void *const *base;
+    int owners, owner_rows, owner_rank;
+};
+
+int swc_fc_tc_owners(swcb200_ctx *ctx, int m, int n, int k, const void *a, const void *a_lo, int lda, const void *wp, int ldw,
+                     const float *bias, int act, void *c, void *c_lo, int c_dtype, int ldc, const FcOwners *own);
+
 // a_lo / c_lo: the second term of a split activation (see the top of the file), or null
 int swc_fc_tc(swcb200_ctx *ctx, int m, int n, int k, const void *a, const void *a_lo, int lda, const void *wp, int ldw,
               const float *bias, int act, void *c, void *c_lo, int c_dtype, int ldc) {
+    return swc_fc_tc_owners(ctx, m, n, k, a, a_lo, lda, wp, ldw, bias, act, c, c_lo, c_dtype, ldc, nullptr);
+}
+
+int swc_fc_tc_owners(swcb200_ctx *ctx, int m, int n, int k, const void *a, const void *a_lo, int lda, const void *wp, int ldw,
+                     const float *bias, int act, void *c, void *c_lo, int c_dtype, int ldc, const FcOwners *own) {
     SWC_REQUIRE(ctx, swc_aligned16(a) && swc_aligned16(wp) && swc_aligned16(a_lo), SWCB200_ERR_MISALIGNED,
                 "fc_bf16: A and Wp must be 16-byte aligned");
     SWC_REQUIRE(ctx, c_lo == nullptr || c_dtype == SWCB200_BF16, SWCB200_ERR_BAD_ARG,
@@ -603,6 +663,17 @@ int swc_fc_tc(swcb200_ctx *ctx, int m, int n, int k, const void *a, const void *
     p.ldc = ldc;
     p.c_vec = swc_aligned16(c) && swc_aligned16(c_lo) && ((size_t)ldc * celem) % 16 == 0;
     p.c_lo = c_lo;
+    p.owners = 0;
+    p.owner_rows = p.owner_rank = 0;
+    if (own != nullptr) {
+        p.owners = own->owners;
+        p.owner_rows = own->owner_rows;
+        p.owner_rank = own->owner_rank;
+        for (int o = 0; o < own->owners; o++) {
+            p.owner_base[o] = (float *)own->base[o];
+            p.c_vec = p.c_vec && swc_aligned16(own->base[o]);
+        }
+    }
     p.status = ctx->dev_status;
     // CTA pairs whenever there is more than one 128-row panel and the tile is wide enough to halve
     const bool pair = m > BM && bn >= 64 && ctx->sm_count >= 2;
@@ -628,6 +699,26 @@ SWC_EXPORT int swcb200_fc_bf16(swcb200_ctx *ctx, int m, int n, int k, const void
     if (m == 0 || n == 0) return SWCB200_OK;
     SWC_REQUIRE(ctx, a_bf16 && wp_bf16 && c, SWCB200_ERR_BAD_ARG, "fc_bf16: null tensor");
     return swc_fc_tc(ctx, m, n, k, a_bf16, nullptr, lda, wp_bf16, ldw, bias, act, c, nullptr, c_dtype, ldc);
+}
+
+SWC_EXPORT int swcb200_fc_bf16_scatter_rows(swcb200_ctx *ctx, int m, int n, int k, const void *a_bf16, int lda,
+                                            const void *wp_bf16, int ldw, void *const *owner_slots, int nranks, int rank,
+                                            int ld_slot) {
+    SWC_CTX(ctx);
+    SWC_REQUIRE(ctx, m >= 0 && n >= 0 && k > 0, SWCB200_ERR_BAD_ARG, "fc_bf16_scatter_rows: bad shape %d x %d x %d", m, n, k);
+    SWC_REQUIRE(ctx, owner_slots && nranks >= 1 && nranks <= SWCB200_MAX_PEERS && rank >= 0 && rank < nranks, SWCB200_ERR_BAD_ARG,
+                "fc_bf16_scatter_rows: bad rank / count (at most %d ranks)", SWCB200_MAX_PEERS);
+    SWC_REQUIRE(ctx, m % nranks == 0 && ld_slot >= n, SWCB200_ERR_BAD_SHAPE,
+                "fc_bf16_scatter_rows: %d rows do not split over %d ranks, or the slot pitch is below n", m, nranks);
+    SWC_REQUIRE(ctx, n % 4 == 0 && ld_slot % 4 == 0, SWCB200_ERR_UNSUPPORTED,
+                "fc_bf16_scatter_rows: n (%d) and the slot pitch (%d) must be multiples of 4", n, ld_slot);
+    if (m == 0 || n == 0) return SWCB200_OK;
+    SWC_REQUIRE(ctx, a_bf16 && wp_bf16, SWCB200_ERR_BAD_ARG, "fc_bf16_scatter_rows: null tensor");
+    for (int o = 0; o < nranks; o++)
+        SWC_REQUIRE(ctx, owner_slots[o] != nullptr, SWCB200_ERR_BAD_ARG, "fc_bf16_scatter_rows: null slot pointer for rank %d", o);
+    const FcOwners own = {owner_slots, nranks, m / nranks, rank};
+    return swc_fc_tc_owners(ctx, m, n, k, a_bf16, nullptr, lda, wp_bf16, ldw, nullptr, SWCB200_ACT_NONE, owner_slots[rank], nullptr,
+                            SWCB200_F32, ld_slot, &own);
 }
 
 SWC_EXPORT int swcb200_fc_bf16_split(swcb200_ctx *ctx, int m, int n, int k, const void *a_hi, const void *a_lo, int lda,

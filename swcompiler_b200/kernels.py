@@ -84,6 +84,11 @@ class Backend:
         """Limit, in SM clock cycles, of every wait inside the tensor-core kernels launched through this context."""
         self._call("set_wait_limit", C.c_longlong(cycles))
 
+    def set_sm_limit(self, sms: int):
+        """The persistent tensor-core kernels of this context take at most `sms` SMs (0 = all): leaves room for a
+        collective of another stream to run beside them."""
+        self._call("set_sm_limit", C.c_int(sms))
+
     def selftest_wait_timeout(self):
         """Launches a kernel whose bounded wait can only run out; `sync()` then raises with status ERR_TIMEOUT."""
         self._call("selftest_wait_timeout")
@@ -265,6 +270,24 @@ class Backend:
             raise ValueError("the two terms of a split activation have the same shape")
         self._call("fc_bf16_split", C.c_int(m), C.c_int(n), C.c_int(k), _p(a), _p(a_lo), C.c_int(k), _p(wp), C.c_int(k),
                    _p(bias), C.c_int(act), _p(out), _p(out_lo), dt, C.c_int(n))
+        return out
+
+    def fc_bf16_scatter_rows(self, a, wp, slot_table, nranks: int, rank: int, ld_slot: int):
+        """A[m,k] . Wp[n,k]^T with fp32 rows scattered to the ranks that own them: row i goes into slot `rank` of the
+        slot array of rank i // (m // nranks) (`slot_table` from `NcclComm.peer_slots_setup`)."""
+        if a.dtype != torch.bfloat16 or wp.dtype != torch.bfloat16 or not (a.is_contiguous() and wp.is_contiguous()):
+            raise ValueError("fc_bf16_scatter_rows wants contiguous bf16 operands")
+        (m, k), (n, k2) = a.shape, wp.shape
+        if k != k2:
+            raise ValueError("inner dimensions differ")
+        self._call("fc_bf16_scatter_rows", C.c_int(m), C.c_int(n), C.c_int(k), _p(a), C.c_int(k), _p(wp), C.c_int(k),
+                   slot_table, C.c_int(nranks), C.c_int(rank), C.c_int(ld_slot))
+
+    def sum_slots(self, slots, out):
+        """out = slots[0] + slots[1] + ... in that order; slots [p, ...] fp32 contiguous, out one slot's shape."""
+        self._f32(slots, out)
+        n = out.numel()
+        self._call("sum_slots", _p(slots), C.c_size_t(n), C.c_int(slots.shape[0]), _p(out), C.c_size_t(n))
         return out
 
     def pack_filter_bf16(self, filt):

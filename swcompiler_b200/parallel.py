@@ -208,6 +208,16 @@ class NcclComm:
         read the result after every rank has synchronised its stream and the ranks have met at a barrier."""
         self.be._call("gather_rows", C.c_void_p(local.data_ptr()))
 
+    def peer_slots_setup(self, local_slots):
+        """Collective.  `local_slots` [p, rows/p, cols] fp32 is this rank's slot array (slot r receives rank r's partial
+        block); returns the ctypes table of every rank's array as this rank addresses it, for `Backend.fc_bf16_scatter_rows`."""
+        table = (C.c_void_p * L.MAX_PEERS)()
+        self.be._call("peer_slots_setup", C.c_void_p(local_slots.data_ptr()), table)
+        return table
+
+    def peer_slots_release(self):
+        self.be._call("peer_slots_release")
+
     def gather_rows_release(self):
         self.be._call("gather_rows_release")
 

@@ -137,10 +137,14 @@ class FcPairProgram:
         """Per rank."""
         return 2.0 * rows * self.n1s * (self.k + self.n2)
 
-    def forward(self, x_bf16: torch.Tensor, chunks: int = 1) -> torch.Tensor:
+    def forward(self, x_bf16: torch.Tensor, chunks: int = 1, comm_sms: int = 0) -> torch.Tensor:
+        """`comm_sms` > 0 (with chunks > 1): the GEMMs leave that many SMs free, on which the all-reduce of the previous
+        chunk can run at the same time (a persistent GEMM CTA fills its SM's shared memory, so a collective kernel
+        launched beside it otherwise waits for the GEMM to drain)."""
         rows = x_bf16.shape[0]
         be = self.be
         chunks = max(1, chunks)
+        be.set_sm_limit(0 if chunks == 1 or comm_sms <= 0 else self._sm_total() - comm_sms)
         step = (rows + chunks - 1) // chunks
         ms, cs = be.torch_stream, self.comm.be.torch_stream
         overlap = ms is not None and cs is not None and cs != ms
@@ -161,7 +165,57 @@ class FcPairProgram:
             done = torch.cuda.Event()
             done.record(cs)
             ms.wait_event(done)
+        be.set_sm_limit(0)
         return self.y[:rows]
+
+    def _sm_total(self) -> int:
+        return torch.cuda.get_device_properties(self.be.device).multi_processor_count
+
+    # ---- the join done by FC2's own epilogue over peer memory
+    def peer_setup(self):
+        """Collective.  Slot arrays for `forward_peer`: every rank owns max_rows / p rows of the output.  Two sets of
+        slots, used by alternate passes."""
+        import ctypes as C
+        p = self.comm.nranks
+        if self.max_rows % p:
+            raise ValueError("the rows do not split evenly over the ranks")
+        self.slots = torch.empty((2, p, self.max_rows // p, self.n2), dtype=torch.float32, device=self.be.device)
+        self.y_own = torch.empty((2, self.max_rows // p, self.n2), dtype=torch.float32, device=self.be.device)  # alternate passes
+        self.word = torch.zeros(1, dtype=torch.float32, device=self.be.device)
+        first = self.comm.peer_slots_setup(self.slots)
+        half = self.slots[0].numel() * 4
+        second = (C.c_void_p * len(first))(*[(v + half) if v else None for v in first])
+        self.slot_tables = (first, second)
+        self._peer_pass = 0
+
+    def forward_peer(self, x_bf16: torch.Tensor) -> torch.Tensor:
+        """FC1 -> ReLU -> FC2 with the partial sums joined WITHOUT a collective kernel: FC2's epilogue stores every
+        row block straight into the slot array of the rank that owns it (peer stores over NVLink, overlapped with the
+        tensor-core work), the ranks meet (a one-word all-reduce), and each rank adds the p slots of its own block in
+        rank order.  Returns this rank's block of the result, [rows / p, n2] (one of two buffers, alternating, so that
+        a copy of it may still be under way while the next pass runs); rank r owns rows [r * rows/p, (r+1) * rows/p).
+
+        Alternate passes use alternate slot sets, which is what makes one meeting point per pass enough: the FC2 that
+        overwrites a set again (two passes later) starts, on any rank, only after the meeting point of the pass in
+        between, and every rank reaches that one only after it has added up its slots of this pass."""
+        rows = x_bf16.shape[0]
+        if rows != self.max_rows:
+            raise ValueError("forward_peer works on the row count the slots were set up for")
+        be, comm = self.be, self.comm
+        ms, cs = be.torch_stream, comm.be.torch_stream
+        s = self._peer_pass & 1
+        self._peer_pass += 1
+        be.fc_bf16(x_bf16, self.wp1, None, L.ACT_RELU, out=self.h)
+        be.fc_bf16_scatter_rows(self.h, self.wp2, self.slot_tables[s], comm.nranks, comm.rank, self.n2)
+        ready = torch.cuda.Event()
+        ready.record(ms)
+        cs.wait_event(ready)
+        comm.allreduce_sum(self.word, out=self.word)   # completes once every rank's FC2, peer stores included, is done
+        met = torch.cuda.Event()
+        met.record(cs)
+        ms.wait_event(met)
+        be.sum_slots(self.slots[s], self.y_own[s])
+        return self.y_own[s]
 
 
 class ResStageProgram:

@@ -95,6 +95,8 @@ def _transform_nd(rank, world):
 
 def _fc_pair(rank, world):
     """X[512,1024] -> FC 1024->2048 (column split) -> ReLU -> FC 2048->768 (row split) -> all-reduce."""
+    import torch.distributed as dist
+
     import swcompiler_b200 as swc
     from swcompiler_b200.programs import FcPairProgram
     be, comm, par = _setup(rank, world, comm_stream=True)
@@ -114,6 +116,20 @@ def _fc_pair(rank, world):
     ref = torch.relu(x.float() @ w1).to(torch.bfloat16).float() @ w2
     assert (y - ref).abs().max().item() <= 2e-2
     assert (y2 - ref).abs().max().item() <= 2e-2
+    y3 = prog.forward(x, chunks=4, comm_sms=16)      # the GEMMs leave 16 SMs to the all-reduce of the previous chunk
+    torch.cuda.synchronize()
+    assert torch.equal(y3, y2)
+    # the join done by FC2's own epilogue over peer memory: this rank's row block, twice in a row
+    prog.peer_setup()
+    rows = 512 // world
+    for _ in range(2):
+        own = prog.forward_peer(x)
+        torch.cuda.synchronize()
+        dist.barrier()
+        mine = y[rank * rows:(rank + 1) * rows]
+        # the same p partial blocks added in rank order instead of NCCL's order: equal to rounding of an fp32 sum
+        assert (own - mine).abs().max().item() <= 1e-5 * float(mine.abs().max().item()) + 1e-6
+        assert (own - ref[rank * rows:(rank + 1) * rows]).abs().max().item() <= 2e-2
     comm.close()
 
 
