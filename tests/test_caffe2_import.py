@@ -101,7 +101,7 @@ def test_imported_programs_on_the_gpu(which, model, tol, tmp_path, oracle):
     got = parse_printed(r.stdout)
     want = c2.reference_forward(oracle, model)
     if tol == 0.0:
-        assert np.abs(got["softmax"] - want).max() <= 1e-6          # printed with limited digits
+        assert np.abs(got["softmax"] - want).max() <= 5.1e-4        # printed with three decimals
         assert got["top1"][:, 0].astype(int).tolist() == oracle.argMax_i(want, 1)[:, 0].tolist()
     else:
         assert np.abs(got["softmax"] - want).max() <= tol
