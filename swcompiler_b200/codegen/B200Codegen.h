@@ -93,6 +93,10 @@ class B200Codegen : public swc::codegen::Codegen {
         swc::Tensor *skip = nullptr;         // residual
         int act = 0;                         // 0 none, 1 relu, 2 tanh
         swc::Tensor *out = nullptr;          // the chain's last tensor
+        // A row-split FC whose partial products a Reduce node sums: the pair is printed as the peer-memory join
+        // (the GEMM's epilogue stores each row block into its owner's slots, the owners add, the master gathers).
+        swc::OpNode *join = nullptr;         // the Reduce node
+        swc::Tensor *join_out = nullptr;     // its result, on the master
     };
     void planFusion();
     bool matchFc(swc::OpNode *op, Group &g);
@@ -141,6 +145,9 @@ class B200Codegen : public swc::codegen::Codegen {
     std::map<swc::Tensor *, bool> made_f32_, made_bf16_;   // what the dry walk materialised (drives the arena plan)
     std::map<swc::Tensor *, size_t> bf16_offsets_, packed_offsets_;
     std::vector<swc::Tensor *> bf16_order_, packed_order_;
+    int join_group_ = -1;                              // the one group printed as a peer-memory join, if any
+    size_t join_rows_offset_ = 0, join_meet_offset_ = 0;
+    std::string joinSlots() { return nameOf(root(groups_[join_group_].out)); }   // the p slots: the partial-sum tensor's storage
     size_t arena_bytes_ = 0, stage_bytes_ = 0;
     std::map<swc::Tensor *, size_t> offsets_;
     std::vector<swc::Tensor *> order_;  // tensors in the order they were placed

@@ -31,7 +31,7 @@ def reference_root() -> str:
 # the sample programs: <graph>[_dp<N> | _mp<N>][_fused], see gen_driver.cpp
 PROGRAMS = ("mlp8", "convnet", "resblock", "mlp8_fused", "convnet_fused", "resblock_fused",
             "resproj", "resproj_fused", "convact", "convact_fused", "c2lenet", "c2resnet", "c2resnet_fused",
-            "mlp8_dp2", "mlp8_dp2_fused", "fcpair_mp2", "mlp8_mp2", "resblock_dp2", "mlp_eval", "mlp_eval_fused",
+            "mlp8_dp2", "mlp8_dp2_fused", "fcpair_mp2", "fcpair_mp2_fused", "mlp8_mp2", "resblock_dp2", "mlp_eval", "mlp_eval_fused",
             "mlp8_graph", "resblock_fused_graph")
 
 

@@ -256,6 +256,37 @@ class Interp:
         if self.rank == 0:
             self.t[dst] = out.numpy()
 
+    # ---- the Reduce join over peer memory: each rank's slot array holds, for the rows it owns, every rank's partial sums
+    def _sym(self, v):
+        return {"nprocs": self.nranks, "rank": self.rank}.get(v.strip(), None) if not v.strip().isdigit() else int(v)
+
+    def op_peer_slots_setup(self, local, table):
+        self.slot_tables = getattr(self, "slot_tables", {})
+        self.slot_tables[table] = local           # the table's entry for this rank is the local array; peers hold theirs
+
+    def op_fc_bf16_scatter_rows(self, m, n, k, a, lda, wp, ldw, table, nranks, rank, ld_slot):
+        import torch
+        m, n, k = int(m), int(n), int(k)
+        assert self._sym(nranks) == self.nranks and self._sym(rank) == self.rank and int(ld_slot) == n and m % self.nranks == 0
+        part = self.o.matrixMatrixMul_f(self._get(a).reshape(m, k), np.ascontiguousarray(self._get(wp).reshape(n, k).T))
+        parts = self.comm.allgather(torch.from_numpy(np.ascontiguousarray(part))).numpy().reshape(self.nranks, m, n)
+        rows = m // self.nranks
+        mine = [p[self.rank * rows:(self.rank + 1) * rows] for p in parts]   # slot r: rank r's partial sums of my rows
+        self.t[self.slot_tables[table]] = np.concatenate([b.reshape(-1) for b in mine]).astype(np.float32)
+
+    def op_allreduce_sum(self, src, dst, count, dt):
+        v = self._get(src)
+        v = np.zeros(int(count), np.float32) if v is None else v[:int(count)]
+        self.t[dst] = self.comm.allreduce_sum(self._torch(v, self._dt(dt))).numpy()
+
+    def op_sum_slots(self, slots, stride, nslots, out, count):
+        stride, count, nslots = int(stride), int(count), self._sym(nslots)
+        s = self._get(slots)
+        acc = s[:count].copy()
+        for r in range(1, nslots):                 # rank order, one rounding per addition
+            acc = (acc + s[r * stride:r * stride + count]).astype(np.float32)
+        self.t[out] = acc
+
     def op_transform(self, src, dst, dims, ndim, pre, post, dt):
         d = self.dims[dims]
         from swcompiler_b200.parallel import shard_dims

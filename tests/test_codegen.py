@@ -104,6 +104,17 @@ def test_model_parallel_fc_pair_is_column_split_row_split_and_a_reduce():
     assert "swcb200_reduce_sum(ctx, y_reduce, y, 8192, SWCB200_F32, 0)" in text
     mk = open(os.path.join(EMITTED, "fcpair_mp2_Makefile")).read()
     assert "for r in 0 1; do SWCB200_RANK=$$r SWCB200_NRANKS=2" in mk
+    # with the planner the row-split GEMM and the Reduce behind it become the join over peer memory: no reduce_sum, the
+    # partial-sum tensor serves as the p slots, and the ranks' mappings of it are made once, before the forward pass
+    calls = _calls("fcpair_mp2_fused")
+    assert "reduce_sum" not in calls and calls.index("peer_slots_setup") < calls.index("fc_bf16")
+    i = calls.index("fc_bf16_scatter_rows")
+    assert calls[i:i + 4] == ["fc_bf16_scatter_rows", "allreduce_sum", "sum_slots", "gather"] and calls[-3] == "peer_slots_release"
+    text = open(os.path.join(EMITTED, "fcpair_mp2_fused_Graph.cpp")).read()
+    assert ("swcb200_fc_bf16_scatter_rows(ctx, 64, 128, 256, hr_tile_bf16, 256, w2_tile_packed, 256, y_reduce_owner_slots, "
+            "nprocs, rank, 128)") in text
+    assert "swcb200_sum_slots(ctx, y_reduce, 4096, nprocs, y_reduce_rows, 4096)" in text
+    assert "swcb200_gather(ctx, y_reduce_rows, y, " in text
 
 
 def test_batch_split_residual_block_runs_untiled_ops_on_the_master():

@@ -87,6 +87,14 @@ def test_model_parallel_fc_pair_on_two_ranks(tmp_path, oracle):
     got = _run_ranks("fcpair_mp2", tmp_path, {"fp_x.bin": x, "fp_w1.bin": w1, "fp_w2.bin": w2}, 2)
     want = oracle.matrixMatrixMul_f(oracle.relu_f(oracle.matrixMatrixMul_f(x, w1)), w2)
     assert np.allclose(got["y"], want, atol=6e-4)   # two partial sums instead of one k-sequential sum, three decimals printed
+    # the planner's form: tensor-core GEMMs, and the Reduce done as the join over peer memory (the second GEMM's epilogue
+    # stores row blocks into their owners' slots over NVLink; owners add in rank order; the master gathers the blocks)
+    fused = _run_ranks("fcpair_mp2_fused", tmp_path, {"fp_x.bin": x, "fp_w1.bin": w1, "fp_w2.bin": w2}, 2)
+    rb = cases.bf16_round
+    part = [oracle.matrixMatrixMul_f(rb(oracle.relu_f(oracle.matrixMatrixMul_f(rb(x), rb(w1[:, c * 256:(c + 1) * 256])))),
+                                     rb(w2[c * 256:(c + 1) * 256])) for c in range(2)]
+    assert np.abs(fused["y"] - (part[0] + part[1])).max() <= 2e-3    # same rounding points; fp32 accumulation order differs
+    assert np.abs(fused["y"] - want).max() <= 2e-2
 
 
 @pytest.mark.parametrize("which", ["mlp_eval", "mlp_eval_fused"])

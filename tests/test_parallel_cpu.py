@@ -151,9 +151,24 @@ def _emitted_programs(rank, world):
         for name, arr in (("fp_x.bin", x), ("fp_w1.bin", w1), ("fp_w2.bin", w2)):
             arr.tofile(os.path.join(d, name))
         out = Interp(o, d, rank, world, comm).run(os.path.join(EMITTED, "fcpair_mp2_Graph.cpp"))
+        fused = Interp(o, d, rank, world, comm)
+        out_fused = fused.run(os.path.join(EMITTED, "fcpair_mp2_fused_Graph.cpp"))
+    # with the planner the Reduce is printed as the join over peer memory: the GEMM stores row blocks into their owners'
+    # slots, the ranks meet, each owner adds its slots in rank order and the master gathers the blocks
+    assert fused.calls.count("fc_bf16_scatter_rows") == 1 and "reduce_sum" not in fused.calls
+    i = fused.calls.index("fc_bf16_scatter_rows")
+    assert fused.calls[i:i + 4] == ["fc_bf16_scatter_rows", "allreduce_sum", "sum_slots", "gather"]
     if rank == 0:
         want = o.matrixMatrixMul_f(o.relu_f(o.matrixMatrixMul_f(x, w1)), w2)
         assert np.allclose(out["y"], want, rtol=1e-5, atol=1e-5)
+        import cases
+        rb = cases.bf16_round
+        part = [o.matrixMatrixMul_f(rb(o.relu_f(o.matrixMatrixMul_f(rb(x), rb(w1[:, c * 256:(c + 1) * 256])))),
+                                    rb(w2[c * 256:(c + 1) * 256])) for c in range(2)]
+        assert np.array_equal(out_fused["y"], part[0] + part[1])      # same rounding points, same order of the two terms
+        assert np.abs(out_fused["y"] - want).max() <= 2e-2
+    else:
+        assert out_fused == {}
     # batch-split residual block: BatchNormalization and ElementAdd carry no tiling descriptor in the reference, so its
     # passes gather their inputs to the master, run them there (printed inside `if (rank == 0)`) and scatter again
     from codegen_util import resblock_inputs, resblock_oracle
