@@ -186,6 +186,10 @@ def _conv_case(r, n, h, w, c, oc, k, pads):
     (1, 14, 14, 64, 128, (5, 5), (2, 2, 2, 2)),    # 5x5 (25 taps resident: 200 KiB > limit) -> must be refused
     (2, 10, 10, 64, 64, (3, 3), (0, 0, 0, 0)),     # no padding: output 8x8
     (1, 11, 13, 64, 64, (3, 2), (2, 0, 2, 0)),     # asymmetric window and padding
+    (2, 10, 12, 64, 64, (3, 3), (1, 1, 1, 1)),     # row-interleaved form, 10 rows: the last 4-row tile is half outside
+    (1, 6, 70, 64, 64, (3, 3), (1, 1, 1, 1)),      # row-interleaved form, two column blocks, 6 rows
+    (3, 4, 9, 64, 64, (3, 3), (1, 1, 1, 1)),       # row-interleaved form, one tile per image
+    (2, 12, 12, 64, 64, (3, 3), (2, 2, 2, 2)),     # row-interleaved form, padding 2: output 14 x 14, first input row -2
 ])
 def test_conv2d_bf16_against_oracle(be, oracle, n, h, w, c, oc, k, pads):
     r = np.random.default_rng(n * 1000 + h * 10 + oc)
