@@ -48,18 +48,21 @@
 // 62.6 us on the same run: the epilogue then reads three times the tensor memory and shuffles 128 values per thread
 // and tile, and even with its arithmetic switched off the kernel took 53.7 us (58 us for this kernel in that state).
 //
+// The 3 x 3 convolution over 64 -> 64 channels with an even number of rows -- the shape where the operand reads
+// bind hardest -- has a form of its own that halves the pixel reads of two thirds of its MMAs (row-interleaved
+// tiles, conv_rows_tcgen05.cu); swc_conv_tc tries it first.
+//
 // Restrictions: stride 1, group 1, iC a multiple of 64, oC a multiple of 32 and <= 256, kw <= 9, filter at
 // most 96 KiB in bf16, two windows fitting beside it.  Other shapes return SWCB200_ERR_UNSUPPORTED (the
 // strict kernel takes them).
 
-#include "tc_common.cuh"
+#include "conv_common.cuh"
 
 namespace {
 
 using namespace tc;
 
 constexpr int BM = 128, BK = 64;
-constexpr int ROW_PIX = 64;              // pixels per window row in shared memory (8 KiB)
 constexpr int kThreads = 384;            // window producer, two MMA issuers, residual producer, 8 epilogue warps
 constexpr int kIssuers = 2;
 constexpr int kResidualWarp = 3;
@@ -86,11 +89,6 @@ struct ConvParams {
     // a_off[g] = offset of the group's A operand inside a window, in 16-byte descriptor address units
     int groups;
     uint32_t a_off[kMaxGroups];
-    // Row-interleaved form (3 x 3 filter, 64 -> 64 channels): a tile is 4 output rows held in two accumulators, rows
-    // {0, 2} and rows {1, 3}; `stages` then counts half-windows (3 input rows of one parity each).
-    int dual;
-    int tile_rows;          // output rows of a tile: 2, or 4 in the row-interleaved form
-    int half_bytes;         // row-interleaved form: staging of one accumulator's two rows (2 x bw pixels x 128 B, 1 KiB granules)
     const float *bias;
     const float *bn_scale, *bn_bias, *bn_mean, *bn_var;
     float bn_eps;
@@ -113,23 +111,6 @@ __device__ __forceinline__ void apply_affine(const uint32_t (&acc)[32], const fl
         v[4 * j + 2] = fmaf(__uint_as_float(acc[4 * j + 2]), a.z, b.z);
         v[4 * j + 3] = fmaf(__uint_as_float(acc[4 * j + 3]), a.w, b.w);
     }
-}
-__device__ __forceinline__ void add_bf16x8(float *v, const uint4 q) {
-    const uint32_t w[4] = {q.x, q.y, q.z, q.w};
-#pragma unroll
-    for (int e = 0; e < 4; e++) {
-        v[2 * e] += __uint_as_float(w[e] << 16);
-        v[2 * e + 1] += __uint_as_float(w[e] & 0xffff0000u);
-    }
-}
-__device__ __forceinline__ uint4 pack_bf16x8(const float *v) {
-    uint4 o;
-    __nv_bfloat162 *h2 = reinterpret_cast<__nv_bfloat162 *>(&o);
-    h2[0] = __floats2bfloat162_rn(v[0], v[1]);
-    h2[1] = __floats2bfloat162_rn(v[2], v[3]);
-    h2[2] = __floats2bfloat162_rn(v[4], v[5]);
-    h2[3] = __floats2bfloat162_rn(v[6], v[7]);
-    return o;
 }
 // residual of channels [c0, c0+32) of pixel `pix`, read from global memory
 __device__ __forceinline__ void add_residual_global(const ConvParams &p, float (&v)[32], size_t pix, int c0) {
@@ -161,38 +142,6 @@ __device__ __forceinline__ void store_global(const ConvParams &p, const float (&
     }
 }
 
-// Position of a CTA's successive tiles, kept without divisions: the tile index advances by a fixed step, so
-// image / row block / column block advance by fixed amounts with one carry each.
-struct TileWalk {
-    int n, rb, cb;
-    int sn, srb, scb, row_blocks, col_blocks;
-    __device__ __forceinline__ TileWalk(long long first, long long step, int row_blocks_, int col_blocks_)
-        : row_blocks(row_blocks_), col_blocks(col_blocks_) {
-        const long long per_image = (long long)row_blocks * col_blocks;
-        n = (int)(first / per_image);
-        int r = (int)(first - (long long)n * per_image);
-        rb = r / col_blocks;
-        cb = r - rb * col_blocks;
-        sn = (int)(step / per_image);
-        r = (int)(step - (long long)sn * per_image);
-        srb = r / col_blocks;
-        scb = r - srb * col_blocks;
-    }
-    __device__ __forceinline__ void advance() {
-        cb += scb;
-        rb += srb;
-        n += sn;
-        if (cb >= col_blocks) {
-            cb -= col_blocks;
-            rb++;
-        }
-        if (rb >= row_blocks) {
-            rb -= row_blocks;
-            n++;
-        }
-    }
-};
-
 // The MMA sequence of one tile with every descriptor offset a compile-time constant: tap (kx, ky), channel chunk kc
 // and the four K = 16 steps of a 64-channel chunk.  The tensor pipe takes a new N = 64 MMA every 48 cycles and runs
 // at most about one instruction ahead of the issuing thread, so anything that thread computes between two
@@ -220,41 +169,6 @@ __device__ __forceinline__ void issue_tile_unrolled(uint32_t d_tmem, uint32_t a_
     __syncwarp();
 }
 
-// The MMAs of one half of a row-interleaved tile (3 x 3 filter, 64 -> 64 channels).  The tile's accumulators are
-// D0 = output rows {0, 2} (tensor-memory columns 0..63) and D1 = output rows {1, 3} (columns 64..127).  The window
-// rows {i, i+2} (i counted from the tile's first input row) are what D0 needs for filter row i and D1 for filter row
-// i-1, so for i = 1 and i = 2 ONE MMA with N = 128 serves both: its B operand is the two filter slices
-// [W(i, ky); W(i-1, ky)], adjacent in shared memory because the producer stores a filter column's slices in
-// descending row order.  Such an MMA reads 8 KiB of operands for 64 cycles of math where two N = 64 MMAs read 12 KiB
-// for the same work.  The rows {0, 2} and {3, 5} serve one accumulator only (N = 64).  HALF 0 is the odd half-window
-// (rows 1, 3, 5; it goes first so that one MMA starts both accumulators), HALF 1 the even one (rows 0, 2, 4).
-template <int HALF>
-__device__ __forceinline__ void issue_dual_half(uint32_t d_tmem, uint32_t a_half, uint32_t b0, uint32_t desc_hi, uint32_t idesc128,
-                                                uint32_t idesc64, bool leader) {
-    constexpr uint32_t slice = (64 * 128) >> 4;        // one [64 x 64] filter slice, in descriptor address units
-    constexpr uint32_t row = (ROW_PIX * 128) >> 4;     // one window row
-    auto desc = [desc_hi](uint32_t lo) { return ((uint64_t)desc_hi << 32) | lo; };
-    if (leader) {
-        // both accumulators: window rows {1, 3} with filter rows (1 | 0), or {2, 4} with (2 | 1)
-#pragma unroll
-        for (int ky = 0; ky < 3; ky++) {
-            const uint32_t a = a_half + (HALF == 0 ? 0u : row) + (uint32_t)ky * 8u;
-            const uint32_t b = b0 + (uint32_t)(ky * 3 + (HALF == 0 ? 1 : 0)) * slice;
-#pragma unroll
-            for (int k = 0; k < 4; k++) umma_bf16(d_tmem, desc(a + 2 * k), desc(b + 2 * k), idesc128, (uint32_t)(HALF != 0 || (ky | k) != 0));
-        }
-        // one accumulator: window rows {3, 5} with filter row 2 into D1, or {0, 2} with filter row 0 into D0
-#pragma unroll
-        for (int ky = 0; ky < 3; ky++) {
-            const uint32_t a = a_half + (HALF == 0 ? row : 0u) + (uint32_t)ky * 8u;
-            const uint32_t b = b0 + (uint32_t)(ky * 3 + (HALF == 0 ? 0 : 2)) * slice;
-#pragma unroll
-            for (int k = 0; k < 4; k++) umma_bf16(d_tmem + (HALF == 0 ? 64u : 0u), desc(a + 2 * k), desc(b + 2 * k), idesc64, 1u);
-        }
-    }
-    __syncwarp();
-}
-
 __global__ void __launch_bounds__(kThreads, 1)
 conv_tc_kernel(const __grid_constant__ CUtensorMap tmIn, const __grid_constant__ CUtensorMap tmF,
                const __grid_constant__ CUtensorMap tmOut, const __grid_constant__ CUtensorMap tmRes, const ConvParams p) {
@@ -266,16 +180,16 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap tmIn, const __grid_constant__
     // windows, then (staged epilogue) 2 x out_tile_bytes, or 1 KiB of slack where there is no staging
     uint8_t *s_out = s_a + (size_t)p.stages * p.stage_bytes + (p.out_tma ? 0 : 1024);
     uint8_t *s_res = s_out + (p.out_tma ? 2 * p.out_tile_bytes : 0);            // 2 x out_tile_bytes (TMA residual)
-    float *s_alpha = reinterpret_cast<float *>(s_res + (p.res_tma && !p.dual ? 2 * p.out_tile_bytes : 0));  // [OC]
+    float *s_alpha = reinterpret_cast<float *>(s_res + (p.res_tma ? 2 * p.out_tile_bytes : 0));  // [OC]
     float *s_beta = s_alpha + p.OC;                             // [OC]
     uint64_t *full = reinterpret_cast<uint64_t *>(s_beta + p.OC);
     uint64_t *empty = full + 8;
     uint64_t *tmem_full = empty + 8;
     uint64_t *tmem_empty = tmem_full + 4;
     uint64_t *filter_bar = tmem_empty + 4;
-    uint64_t *res_full = filter_bar + 1;   // [2]; row-interleaved form: [2 groups][2 halves] "half buffer ready"
-    uint64_t *res_empty = res_full + 4;    // [2]; row-interleaved form: [2 groups][2 halves] "half staged"
-    uint32_t *tmem_holder = reinterpret_cast<uint32_t *>(res_empty + 4);
+    uint64_t *res_full = filter_bar + 1;
+    uint64_t *res_empty = res_full + 2;
+    uint32_t *tmem_holder = reinterpret_cast<uint32_t *>(res_empty + 2);
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int taps = p.kh * p.kw;
@@ -294,7 +208,7 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap tmIn, const __grid_constant__
             mbar_init(&tmem_full[b], 1);
             mbar_init(&tmem_empty[b], 4);  // one arrival per warp of the epilogue group that reads it
         }
-        for (int b = 0; b < 4; b++) {
+        for (int b = 0; b < 2; b++) {
             mbar_init(&res_full[b], 1);   // the residual tile has landed in residual buffer b
             mbar_init(&res_empty[b], 4);  // one arrival per warp of the epilogue group that read it
         }
@@ -330,44 +244,30 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap tmIn, const __grid_constant__
             // the filter, once: one box [OC x 64] per (tap, channel chunk)
             mbar_expect_tx(filter_bar, (uint32_t)p.filter_bytes);
             for (int t = 0; t < taps; t++)
-                for (int kc = 0; kc < p.kchunks; kc++) {
-                    // row-interleaved form: the slices of a filter column in descending row order
-                    const int slot = p.dual ? (t % p.kw) * p.kh + (p.kh - 1 - t / p.kw) : t * p.kchunks + kc;
-                    tma_load_3d(s_filter + (size_t)slot * p.OC * 128, &tmF, filter_bar, kc * BK, t, 0);
-                }
+                for (int kc = 0; kc < p.kchunks; kc++)
+                    tma_load_3d(s_filter + (size_t)(t * p.kchunks + kc) * p.OC * 128, &tmF, filter_bar, kc * BK, t, 0);
         }
         __syncwarp();
         uint32_t issued = 0, ph = 0;
         int st = 0;
         TileWalk tw(blockIdx.x, gridDim.x, p.row_blocks, p.col_blocks);
         for (long long tile = blockIdx.x; tile < p.num_tiles; tile += gridDim.x, tw.advance()) {
-            const int n = tw.n, oh0 = tw.rb * p.tile_rows, ow0 = tw.cb * p.cw;
-            bool ok = true;
-            // row-interleaved form: two half-windows per tile, the odd input rows first (the image's rows are split
-            // into (row / 2, row % 2) in the tensor map, so three rows of one parity are one box)
-            for (int half = 0; half < (p.dual ? 2 : 1) && ok; half++) {
-                ok = mbar_wait(&empty[st], ph ^ 1, p.status, kWaitEmpty);
-                ok = __all_sync(0xffffffffu, ok);
-                if (!ok) break;
-                if (leader) {
-                    mbar_expect_tx(&full[st], (uint32_t)p.stage_bytes);
-                    uint8_t *dst = s_a + (size_t)st * p.stage_bytes;
-                    if (p.dual) {
-                        const int r = oh0 - p.pt + 1 - half;  // first row of the half-window; may be negative (zeros)
-                        tma_load_5d(dst, &tmIn, &full[st], 0, ow0 - p.pl, r & 1, r >> 1, n);
-                    } else {
-                        for (int kc = 0; kc < p.kchunks; kc++, dst += p.chunk_bytes)
-                            tma_load_4d(dst, &tmIn, &full[st], kc * BK, ow0 - p.pl, oh0 - p.pt, n);  // outside the image: zeros
-                    }
-                }
-                __syncwarp();
-                issued++;
-                if (++st == p.stages) {
-                    st = 0;
-                    ph ^= 1;
-                }
-            }
+            const int n = tw.n, oh0 = tw.rb * 2, ow0 = tw.cb * p.cw;
+            bool ok = mbar_wait(&empty[st], ph ^ 1, p.status, kWaitEmpty);
+            ok = __all_sync(0xffffffffu, ok);
             if (!ok) break;
+            if (leader) {
+                mbar_expect_tx(&full[st], (uint32_t)p.stage_bytes);
+                uint8_t *dst = s_a + (size_t)st * p.stage_bytes;
+                for (int kc = 0; kc < p.kchunks; kc++, dst += p.chunk_bytes)
+                    tma_load_4d(dst, &tmIn, &full[st], kc * BK, ow0 - p.pl, oh0 - p.pt, n);  // outside the image: zeros
+            }
+            __syncwarp();
+            issued++;
+            if (++st == p.stages) {
+                st = 0;
+                ph ^= 1;
+            }
         }
         // Drain: do not leave while copies may still be landing in this CTA's shared memory.  Walk back
         // over the last fill of every stage (and of both residual buffers) and wait for it to complete.
@@ -389,57 +289,13 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap tmIn, const __grid_constant__
         // ------------------------------------------------------------ residual producer (only with a bf16 residual)
         // A warp of its own, so that the input windows can run ahead of the epilogue by every free stage while the
         // residual of a tile waits for its staging buffer (the one the epilogue of two tiles back is still reading).
-        if (p.dual) {
-            // Row-interleaved form: this warp runs the output staging.  Each epilogue group has two half buffers, one
-            // per accumulator (two output rows of one parity: one box of the parity-split tensor map).  A half goes
-            // round a ring: ready (res_full) -> the group adds, applies and writes in place -> staged (res_empty) ->
-            // stored from here by TMA -> once the store has read it, the residual of the group's NEXT tile is loaded
-            // into it (or, without a residual, it is simply declared ready).  The residual of a tile is thus asked
-            // for as early as its buffer allows, half a tile sooner than with one buffer per tile.
-            if (lane == 0) {
-                const uint32_t half_tx = (uint32_t)(p.bw * 2 * 128);
-                auto make_ready = [&](int h, int n, int oh0, int ow0) {
-                    if (p.res_tma) {
-                        mbar_expect_tx(&res_full[h], half_tx);
-                        tma_load_5d(s_out + (size_t)h * p.half_bytes, &tmRes, &res_full[h], 0, ow0, h & 1, oh0 >> 1, n);
-                    } else {
-                        mbar_arrive(&res_full[h]);
-                    }
-                };
-                TileWalk tw(blockIdx.x, gridDim.x, p.row_blocks, p.col_blocks);                              // the tile being stored
-                TileWalk ahead(blockIdx.x, gridDim.x, p.row_blocks, p.col_blocks);                           // two tiles further on
-                long long tile_ahead = blockIdx.x;
-                for (int i = 0; i < 2 && tile_ahead < p.num_tiles; i++, tile_ahead += gridDim.x, ahead.advance())
-                    for (int j = 0; j < 2; j++) make_ready(2 * i + j, ahead.n, ahead.rb * 4, ahead.cb * p.cw);
-                uint32_t i = 0;
-                bool ok = true;
-                for (long long tile = blockIdx.x; tile < p.num_tiles && ok; tile += gridDim.x, tw.advance(), i++) {
-                    const int g = (int)(i & 1);
-                    for (int j = 0; j < 2 && ok; j++) {
-                        const int h = 2 * g + j;
-                        ok = mbar_wait(&res_empty[h], (i >> 1) & 1, p.status, kWaitFull);
-                        if (!ok) break;
-                        tma_store_5d(&tmOut, s_out + (size_t)h * p.half_bytes, 0, tw.cb * p.cw, j, (tw.rb * 4) >> 1, tw.n);
-                        bulk_commit_group();
-                        bulk_wait_read_all();
-                        if (tile_ahead < p.num_tiles) make_ready(h, ahead.n, ahead.rb * 4, ahead.cb * p.cw);
-                    }
-                    if (tile_ahead < p.num_tiles) {
-                        tile_ahead += gridDim.x;
-                        ahead.advance();
-                    }
-                }
-                bulk_wait_all();  // shared memory stays valid until the last store has read it
-            }
-            __syncwarp();
-        } else if (p.res_tma) {
+        if (p.res_tma) {
             const bool leader = elect_one();
-            const uint32_t res_box_bytes = (uint32_t)(p.bw * p.tile_rows * 128);
-            uint8_t *const res_buf = s_res;
+            const uint32_t res_box_bytes = (uint32_t)(p.bw * 2 * 128);
             uint32_t issued = 0;
             TileWalk tw(blockIdx.x, gridDim.x, p.row_blocks, p.col_blocks);
             for (long long tile = blockIdx.x; tile < p.num_tiles; tile += gridDim.x, tw.advance()) {
-                const int n = tw.n, oh0 = tw.rb * p.tile_rows, ow0 = tw.cb * p.cw;
+                const int n = tw.n, oh0 = tw.rb * 2, ow0 = tw.cb * p.cw;
                 const uint32_t b = issued & 1, rph = (issued >> 1) & 1;
                 bool ok = mbar_wait(&res_empty[b], rph ^ 1, p.status, kWaitEmpty);
                 ok = __all_sync(0xffffffffu, ok);
@@ -448,7 +304,7 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap tmIn, const __grid_constant__
                     // in the layout the epilogue stages its output in
                     mbar_expect_tx(&res_full[b], res_box_bytes * (uint32_t)ochunks);
                     for (int oc = 0; oc < ochunks; oc++)
-                        tma_load_4d(res_buf + (size_t)b * p.out_tile_bytes + (size_t)oc * p.out_chunk_bytes, &tmRes, &res_full[b],
+                        tma_load_4d(s_res + (size_t)b * p.out_tile_bytes + (size_t)oc * p.out_chunk_bytes, &tmRes, &res_full[b],
                                     oc * 64, ow0, oh0, n);
                 }
                 __syncwarp();
@@ -475,9 +331,8 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap tmIn, const __grid_constant__
         bool ok = mbar_wait(filter_bar, 0, p.status, kWaitFull);
         ok = __all_sync(0xffffffffu, ok);
         tc_fence_after();
-        const uint32_t idesc128 = idesc_bf16_f32(BM, 128);
-        uint32_t it = iw, ph = p.dual ? 0u : (iw / (uint32_t)p.stages) & 1;
-        int st = p.dual ? (int)(2 * iw) : (int)(iw % (uint32_t)p.stages);
+        uint32_t it = iw, ph = (iw / (uint32_t)p.stages) & 1;
+        int st = (int)(iw % (uint32_t)p.stages);
         uint32_t buf = iw % (uint32_t)p.num_acc, aph = (iw / (uint32_t)p.num_acc) & 1;
         // Descriptors differ from window to window and from tap to tap only in the 14-bit address field, the low
         // bits of the low word (no carry leaves the field: shared-memory addresses stay below 256 KiB).
@@ -494,29 +349,6 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap tmIn, const __grid_constant__
             if (!ok) break;
             tc_fence_after();
             const uint32_t d_tmem = tmem_base + buf * p.acc_stride;
-            if (p.dual) {
-                // a tile's two half-windows are the stages st and st + 1; each is handed back as soon as its MMAs are queued
-                issue_dual_half<0>(d_tmem, a_lo0 + (uint32_t)st * stage_step, b_lo0, desc_hi, idesc128, idesc, leader);
-                if (leader) umma_commit(&empty[st]);
-                __syncwarp();
-                ok = mbar_wait(&full[st + 1], ph, p.status, kWaitFull);
-                ok = __all_sync(0xffffffffu, ok);
-                if (!ok) break;
-                tc_fence_after();
-                issue_dual_half<1>(d_tmem, a_lo0 + (uint32_t)(st + 1) * stage_step, b_lo0, desc_hi, idesc128, idesc, leader);
-                if (leader) {
-                    umma_commit(&empty[st + 1]);
-                    umma_commit(&tmem_full[buf]);
-                }
-                __syncwarp();
-                ph ^= 1;  // four stages, two issuers: this warp's tiles always use the same two stages
-                buf += kIssuers;
-                if (buf >= (uint32_t)p.num_acc) {
-                    buf -= (uint32_t)p.num_acc;
-                    aph ^= 1;
-                }
-                continue;
-            }
             if (p.kh == 3 && p.kw == 3 && p.kchunks == 1) {
                 issue_tile_unrolled<3, 3, 1>(d_tmem, a_lo0 + (uint32_t)st * stage_step, b_lo0, b_step, desc_hi, idesc, leader);
             } else {
@@ -565,43 +397,42 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap tmIn, const __grid_constant__
         const int row = quarter * 32 + lane;          // row of the tile = TMEM lane
         const int trow = row >> 6, tcol = row & 63;   // position inside the 2 x 64 tile
         const int q = trow * p.bw + tcol;             // pixel's row in the staged tile (box {64 ch, bw, 2, 1})
+        const uint32_t swz = (uint32_t)(q & 7);       // 128-byte swizzle: 16-byte chunk index ^ (row & 7)
         const bool issuer = ((warp - kFirstEpilogueWarp) & 3) == 0 && lane == 0;  // issues the group's TMA stores
         const int bar_id = 1 + group;
         const uint32_t lane_base = tmem_base + ((uint32_t)(quarter * 32) << 16);
-        // staging of this group's tile; in the row-interleaved form one half buffer at a time, the residual in place
-        uint8_t *so_tile = s_out + (size_t)group * p.out_tile_bytes;
-        const uint8_t *sr_tile = s_res + (size_t)group * p.out_tile_bytes;
+        uint8_t *const so_tile = s_out + (size_t)group * p.out_tile_bytes;
+        const uint8_t *const sr_tile = s_res + (size_t)group * p.out_tile_bytes;
         uint32_t buf = (uint32_t)group % (uint32_t)p.num_acc, aph = ((uint32_t)group / (uint32_t)p.num_acc) & 1, sph = 0;
         TileWalk tw(blockIdx.x + (long long)group * gridDim.x, (long long)kEpilogueGroups * gridDim.x, p.row_blocks, p.col_blocks);
         for (long long tile = blockIdx.x + (long long)group * gridDim.x; tile < p.num_tiles;
              tile += (long long)kEpilogueGroups * gridDim.x, tw.advance()) {
-            const int n = tw.n, oh0 = tw.rb * p.tile_rows, ow0 = tw.cb * p.cw;
+            const int n = tw.n, oh0 = tw.rb * 2, ow0 = tw.cb * p.cw;
             const int oh = oh0 + trow, ow = ow0 + tcol;
             const bool valid = tcol < p.cw && oh < p.OH && ow < p.OW;
             const bool skip = p.out_tma ? tcol >= p.bw : !valid;  // staged tiles are clipped by the TMA store
             const size_t pix = ((size_t)n * p.OH + oh) * p.OW + ow;
             bool ok = true;
-            if (p.out_tma && !p.dual) {
+            if (p.out_tma) {
                 // the group's previous store must have finished reading the staging buffer before anyone refills it
                 if (issuer) bulk_wait_read_all();
                 named_barrier(bar_id, kEpilogueGroupThreads);
             }
             if (lane == 0) {
                 ok = mbar_wait(&tmem_full[buf], aph, p.status, kWaitTmemFull);
-                if (ok && p.res_tma && !p.dual) ok = mbar_wait(&res_full[group], sph, p.status, kWaitFull);
+                if (ok && p.res_tma) ok = mbar_wait(&res_full[group], sph, p.status, kWaitFull);
             }
             ok = __shfl_sync(0xffffffffu, ok, 0);
             if (!ok) break;
             tc_fence_after();
 
             // one 32-channel pass: affine, residual, ReLU, then staging (or a direct store)
-            auto pass = [&](const uint32_t (&acc)[32], int c0, int q) {  // q: the pixel's row in the staged tile
+            auto pass = [&](const uint32_t (&acc)[32], int c0) {
                 if (skip) return;
                 float v[32];
                 apply_affine(acc, s_alpha, s_beta, c0, v);
                 // this pass's 64 bytes of the pixel's 128-byte row in a staged 64-channel chunk: 16-byte chunks ch16 .. ch16+3
                 const uint32_t row_off = (uint32_t)(c0 >> 6) * p.out_chunk_bytes + (uint32_t)q * 128u;
-                const uint32_t swz = (uint32_t)(q & 7);  // 128-byte swizzle: 16-byte chunk index ^ (row & 7)
                 const uint32_t ch16 = (uint32_t)(c0 & 63) >> 3;
                 if (p.residual) {
                     if (p.res_tma) {
@@ -626,35 +457,6 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap tmIn, const __grid_constant__
                 }
             };
             const uint32_t acc_base = lane_base + buf * p.acc_stride;
-            if (p.dual) {
-                // accumulator j holds output rows {j, j + 2} of the tile, 64 channels each
-#pragma unroll 1
-                for (int j = 0; j < 2 && ok; j++) {
-                    const int h = 2 * group + j;
-                    // the half buffer is free (its previous store has left) and holds the residual, if there is one
-                    if (lane == 0) ok = mbar_wait(&res_full[h], sph, p.status, kWaitFull);
-                    ok = __shfl_sync(0xffffffffu, ok, 0);
-                    if (!ok) break;
-                    so_tile = s_out + (size_t)h * p.half_bytes;
-                    sr_tile = so_tile;
-                    uint32_t acc0[32], acc1[32];
-                    tmem_ld_32x32(acc_base + j * 64, acc0);
-                    tmem_ld_32x32(acc_base + j * 64 + 32, acc1);
-                    tmem_ld_wait();
-                    if (j == 1) {
-                        tc_fence_before();
-                        __syncwarp();
-                        if (lane == 0) mbar_arrive(&tmem_empty[buf]);
-                    }
-                    pass(acc0, 0, q);
-                    pass(acc1, 32, q);
-                    // staged: the staging warp stores it
-                    fence_proxy_async();
-                    __syncwarp();
-                    if (lane == 0) mbar_arrive(&res_empty[h]);
-                }
-                if (!ok) break;
-            } else
             for (int c0 = 0; c0 < p.OC; c0 += 64) {
                 uint32_t acc0[32], acc1[32];
                 const bool two = c0 + 32 < p.OC;  // warp-uniform
@@ -668,12 +470,12 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap tmIn, const __grid_constant__
                     __syncwarp();
                     if (lane == 0) mbar_arrive(&tmem_empty[buf]);
                 }
-                pass(acc0, c0, q);
-                if (two) pass(acc1, c0 + 32, q);
+                pass(acc0, c0);
+                if (two) pass(acc1, c0 + 32);
             }
             __syncwarp();
-            if (p.res_tma && !p.dual && lane == 0) mbar_arrive(&res_empty[group]);
-            if (p.out_tma && !p.dual) {
+            if (p.res_tma && lane == 0) mbar_arrive(&res_empty[group]);
+            if (p.out_tma) {
                 // the staged tile leaves by TMA once the whole group has written its part
                 fence_proxy_async();
                 named_barrier(bar_id, kEpilogueGroupThreads);
@@ -689,7 +491,7 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap tmIn, const __grid_constant__
             }
             sph ^= 1;
         }
-        if (p.out_tma && !p.dual && issuer) bulk_wait_all();  // shared memory stays valid until the last store has read it
+        if (p.out_tma && issuer) bulk_wait_all();  // shared memory stays valid until the last store has read it
     }
 
     __syncwarp();
@@ -704,6 +506,9 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap tmIn, const __grid_constant__
 }  // namespace
 
 // input/filter bf16; output and residual bf16 or fp32
+int swc_conv_tc_rows(swcb200_ctx *ctx, void *output, const void *input, const void *filt, const float *bias, const size_t *odims,
+                     const size_t *idims, const size_t *kernels, const size_t *pads, const swcb200_conv_epilogue *ep);
+
 int swc_conv_tc(swcb200_ctx *ctx, void *output, int out_dtype, const void *input, const void *filt, const float *bias,
                 const size_t *odims, const size_t *idims, const size_t *fdims, const size_t *kernels, const size_t *strides,
                 const size_t *pads, const swcb200_conv_epilogue *ep, int res_dtype) {
@@ -716,6 +521,15 @@ int swc_conv_tc(swcb200_ctx *ctx, void *output, int out_dtype, const void *input
     if (p.C % 64 != 0 || p.OC % 32 != 0 || p.OC > 256 || p.OC < 32)
         return swc_fail(ctx, SWCB200_ERR_UNSUPPORTED, "conv2d_bf16: needs iC %% 64 == 0 and oC in {32, 64, ..., 256}");
     if (p.kw > 9) return swc_fail(ctx, SWCB200_ERR_UNSUPPORTED, "conv2d_bf16: filter wider than 9");
+    SWC_REQUIRE(ctx, swc_aligned16(input) && swc_aligned16(filt) && swc_aligned16(output) &&
+                         (!ep || !ep->residual || swc_aligned16(ep->residual)),
+                SWCB200_ERR_MISALIGNED, "conv2d_bf16: tensors must be 16-byte aligned");
+    SWC_REQUIRE(ctx, p.OH <= p.H + 2 * p.kh && p.OW <= p.W + 2 * p.kw, SWCB200_ERR_BAD_SHAPE, "conv2d_bf16: odims too large");
+    if (out_dtype == SWCB200_BF16 && (!ep || !ep->residual || res_dtype == SWCB200_BF16)) {
+        // the row-interleaved form of the 3 x 3, 64 -> 64 channel convolution (conv_rows_tcgen05.cu)
+        const int rc = swc_conv_tc_rows(ctx, output, input, filt, bias, odims, idims, kernels, pads, ep);
+        if (rc != SWCB200_ERR_UNSUPPORTED) return rc;
+    }
     p.kchunks = p.C / 64;
     p.filter_bytes = p.kh * p.kw * p.kchunks * p.OC * 128;
     if (p.filter_bytes > kMaxFilterBytes)
@@ -726,12 +540,7 @@ int swc_conv_tc(swcb200_ctx *ctx, void *output, int out_dtype, const void *input
                 SWCB200_ERR_MISALIGNED, "conv2d_bf16: tensors must be 16-byte aligned");
     // the output a stride-1 convolution of this input can have; rows/columns beyond it would read outside the padding
     SWC_REQUIRE(ctx, p.OH <= p.H + 2 * p.kh && p.OW <= p.W + 2 * p.kw, SWCB200_ERR_BAD_SHAPE, "conv2d_bf16: odims too large");
-    // Row-interleaved form: a 3 x 3 filter over 64 -> 64 channels with a bf16 (staged) output and an image of an even
-    // number of rows, which the tensor map splits into (row / 2, row % 2).
-    const bool res_ok = !ep || !ep->residual || res_dtype == SWCB200_BF16;
-    p.dual = p.kh == 3 && p.kw == 3 && p.C == 64 && p.OC == 64 && out_dtype == SWCB200_BF16 && p.H % 2 == 0 && p.OH % 2 == 0 && p.OH >= 4 && res_ok;
-    p.tile_rows = p.dual ? 4 : 2;
-    p.acc_stride = p.dual ? 128 : (p.OC <= 64 ? 64 : (p.OC <= 128 ? 128 : 256));
+    p.acc_stride = p.OC <= 64 ? 64 : (p.OC <= 128 ? 128 : 256);
     p.num_acc = 512 / p.acc_stride < 4 ? 512 / p.acc_stride : 4;
     p.tmem_cols = p.acc_stride * p.num_acc;
     p.bias = bias;
@@ -749,16 +558,14 @@ int swc_conv_tc(swcb200_ctx *ctx, void *output, int out_dtype, const void *input
     p.status = ctx->dev_status;
 
     // shared-memory plan: filter | windows | output staging, residual staging (or 1 KiB slack) | coefficients | barriers
-    p.hr = p.dual ? 3 : p.kh + 1;  // rows of a window, or of one of the two half-windows of a row-interleaved tile
-    p.cw = p.dual ? 56 : ROW_PIX - (p.kw - 1);  // row-interleaved form: 56 columns, so that four half buffers of a tile fit
+    p.hr = p.kh + 1;
+    p.cw = ROW_PIX - (p.kw - 1);
     p.chunk_bytes = p.hr * ROW_PIX * 128;
     p.stage_bytes = p.chunk_bytes * p.kchunks;
     p.bw = p.OW < p.cw ? p.OW : p.cw;
-    p.out_chunk_bytes = (p.tile_rows * p.bw * 128 + 1023) & ~1023;  // 1 KiB granules keep every chunk on a swizzle-pattern boundary
+    p.out_chunk_bytes = (2 * p.bw * 128 + 1023) & ~1023;  // 1 KiB granules keep every chunk on a swizzle-pattern boundary
     p.out_tile_bytes = (p.OC / 64) * p.out_chunk_bytes;
-    p.half_bytes = (2 * p.bw * 128 + 1023) & ~1023;
-    if (p.dual) p.out_tile_bytes = 2 * p.half_bytes;
-    const int fixed = p.filter_bytes + 2 * p.OC * 4 + 384 + 1024;  // filter, coefficients, barriers, alignment of the base
+    const int fixed = p.filter_bytes + 2 * p.OC * 4 + 256 + 1024;  // filter, coefficients, barriers, alignment of the base
     p.out_tma = !p.out_is_f32 && p.OC % 64 == 0;
     p.res_tma = p.out_tma && p.residual != nullptr && !p.res_is_f32;
     // the 1 KiB of slack after the windows (scrap columns of the last tap read up to kw-1 pixels past them) is only
@@ -767,20 +574,14 @@ int swc_conv_tc(swcb200_ctx *ctx, void *output, int out_dtype, const void *input
         return fixed + stages * p.stage_bytes + (out_tma ? 2 * p.out_tile_bytes : 1024) + (res_tma ? 2 * p.out_tile_bytes : 0);
     };
     auto stages_for = [&](int out_tma, int res_tma) { return (kMaxSmem - smem_for(0, out_tma, res_tma)) / p.stage_bytes; };
-    if (p.dual) {
-        // four half-windows (two tiles in flight, one per issuing warp); the residual shares the output staging buffers
-        p.stages = 4;
-        SWC_REQUIRE(ctx, smem_for(4, 1, 0) <= kMaxSmem, SWCB200_ERR_UNSUPPORTED, "conv2d_bf16: shared-memory plan of the row-interleaved form");
-    } else {
-        if (stages_for(p.out_tma, p.res_tma) < 2) p.res_tma = 0;
-        if (stages_for(p.out_tma, p.res_tma) < 2) p.out_tma = 0;
-        p.stages = stages_for(p.out_tma, p.res_tma);
-    }
+    if (stages_for(p.out_tma, p.res_tma) < 2) p.res_tma = 0;
+    if (stages_for(p.out_tma, p.res_tma) < 2) p.out_tma = 0;
+    p.stages = stages_for(p.out_tma, p.res_tma);
     if (p.stages > 8) p.stages = 8;
     if (p.stages < 2)
         return swc_fail(ctx, SWCB200_ERR_UNSUPPORTED, "conv2d_bf16: two input windows (2 x %d KiB) do not fit beside the filter",
                         p.stage_bytes / 1024);
-    p.row_blocks = (p.OH + p.tile_rows - 1) / p.tile_rows;
+    p.row_blocks = (p.OH + 1) / 2;
     p.col_blocks = (p.OW + p.cw - 1) / p.cw;
     p.num_tiles = (long long)p.N * p.row_blocks * p.col_blocks;
     p.groups = p.kh * p.kw * p.kchunks;  // <= kMaxGroups: the filter fits in kMaxFilterBytes and oC >= 32
@@ -795,16 +596,7 @@ int swc_conv_tc(swcb200_ctx *ctx, void *output, int out_dtype, const void *input
         uint64_t dims[4] = {(uint64_t)p.C, (uint64_t)p.W, (uint64_t)p.H, (uint64_t)p.N};
         uint64_t str[4] = {2, (uint64_t)p.C * 2, (uint64_t)p.W * p.C * 2, (uint64_t)p.H * p.W * p.C * 2};
         uint32_t box[4] = {64, (uint32_t)ROW_PIX, (uint32_t)p.hr, 1};
-        int rc;
-        if (p.dual) {
-            // rows split by parity, {iC, W, row % 2, row / 2, N}: a box of three rows of one parity is a half-window
-            uint64_t dims5[5] = {(uint64_t)p.C, (uint64_t)p.W, 2, (uint64_t)(p.H / 2), (uint64_t)p.N};
-            uint64_t str5[5] = {2, (uint64_t)p.C * 2, (uint64_t)p.W * p.C * 2, (uint64_t)p.W * p.C * 4, (uint64_t)p.H * p.W * p.C * 2};
-            uint32_t box5[5] = {64, (uint32_t)ROW_PIX, 1, 3, 1};
-            rc = tc::make_tmap_bf16(ctx, &tmIn, input, 5, dims5, str5, box5);
-        } else {
-            rc = tc::make_tmap_bf16(ctx, &tmIn, input, 4, dims, str, box);
-        }
+        int rc = tc::make_tmap_bf16(ctx, &tmIn, input, 4, dims, str, box);
         if (rc) return rc;
     }
     {
@@ -822,14 +614,10 @@ int swc_conv_tc(swcb200_ctx *ctx, void *output, int out_dtype, const void *input
         uint64_t dims[4] = {(uint64_t)p.OC, (uint64_t)p.OW, (uint64_t)p.OH, (uint64_t)p.N};
         uint64_t str[4] = {2, (uint64_t)p.OC * 2, (uint64_t)p.OW * p.OC * 2, (uint64_t)p.OH * p.OW * p.OC * 2};
         uint32_t box[4] = {64, (uint32_t)p.bw, 2, 1};
-        // row-interleaved form: rows split by parity, one box = the two rows of one accumulator
-        uint64_t dims5[5] = {(uint64_t)p.OC, (uint64_t)p.OW, 2, (uint64_t)(p.OH / 2), (uint64_t)p.N};
-        uint64_t str5[5] = {2, (uint64_t)p.OC * 2, (uint64_t)p.OW * p.OC * 2, (uint64_t)p.OW * p.OC * 4, (uint64_t)p.OH * p.OW * p.OC * 2};
-        uint32_t box5[5] = {64, (uint32_t)p.bw, 1, 2, 1};
-        int rc = p.dual ? tc::make_tmap_bf16(ctx, &tmOut, output, 5, dims5, str5, box5) : tc::make_tmap_bf16(ctx, &tmOut, output, 4, dims, str, box);
+        int rc = tc::make_tmap_bf16(ctx, &tmOut, output, 4, dims, str, box);
         if (rc) return rc;
         if (p.res_tma) {
-            rc = p.dual ? tc::make_tmap_bf16(ctx, &tmRes, p.residual, 5, dims5, str5, box5) : tc::make_tmap_bf16(ctx, &tmRes, p.residual, 4, dims, str, box);
+            rc = tc::make_tmap_bf16(ctx, &tmRes, p.residual, 4, dims, str, box);
             if (rc) return rc;
         }
     }
@@ -838,7 +626,7 @@ int swc_conv_tc(swcb200_ctx *ctx, void *output, int out_dtype, const void *input
         SWC_CUDA(ctx, cudaFuncSetAttribute(conv_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kMaxSmem));
         attr_set[ctx->device & 63] = true;
     }
-    const size_t smem = (size_t)smem_for(p.stages, p.out_tma, p.res_tma && !p.dual);
+    const size_t smem = (size_t)smem_for(p.stages, p.out_tma, p.res_tma);
     unsigned grid = (unsigned)(p.num_tiles < swc_tc_sms(ctx) ? p.num_tiles : swc_tc_sms(ctx));
     conv_tc_kernel<<<grid, kThreads, smem, ctx->stream>>>(tmIn, tmF, tmOut, tmRes, p);
     return swc_check_launch(ctx, "conv2d_bf16");
