@@ -670,7 +670,9 @@ def run_resstage(env, args):
     world, rank, device = env.world, env.rank, env.device
     N, HW, CH, BLOCKS = 256, 56, 64, 3
     n = N // world
-    be = swc.Backend(env.local_rank, swc.TC_BF16)
+    main_stream = torch.cuda.Stream(device)  # a stream of its own: the forward pass is captured into a CUDA graph
+    torch.cuda.set_stream(main_stream)
+    be = swc.Backend(env.local_rank, swc.TC_BF16, stream=main_stream)
     g = torch.Generator(device=device).manual_seed(1005)
     convs = [dict(w=torch.randn((CH, 3, 3, CH), generator=g, device=device) * (2.0 / (9 * CH)) ** 0.5,
                   b=torch.zeros(CH, device=device)) for _ in range(2 * BLOCKS)]
@@ -690,10 +692,16 @@ def run_resstage(env, args):
         if rank == 0:
             gathered = torch.empty((N, HW // 2, HW // 2, CH), dtype=torch.bfloat16, device=device)
         comm.gather_rows_setup(gathered, n * (HW // 2) * (HW // 2) * CH * 2, root=0)
-    main_stream = torch.cuda.current_stream(device)
+    replay, pooled = prog.capture(x)
 
+    # One step: the stage's seven launches as ONE graph launch (eager only for the per-launch event timing below: at
+    # 2 GPUs and more a launch is 10-30 us long and seven calls through Python take longer than the kernels).
     def step(on_launch=None):
-        out = prog.forward(x, on_launch=on_launch)
+        if on_launch is None:
+            replay()
+            out = pooled
+        else:
+            out = prog.forward(x, on_launch=on_launch)
         if world > 1:
             ready = torch.cuda.Event()
             ready.record(main_stream)
@@ -708,15 +716,21 @@ def run_resstage(env, args):
     nl = prog.launches_per_forward
     ev = [[(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(nl)] for _ in range(steps)]
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    launches0 = be.launches
     with ClockSampler(env.local_rank) as clocks:
         env.barrier()
         e0.record()
         for s in range(steps):
-            step(on_launch=lambda i, when, s=s: ev[s][i][when].record())
+            step()
         e1.record()
         env.barrier()
-    launches = be.launches - launches0
+        # the same steps once more, launch by launch with an event on either side of each: the kernels' own durations.
+        # A spinning kernel is queued ahead of every step so that the step's launches are all enqueued by the time
+        # the first one starts; otherwise, with launches this short, an event pair would also span the host's time
+        # between two calls.
+        for s in range(steps):
+            torch.cuda._sleep(2_000_000)
+            step(on_launch=lambda i, when, s=s: ev[s][i][when].record())
+    launches = steps * nl  # kernels inside the timed region: every replay launches the captured seven
     be.sync()
     per_launch = [sum(ev[s][i][0].elapsed_time(ev[s][i][1]) for s in range(steps)) / steps for i in range(nl)]
     conv_avg = sum(per_launch[:-1]) / (nl - 1)
@@ -770,11 +784,15 @@ def run_resstage(env, args):
                          "traffic": None, "kernel": "conv_rows_kernel (3x3 64->64 + BN [+ skip] + ReLU, one launch; mean of the stage's six)",
                          "launch_ms": conv_avg, "flops_per_launch": flops,
                          "peak_source": pk["source"] + " bf16_tflops (burst: the launches are short)"},
-            "per_launch_ms": per_launch, "gather_check": check, "gpu_launches": launches, "clocks": clocks.summary()}
+            "per_launch_ms": per_launch, "gather_check": check, "gpu_launches": launches, "clocks": clocks.summary(),
+            "timing": "value: graph replays (one CUDA-graph launch per step); per_launch_ms and the roofline: the same steps "
+                      "issued call by call right after (behind a spinning kernel, so that they are queued before they run), one "
+                      "CUDA event on either side of every launch"}
     env.barrier()
     if world > 1:
         comm.close()
-    del prog, x, gathered
+    del prog, x, gathered, replay, pooled
+    torch.cuda.set_stream(torch.cuda.default_stream(device))
     torch.cuda.empty_cache()
     return rec
 
