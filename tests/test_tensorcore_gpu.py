@@ -220,6 +220,46 @@ def test_conv2d_bf16_against_oracle(be, oracle, n, h, w, c, oc, k, pads):
         assert np.all(err <= 1e-2 * np.abs(ref) + 1e-2), err.max()
 
 
+def test_conv2d_bf16_at_full_config5_size(be):
+    """The whole [256,56,56,64] layer of the ResNet-style stage (3584 four-row tiles over the persistent CTAs).
+    Sampled output pixels -- the image corners, rows on either side of every kind of tile boundary, random ones --
+    against a float64 dot product over their 3x3 patches; and two checks that cover every pixel: images are
+    independent (a permuted batch gives the permuted result, bit for bit: a tile-walk or staging-ring fault would
+    break that), and the launch with a skip tensor and ReLU agrees with relu(plain result + skip)."""
+    g = torch.Generator(device="cuda").manual_seed(55)
+    n, hw, ch = 256, 56, 64
+    x = torch.randn((n, hw, hw, ch), generator=g, device="cuda").to(torch.bfloat16)
+    f = (torch.randn((ch, 3, 3, ch), generator=g, device="cuda") * (2.0 / (9 * ch)) ** 0.5).to(torch.bfloat16).float()
+    b = torch.randn(ch, generator=g, device="cuda") * 0.1
+    fp = be.pack_filter_bf16(f)
+    k3, s1, p1 = (3, 3), (1, 1), (1, 1, 1, 1)
+    y = be.conv2d_bf16(x, fp, b, k3, s1, p1)
+    be.sync()
+    xp = torch.zeros((n, hw + 2, hw + 2, ch), dtype=torch.float64, device="cuda")
+    xp[:, 1:-1, 1:-1] = x.double()
+    r = np.random.default_rng(5)
+    pix = [(i, h, w) for i in (0, 255) for h in (0, 55) for w in (0, 55)]
+    pix += [(int(r.integers(n)), h, int(r.integers(hw))) for h in (3, 4, 5, 51, 52, 54) for _ in range(8)]
+    pix += [(int(r.integers(n)), int(r.integers(hw)), int(r.integers(hw))) for _ in range(200)]
+    fd, bd = f.double(), b.double()
+    for (i, h, w) in pix:
+        patch = xp[i, h:h + 3, w:w + 3]                                  # [3, 3, ch]
+        want = torch.einsum("okli,kli->o", fd, patch) + bd
+        got = y[i, h, w].double()
+        assert torch.all((got - want).abs() <= 1e-2 * want.abs() + 1e-2), (i, h, w)
+    perm = torch.randperm(n, generator=torch.Generator().manual_seed(3)).cuda()
+    y2 = be.conv2d_bf16(x[perm].contiguous(), fp, b, k3, s1, p1)
+    be.sync()
+    assert torch.equal(y2, y[perm])
+    # with a skip tensor and ReLU: relu(conv + skip) from the plain result, in the kernel's order of rounding
+    y3 = be.conv2d_bf16(x, fp, b, k3, s1, p1, residual=x, relu=True)
+    be.sync()
+    # the plain result was rounded to bf16 before the skip is added here, the fused one once, after the addition:
+    # half a bf16 step of the convolution's size on one side, half a step of the sum's size on the other
+    want3 = torch.relu(y.float() + x.float())
+    assert torch.all((y3.float() - want3).abs() <= 2.0 ** -8 * (y.float().abs() + want3.abs()) + 1e-6)
+
+
 def test_conv2d_f_in_tensor_core_mode(be, oracle):
     """fp32 drop-in entry point with the context in TC_BF16 mode; and a shape it cannot take falls to the strict kernel."""
     r = np.random.default_rng(8)
