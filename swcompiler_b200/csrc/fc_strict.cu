@@ -74,26 +74,49 @@ __global__ void __launch_bounds__(256) fc_strict_kernel(int m, int n, int k, con
 }
 
 // The same arithmetic for shapes whose 64 x 64 tiles would occupy only a few SMs (a batch of 64 rows, a 10-column
-// classifier): 8 x 32 output tiles, one output element per thread, 32-deep k slices.  The order of the additions
-// per element is unchanged (k ascending), so the result is the same bit for bit.
-constexpr int SM_ROWS = 8, SM_COLS = 32, SM_K = 32;
+// classifier): 8 x 32 output tiles, one output element per thread, 64-deep k slices.  The order of the additions
+// per element is unchanged (k ascending), so the result is the same bit for bit.  These shapes are bound by
+// latency -- a chain of k dependent additions per element -- so the next slice is fetched into registers while
+// the current one is being added up: the global loads never stand between two slices.
+constexpr int SM_ROWS = 8, SM_COLS = 32, SM_K = 64;
 
 __global__ void __launch_bounds__(256) fc_strict_small_kernel(int m, int n, int k, const float *__restrict__ a, int lda,
                                                               const float *__restrict__ b, int ldb, float *__restrict__ c,
                                                               int ldc) {
     __shared__ float As[SM_ROWS][SM_K];       // As[i][p]: read as a broadcast by the 32 threads of a row
     __shared__ float Bs[SM_K][SM_COLS + 1];   // Bs[p][j]
-    const int tx = threadIdx.x & 31, ty = threadIdx.x >> 5;
-    const int row = blockIdx.y * SM_ROWS + ty, col = blockIdx.x * SM_COLS + tx;
-    float acc = 0.f;
-    for (int k0 = 0; k0 < k; k0 += SM_K) {
-        As[ty][tx] = (row < m && k0 + tx < k) ? a[(size_t)row * lda + k0 + tx] : 0.f;
+    const int tid = threadIdx.x, tx = tid & 31, ty = tid >> 5;
+    const int row0 = blockIdx.y * SM_ROWS, col0 = blockIdx.x * SM_COLS;
+    const int row = row0 + ty, col = col0 + tx;
+    constexpr int A_PER = SM_ROWS * SM_K / 256, B_PER = SM_K * SM_COLS / 256;  // 2 and 8 elements per thread and slice
+    float ra[A_PER], rb[B_PER];
+    auto fetch = [&](int k0) {
 #pragma unroll
-        for (int u = 0; u < SM_K / SM_ROWS; u++) {
-            const int kk = ty + SM_ROWS * u;
-            Bs[kk][tx] = (k0 + kk < k && col < n) ? b[(size_t)(k0 + kk) * ldb + col] : 0.f;
+        for (int u = 0; u < A_PER; u++) {
+            const int idx = tid + 256 * u, r = idx / SM_K, kk = idx % SM_K;
+            ra[u] = (row0 + r < m && k0 + kk < k) ? a[(size_t)(row0 + r) * lda + k0 + kk] : 0.f;
+        }
+#pragma unroll
+        for (int u = 0; u < B_PER; u++) {
+            const int idx = tid + 256 * u, kk = idx / SM_COLS, cc = idx % SM_COLS;
+            rb[u] = (k0 + kk < k && col0 + cc < n) ? b[(size_t)(k0 + kk) * ldb + col0 + cc] : 0.f;
+        }
+    };
+    float acc = 0.f;
+    fetch(0);
+    for (int k0 = 0; k0 < k; k0 += SM_K) {
+#pragma unroll
+        for (int u = 0; u < A_PER; u++) {
+            const int idx = tid + 256 * u;
+            As[idx / SM_K][idx % SM_K] = ra[u];
+        }
+#pragma unroll
+        for (int u = 0; u < B_PER; u++) {
+            const int idx = tid + 256 * u;
+            Bs[idx / SM_COLS][idx % SM_COLS] = rb[u];
         }
         __syncthreads();
+        if (k0 + SM_K < k) fetch(k0 + SM_K);  // in flight while this slice is added up
         const int kmax = min(SM_K, k - k0);
         if (kmax == SM_K) {
 #pragma unroll
