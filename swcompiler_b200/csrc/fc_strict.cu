@@ -74,11 +74,11 @@ __global__ void __launch_bounds__(256) fc_strict_kernel(int m, int n, int k, con
 }
 
 // The same arithmetic for shapes whose 64 x 64 tiles would occupy only a few SMs (a batch of 64 rows, a 10-column
-// classifier): 8 x 32 output tiles, one output element per thread, 64-deep k slices.  The order of the additions
+// classifier): 8 x 32 output tiles, one output element per thread, 128-deep k slices.  The order of the additions
 // per element is unchanged (k ascending), so the result is the same bit for bit.  These shapes are bound by
 // latency -- a chain of k dependent additions per element -- so the next slice is fetched into registers while
 // the current one is being added up: the global loads never stand between two slices.
-constexpr int SM_ROWS = 8, SM_COLS = 32, SM_K = 64;
+constexpr int SM_ROWS = 8, SM_COLS = 32, SM_K = 128;
 
 __global__ void __launch_bounds__(256) fc_strict_small_kernel(int m, int n, int k, const float *__restrict__ a, int lda,
                                                               const float *__restrict__ b, int ldb, float *__restrict__ c,
@@ -88,7 +88,7 @@ __global__ void __launch_bounds__(256) fc_strict_small_kernel(int m, int n, int 
     const int tid = threadIdx.x, tx = tid & 31, ty = tid >> 5;
     const int row0 = blockIdx.y * SM_ROWS, col0 = blockIdx.x * SM_COLS;
     const int row = row0 + ty, col = col0 + tx;
-    constexpr int A_PER = SM_ROWS * SM_K / 256, B_PER = SM_K * SM_COLS / 256;  // 2 and 8 elements per thread and slice
+    constexpr int A_PER = SM_ROWS * SM_K / 256, B_PER = SM_K * SM_COLS / 256;  // 4 and 16 elements per thread and slice
     float ra[A_PER], rb[B_PER];
     auto fetch = [&](int k0) {
 #pragma unroll
