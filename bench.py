@@ -781,7 +781,11 @@ def run_resstage(env, args):
                        "global_batch": N, "images_per_gpu": n, "parallelism": f"dp{world} (batch split; pooled outputs gathered on rank 0)",
                        "l2": "activations (103 MB per tensor at 256 images) larger than L2 at 1 and 2 GPUs; smaller beyond"},
             "roofline": {"bound": "tensor", "achieved": achieved, "peak": pk["burst"], "unit": "TFLOP/s", "frac": achieved / pk["burst"],
-                         "traffic": None, "kernel": "conv_rows_kernel (3x3 64->64 + BN [+ skip] + ReLU, one launch; mean of the stage's six)",
+                         "traffic": 2.5 * n * HW * HW * CH * 2,
+                         "traffic_source": "operand bytes of one launch, mean of the six (input + output, and the skip tensor in every "
+                                           "second one), not measured in this run; an ncu capture of the 256-image launch without a "
+                                           "skip tensor read 103 MB and wrote 55 MB (the rest of the output was still in L2)",
+                         "kernel": "conv_rows_kernel (3x3 64->64 + BN [+ skip] + ReLU, one launch; mean of the stage's six)",
                          "launch_ms": conv_avg, "flops_per_launch": flops,
                          "peak_source": pk["source"] + " bf16_tflops (burst: the launches are short)"},
             "per_launch_ms": per_launch, "gather_check": check, "gpu_launches": launches, "clocks": clocks.summary(),

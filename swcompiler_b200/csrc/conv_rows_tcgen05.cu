@@ -140,6 +140,11 @@ conv_rows_kernel(const __grid_constant__ CUtensorMap tmIn, const __grid_constant
         mbar_init(filter_bar, 1);
         fence_barrier_init();
         fence_proxy_async();
+        // The filter is asked for at once, by the thread that has just initialised its barrier: the 72 KiB arrive
+        // while the other warps allocate tensor memory and compute the epilogue coefficients.
+        mbar_expect_tx(filter_bar, (uint32_t)kFilterBytes);
+        for (int t = 0; t < 9; t++)  // tap t = (row t / 3, column t % 3) -> slice 3 * column + (2 - row)
+            tma_load_3d(s_filter + (size_t)((t % 3) * 3 + (2 - t / 3)) * 64 * 128, &tmF, filter_bar, 0, t, 0);
     }
     if (warp == 1) {
         tmem_alloc(tmem_holder, (uint32_t)(kAccs * kAccCols));
@@ -166,12 +171,6 @@ conv_rows_kernel(const __grid_constant__ CUtensorMap tmIn, const __grid_constant
     if (warp == 0) {
         // ------------------------------------------------------------ window producer (warp-uniform loop, one elected lane issues)
         const bool leader = elect_one();
-        if (leader) {
-            mbar_expect_tx(filter_bar, (uint32_t)kFilterBytes);
-            for (int t = 0; t < 9; t++)  // tap t = (row t / 3, column t % 3) -> slice 3 * column + (2 - row)
-                tma_load_3d(s_filter + (size_t)((t % 3) * 3 + (2 - t / 3)) * 64 * 128, &tmF, filter_bar, 0, t, 0);
-        }
-        __syncwarp();
         uint32_t issued = 0, ph = 0;
         int st = 0;
         bool ok = true;
