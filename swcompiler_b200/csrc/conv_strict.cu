@@ -305,7 +305,8 @@ SWC_EXPORT int swcb200_conv2d_f(swcb200_ctx *ctx, float *output, const float *in
         const size_t smem = (size_t)K * ocp * sizeof(float);
         const unsigned total = (unsigned)(npix * g.OC);
         const bool vec = g.C % 4 == 0 && swc_aligned16(input);
-        const unsigned per_sm = smem > 100 * 1024 ? 1 : (smem > 50 * 1024 ? 2 : (smem > 24 * 1024 ? 4 : 8));
+        unsigned per_sm = (unsigned)((227 * 1024) / (smem + 1024));  // CTAs of this filter size that share an SM
+        per_sm = per_sm > 8 ? 8 : per_sm;
         const unsigned want = (total + 255) / 256, cap = (unsigned)ctx->sm_count * per_sm;
         const unsigned gx = want < cap ? want : cap;
         // the filter shapes of the small networks this path exists for get kernels with their tap loops unrolled

@@ -172,23 +172,6 @@ __device__ __forceinline__ void tma_load_2d_pair(void *smem_dst, const CUtensorM
         : "r"(smem_u32(smem_dst)), "l"(reinterpret_cast<uint64_t>(m)), "r"(bar_cluster_addr), "r"(c0), "r"(c1)
         : "memory");
 }
-__device__ __forceinline__ void tma_load_3d_pair(void *smem_dst, const CUtensorMap *m, uint32_t bar_cluster_addr, int c0,
-                                                 int c1, int c2) {
-    asm volatile(
-        "cp.async.bulk.tensor.3d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5}], [%2];"
-        :
-        : "r"(smem_u32(smem_dst)), "l"(reinterpret_cast<uint64_t>(m)), "r"(bar_cluster_addr), "r"(c0), "r"(c1), "r"(c2)
-        : "memory");
-}
-__device__ __forceinline__ void tma_load_4d_pair(void *smem_dst, const CUtensorMap *m, uint32_t bar_cluster_addr, int c0,
-                                                 int c1, int c2, int c3) {
-    asm volatile(
-        "cp.async.bulk.tensor.4d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5, %6}], [%2];"
-        :
-        : "r"(smem_u32(smem_dst)), "l"(reinterpret_cast<uint64_t>(m)), "r"(bar_cluster_addr), "r"(c0), "r"(c1), "r"(c2),
-          "r"(c3)
-        : "memory");
-}
 __device__ __forceinline__ void tmem_alloc_pair(uint32_t *smem_dst, uint32_t ncols) {  // whole warp, in both CTAs
     asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(smem_dst)), "r"(ncols)
                  : "memory");

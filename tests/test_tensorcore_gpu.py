@@ -298,3 +298,28 @@ def test_config5_stage_slice_tensor_core(be, oracle):
     rel = err.max() / np.abs(want).max()
     print(f"config5 slice: max-abs err over max-abs ref {rel:.3e}")
     assert rel <= 2e-2 and err.mean() <= 1e-2 * np.abs(want).mean() + 1e-3   # six layers of bf16 storage
+
+
+def test_res_stage_replayed_as_a_cuda_graph_equals_the_calls(oracle):
+    """ResStageProgram.capture: the stage's seven launches captured once and replayed give, bit for bit, what the same
+    calls give one by one -- also after the input buffer's contents have changed (the graph holds addresses, not data)."""
+    from swcompiler_b200.programs import ResStageProgram
+    stream = torch.cuda.Stream()
+    with torch.cuda.stream(stream):
+        be = swc.Backend(0, swc.TC_BF16, stream=stream)
+        c = cases.config5_res_stage(batch=4)
+        t = lambda a: torch.from_numpy(a).cuda()
+        prog = ResStageProgram(be, [dict(w=t(cv["w"]), b=t(cv["b"])) for cv in c["conv"]],
+                               [dict(scale=t(b["scale"]), bias=t(b["bias"]), mean=t(b["mean"]), var=t(b["var"]), eps=b["eps"])
+                                for b in c["bn"]], max_batch=4, hw=56, ch=64)
+        x = _bf16(c["x"])
+        replay, pooled = prog.capture(x)
+        for trial in range(2):
+            want = prog.forward(x).clone()
+            be.sync()
+            pooled.zero_()
+            replay()
+            stream.synchronize()
+            assert torch.equal(pooled, want)
+            x.copy_(torch.flip(x, dims=(0,)))   # other contents at the same address
+        be.sync()
