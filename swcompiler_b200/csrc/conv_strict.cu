@@ -247,6 +247,72 @@ __global__ void __launch_bounds__(256, 4) conv_strict_point_kernel(float *__rest
     }
 }
 
+// The same with TWO horizontally adjacent output pixels per thread (iC a multiple of 4): every filter word read from
+// shared memory serves both, which halves the reads that bound the kernel above once a layer has 16 or more input
+// channels (one shared-memory read per multiply-add there).  Output columns are paired inside a row: OW must be even.
+template <int CI>
+__global__ void __launch_bounds__(256, 4) conv_strict_point2_kernel(float *__restrict__ out, const float *__restrict__ in,
+                                                                 const float *__restrict__ filt, const float *__restrict__ bias,
+                                                                 ConvGeom gg, int ocp, unsigned total_pairs) {
+    extern __shared__ float fr[];  // fr[q][co], pitch ocp, q = (kx * kw + ky) * C + ci
+    ConvGeom g = gg;
+    if (CI) g.C = CI;
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int K = g.kh * g.kw * g.C;
+    for (int r = warp; r < g.OC; r += 8) {
+        const float *src = filt + (size_t)r * K;
+        for (int q = lane; q < K; q += 32) fr[q * ocp + r] = src[q];
+    }
+    __syncthreads();
+    const int row_words = g.W * g.C, tap_words = g.C * ocp, half_ow = g.OW >> 1;
+    for (unsigned idx = blockIdx.x * 256u + threadIdx.x; idx < total_pairs; idx += gridDim.x * 256u) {
+        const unsigned pp = idx / (unsigned)g.OC;          // pixel pair
+        const int co = (int)(idx - pp * (unsigned)g.OC);
+        const unsigned t = pp / (unsigned)half_ow;
+        const int ow = 2 * (int)(pp - t * (unsigned)half_ow);
+        const unsigned n = t / (unsigned)g.OH;
+        const int oh = (int)(t - n * (unsigned)g.OH);
+        const float *img = in + (size_t)n * g.H * row_words;
+        const int ih0 = oh * g.sh - g.pt, iwa = ow * g.sw - g.pl, iwb = iwa + g.sw;
+        float acc0 = bias[co], acc1 = acc0;
+        const float *fk = fr + co;
+        for (int kx = 0; kx < g.kh; kx++, fk += g.kw * tap_words) {
+            const int ih = ih0 + kx;
+            if (ih < 0 || ih >= g.H) continue;
+            const float *rowp = img + ih * row_words;
+            const float *fq = fk;
+            for (int ky = 0; ky < g.kw; ky++, fq += tap_words) {
+                const int ia = iwa + ky, ib = iwb + ky;
+                const bool oka = ia >= 0 && ia < g.W, okb = ib >= 0 && ib < g.W;
+                if (!oka && !okb) continue;
+                const float *pa = oka ? rowp + ia * g.C : in, *pb = okb ? rowp + ib * g.C : in;
+#pragma unroll
+                for (int ci = 0; ci < g.C; ci += 4) {
+                    const float4 va = __ldg(reinterpret_cast<const float4 *>(pa + ci));
+                    const float4 vb = __ldg(reinterpret_cast<const float4 *>(pb + ci));
+                    const float *f = fq + ci * ocp;
+                    const float w0 = f[0], w1 = f[ocp], w2 = f[2 * ocp], w3 = f[3 * ocp];
+                    if (oka) {
+                        acc0 = __fadd_rn(acc0, __fmul_rn(va.x, w0));
+                        acc0 = __fadd_rn(acc0, __fmul_rn(va.y, w1));
+                        acc0 = __fadd_rn(acc0, __fmul_rn(va.z, w2));
+                        acc0 = __fadd_rn(acc0, __fmul_rn(va.w, w3));
+                    }
+                    if (okb) {
+                        acc1 = __fadd_rn(acc1, __fmul_rn(vb.x, w0));
+                        acc1 = __fadd_rn(acc1, __fmul_rn(vb.y, w1));
+                        acc1 = __fadd_rn(acc1, __fmul_rn(vb.z, w2));
+                        acc1 = __fadd_rn(acc1, __fmul_rn(vb.w, w3));
+                    }
+                }
+            }
+        }
+        const size_t o = ((size_t)(t * (unsigned)g.OW) + (unsigned)ow) * (unsigned)g.OC + (unsigned)co;
+        out[o] = acc0;
+        out[o + g.OC] = acc1;
+    }
+}
+
 template <int P, bool VEC4>
 int launch_resident(swcb200_ctx *ctx, float *out, const float *in, const float *filt, const float *bias, const ConvGeom &g,
                     unsigned cap, unsigned grid_y, size_t smem) {
@@ -320,6 +386,21 @@ SWC_EXPORT int swcb200_conv2d_f(swcb200_ctx *ctx, float *output, const float *in
         }                                                                                                                      \
         conv_strict_point_kernel<VEC, KH_, KW_, CI_><<<gx, 256, smem, ctx->stream>>>(output, input, filter, bias, g, ocp, total); \
     } while (0)
+        if (vec && g.C >= 16 && g.OW % 2 == 0) {
+            // two pixels per thread: half the shared-memory reads per multiply-add
+            const unsigned pairs = total / 2, want2 = (pairs + 255) / 256, gx2 = want2 < cap ? want2 : cap;
+            static bool set2[64] = {false};
+            if (!set2[ctx->device & 63]) {
+                SWC_CUDA(ctx, cudaFuncSetAttribute(conv_strict_point2_kernel<16>, cudaFuncAttributeMaxDynamicSharedMemorySize, 100 * 1024));
+                SWC_CUDA(ctx, cudaFuncSetAttribute(conv_strict_point2_kernel<0>, cudaFuncAttributeMaxDynamicSharedMemorySize, 100 * 1024));
+                set2[ctx->device & 63] = true;
+            }
+            if (g.C == 16)
+                conv_strict_point2_kernel<16><<<gx2, 256, smem, ctx->stream>>>(output, input, filter, bias, g, ocp, pairs);
+            else
+                conv_strict_point2_kernel<0><<<gx2, 256, smem, ctx->stream>>>(output, input, filter, bias, g, ocp, pairs);
+            return swc_check_launch(ctx, "conv2d_f(strict)");
+        }
         if (g.kh == 5 && g.kw == 5 && g.C == 1) SWC_POINT(false, 5, 5, 1);
         else if (g.kh == 3 && g.kw == 3 && g.C == 1) SWC_POINT(false, 3, 3, 1);
         else if (g.C == 16 && vec) SWC_POINT(true, 0, 0, 16);
