@@ -208,8 +208,13 @@ int swcb200_pack_filter_bf16(swcb200_ctx *ctx, const float *filter, const size_t
 typedef struct swcb200_conv_epilogue {
     const float *bn_scale, *bn_bias, *bn_mean, *bn_var; /* all four or none */
     float bn_eps;
-    const void *residual; /* same shape and dtype as the output, or NULL */
+    const void *residual; /* same shape and dtype as the convolution's result, or NULL */
     int relu;
+    /* MaxPool 2x2, stride 2, no padding (maxpool_f, kernels.h:323-377) applied last, inside the same launch: the
+     * output tensor is then [N, OH/2, OW/2, oC] while odims stay the convolution's.  Only where the
+     * row-interleaved kernel runs (3x3 filter, 64 -> 64 channels, H, OH and OW even): other shapes return
+     * SWCB200_ERR_UNSUPPORTED and the caller pools with swcb200_maxpool_bf16. */
+    int pool2x2;
 } swcb200_conv_epilogue;
 /* NHWC implicit-GEMM convolution on tensor cores (replaces the chain conv2d_f -> batchnormalization_f ->
  * vecAdd_f -> relu_f, kernels.h:177-243, :496-517, :592-596, :575-580, in one launch).  input, filter

@@ -64,6 +64,8 @@ struct RowsParams {
     const float *bn_scale, *bn_bias, *bn_mean, *bn_var;
     float bn_eps;
     int has_res, relu;
+    int pool;                // the 2x2 / 2 max-pool of the result is what is stored, straight from registers
+    void *pool_out;          // [N, OH/2, OW/2, 64] bf16
     int *status;
 };
 
@@ -98,6 +100,9 @@ __device__ __forceinline__ void issue_half(uint32_t d_tmem, uint32_t a_half, uin
     __syncwarp();
 }
 
+// POOL: the 2x2 / 2 max-pool of the result is what is stored (RowsParams::pool), fixed at compile time so that the
+// plain form carries none of its registers.
+template <bool POOL>
 __global__ void __launch_bounds__(kRowsThreads, 1)
 conv_rows_kernel(const __grid_constant__ CUtensorMap tmIn, const __grid_constant__ CUtensorMap tmF,
                  const __grid_constant__ CUtensorMap tmOut, const __grid_constant__ CUtensorMap tmRes, const RowsParams p) {
@@ -256,7 +261,8 @@ conv_rows_kernel(const __grid_constant__ CUtensorMap tmIn, const __grid_constant
         // Step s = 2 * (tile number in this CTA) + accumulator uses half buffer s % 4.  After the store of step s
         // has read its buffer, the buffer is made ready for step s + 4 (same accumulator, two tiles further on):
         // with a residual by loading it (the barrier completes when it has landed), without one by a plain arrive.
-        if (lane == 0) {
+        // With the pool fused, nothing is staged for a store: a half buffer only ever carries a residual (or nothing).
+        if (lane == 0 && !(POOL && !p.has_res)) {
             const uint32_t half_tx = (uint32_t)(p.bw * 2 * 128);
             auto make_ready = [&](int h, int n, int oh0, int ow0) {
                 if (p.has_res) {
@@ -278,10 +284,12 @@ conv_rows_kernel(const __grid_constant__ CUtensorMap tmIn, const __grid_constant
                     const int h = (int)((2 * i + j) & 3);
                     ok = mbar_wait(&staged[h], (i >> 1) & 1, p.status, kWaitFull);
                     if (!ok) break;
-                    // rows {j, j + 2} of the tile: parity j, row pairs oh0 / 2 and oh0 / 2 + 1; TMA clips what lies outside
-                    tma_store_5d(&tmOut, s_out + (size_t)h * p.half_bytes, 0, tw.cb * kTileCols, j, (tw.rb * 4) >> 1, tw.n);
-                    bulk_commit_group();
-                    bulk_wait_read_all();
+                    if (!POOL) {
+                        // rows {j, j + 2} of the tile: parity j, row pairs oh0 / 2 and oh0 / 2 + 1; TMA clips what lies outside
+                        tma_store_5d(&tmOut, s_out + (size_t)h * p.half_bytes, 0, tw.cb * kTileCols, j, (tw.rb * 4) >> 1, tw.n);
+                        bulk_commit_group();
+                        bulk_wait_read_all();
+                    }
                     if (tile_ahead < p.num_tiles) make_ready(h, ahead.n, ahead.rb * 4, ahead.cb * kTileCols);
                 }
                 if (tile_ahead < p.num_tiles) {
@@ -312,17 +320,22 @@ conv_rows_kernel(const __grid_constant__ CUtensorMap tmIn, const __grid_constant
         const uint32_t lane_base = tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(16 * slice);
         uint32_t buf = 0, aph = 0, step = 0;
         bool ok = true;
-        for (long long tile = blockIdx.x; tile < p.num_tiles && ok; tile += gridDim.x) {
+        const bool use_halves = !(POOL && !p.has_res);  // half buffers carry the output, the residual, or both
+        TileWalk tw(blockIdx.x, gridDim.x, p.row_blocks, p.col_blocks);
+        for (long long tile = blockIdx.x; tile < p.num_tiles && ok; tile += gridDim.x, tw.advance()) {
             if (lane == 0) ok = mbar_wait(&tmem_full[buf], aph, p.status, kWaitTmemFull);
             ok = __shfl_sync(0xffffffffu, ok, 0);
             if (!ok) break;
             tc_fence_after();
+            float vmax[16];  // pool: the running maximum over the tile's two accumulators (rows 2r and 2r + 1)
 #pragma unroll 1
             for (int j = 0; j < 2; j++, step++) {
                 const uint32_t h = step & 3;
-                if (lane == 0) ok = mbar_wait(&half_ready[h], (step >> 2) & 1, p.status, kWaitFull);
-                ok = __shfl_sync(0xffffffffu, ok, 0);
-                if (!ok) break;
+                if (use_halves) {
+                    if (lane == 0) ok = mbar_wait(&half_ready[h], (step >> 2) & 1, p.status, kWaitFull);
+                    ok = __shfl_sync(0xffffffffu, ok, 0);
+                    if (!ok) break;
+                }
                 uint32_t acc[16];
                 tmem_ld_32x16(lane_base + buf * kAccCols + (uint32_t)(j * 64), acc);
                 tmem_ld_wait();
@@ -332,12 +345,12 @@ conv_rows_kernel(const __grid_constant__ CUtensorMap tmIn, const __grid_constant
                     __syncwarp();
                     if (lane == 0) mbar_arrive(&tmem_empty[buf]);
                 }
-                if (!skip) {
+                {
                     uint8_t *half = s_out + (size_t)h * p.half_bytes;
                     float v[16];
 #pragma unroll
                     for (int c = 0; c < 16; c++) v[c] = fmaf(__uint_as_float(acc[c]), alpha[c], beta[c]);
-                    if (p.has_res) {  // the residual is already in the buffer, in the output's layout
+                    if (p.has_res && !skip) {  // the residual is already in the buffer, in the output's layout
                         add_bf16x8(v, *reinterpret_cast<const uint4 *>(half + off0));
                         add_bf16x8(v + 8, *reinterpret_cast<const uint4 *>(half + off1));
                     }
@@ -345,13 +358,36 @@ conv_rows_kernel(const __grid_constant__ CUtensorMap tmIn, const __grid_constant
 #pragma unroll
                         for (int c = 0; c < 16; c++) v[c] = fmaxf(v[c], 0.f);
                     }
-                    *reinterpret_cast<uint4 *>(half + off0) = pack_bf16x8(v);
-                    *reinterpret_cast<uint4 *>(half + off1) = pack_bf16x8(v + 8);
+                    if (POOL) {
+#pragma unroll
+                        for (int c = 0; c < 16; c++) vmax[c] = j == 0 ? v[c] : fmaxf(vmax[c], v[c]);
+                    } else if (!skip) {
+                        *reinterpret_cast<uint4 *>(half + off0) = pack_bf16x8(v);
+                        *reinterpret_cast<uint4 *>(half + off1) = pack_bf16x8(v + 8);
+                    }
                 }
-                // staged: the staging warp stores the half once all sixteen warps have said so
-                fence_proxy_async();
-                __syncwarp();
-                if (lane == 0) mbar_arrive(&staged[h]);
+                if (use_halves) {
+                    // staged (or, with the pool fused, its residual consumed): the staging warp takes the half over
+                    // once all sixteen warps have said so
+                    fence_proxy_async();
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive(&staged[h]);
+                }
+            }
+            if (!ok) break;
+            if (POOL) {
+                // A thread holds column tcol of rows 2 * trow and 2 * trow + 1 of the tile: the vertical half of the
+                // 2 x 2 window is the maximum it already took, the horizontal half its neighbour lane's.  Rounding
+                // to bf16 is monotonic, so pooling before the rounding gives the same bits as pooling after it.
+#pragma unroll
+                for (int c = 0; c < 16; c++) vmax[c] = fmaxf(vmax[c], __shfl_xor_sync(0xffffffffu, vmax[c], 1));
+                const int oh = tw.rb * 4 + 2 * trow, ow = tw.cb * kTileCols + tcol;
+                if (!(lane & 1) && !skip && oh < p.OH && ow < p.OW) {
+                    const size_t pix = ((size_t)tw.n * (p.OH >> 1) + (oh >> 1)) * (p.OW >> 1) + (ow >> 1);
+                    uint4 *dst = reinterpret_cast<uint4 *>(reinterpret_cast<__nv_bfloat16 *>(p.pool_out) + pix * 64 + 16 * slice);
+                    dst[0] = pack_bf16x8(vmax);
+                    dst[1] = pack_bf16x8(vmax + 8);
+                }
             }
             if (++buf == (uint32_t)kAccs) {
                 buf = 0;
@@ -392,7 +428,10 @@ int swc_conv_tc_rows(swcb200_ctx *ctx, void *output, const void *input, const vo
         p.bn_eps = ep->bn_eps;
         p.has_res = ep->residual != nullptr;
         p.relu = ep->relu;
+        p.pool = ep->pool2x2 != 0;
     }
+    if (p.pool && p.OW % 2 != 0) return SWCB200_ERR_UNSUPPORTED;
+    p.pool_out = output;
     p.status = ctx->dev_status;
     const size_t smem = 1024 /*alignment of the base*/ + kFilterBytes + kSlots * kSlotBytes + kHalves * (size_t)p.half_bytes + 2 * 64 * 4 +
                         (2 * kSlots + 2 * kAccs + 2 * kHalves + 1) * 8 + 16;
@@ -430,10 +469,14 @@ int swc_conv_tc_rows(swcb200_ctx *ctx, void *output, const void *input, const vo
     }
     static bool attr_set[64] = {false};  // per device: the opt-in to large dynamic shared memory
     if (!attr_set[ctx->device & 63]) {
-        SWC_CUDA(ctx, cudaFuncSetAttribute(conv_rows_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kMaxSmem));
+        SWC_CUDA(ctx, cudaFuncSetAttribute(conv_rows_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, kMaxSmem));
+        SWC_CUDA(ctx, cudaFuncSetAttribute(conv_rows_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, kMaxSmem));
         attr_set[ctx->device & 63] = true;
     }
     unsigned grid = (unsigned)(p.num_tiles < swc_tc_sms(ctx) ? p.num_tiles : swc_tc_sms(ctx));
-    conv_rows_kernel<<<grid, kRowsThreads, smem, ctx->stream>>>(tmIn, tmF, tmOut, tmRes, p);
+    if (p.pool)
+        conv_rows_kernel<true><<<grid, kRowsThreads, smem, ctx->stream>>>(tmIn, tmF, tmOut, tmRes, p);
+    else
+        conv_rows_kernel<false><<<grid, kRowsThreads, smem, ctx->stream>>>(tmIn, tmF, tmOut, tmRes, p);
     return swc_check_launch(ctx, "conv2d_bf16");
 }

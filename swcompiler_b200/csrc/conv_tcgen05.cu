@@ -530,6 +530,9 @@ int swc_conv_tc(swcb200_ctx *ctx, void *output, int out_dtype, const void *input
         const int rc = swc_conv_tc_rows(ctx, output, input, filt, bias, odims, idims, kernels, pads, ep);
         if (rc != SWCB200_ERR_UNSUPPORTED) return rc;
     }
+    if (ep && ep->pool2x2)
+        return swc_fail(ctx, SWCB200_ERR_UNSUPPORTED,
+                        "conv2d_bf16: the fused 2x2 max-pool needs a 3x3 filter over 64 -> 64 channels, bf16 tensors and even H, OH, OW");
     p.kchunks = p.C / 64;
     p.filter_bytes = p.kh * p.kw * p.kchunks * p.OC * 128;
     if (p.filter_bytes > kMaxFilterBytes)

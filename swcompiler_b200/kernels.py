@@ -297,15 +297,18 @@ class Backend:
         self._call("pack_filter_bf16", _p(filt), _dims(filt.shape), _p(fp))
         return fp
 
-    def conv2d_bf16(self, x, fp, bias, kernels, strides, pads, bn=None, residual=None, relu=False, out=None):
-        """Conv2d [-> BatchNormalization] [-> ElementAdd(residual)] [-> Relu] in one tensor-core launch.
-        x, fp (packed filter), residual, out: bf16 NHWC.  bn = (scale, bias, mean, var, eps) or None."""
+    def conv2d_bf16(self, x, fp, bias, kernels, strides, pads, bn=None, residual=None, relu=False, out=None, pool=False):
+        """Conv2d [-> BatchNormalization] [-> ElementAdd(residual)] [-> Relu] [-> MaxPool 2x2/2] in one tensor-core
+        launch.  x, fp (packed filter), residual, out: bf16 NHWC.  bn = (scale, bias, mean, var, eps) or None.
+        With `pool` the result is [N, OH/2, OW/2, oC] (3x3 filters over 64 -> 64 channels only)."""
         odims = conv_out_dims(x.shape, fp.shape, kernels, strides, pads)
-        out = out if out is not None else self._new(odims, torch.bfloat16)
+        out_shape = (odims[0], odims[1] // 2, odims[2] // 2, odims[3]) if pool else odims
+        out = out if out is not None else self._new(out_shape, torch.bfloat16)
 
         class Ep(C.Structure):
             _fields_ = [("bn_scale", C.c_void_p), ("bn_bias", C.c_void_p), ("bn_mean", C.c_void_p),
-                        ("bn_var", C.c_void_p), ("bn_eps", C.c_float), ("residual", C.c_void_p), ("relu", C.c_int)]
+                        ("bn_var", C.c_void_p), ("bn_eps", C.c_float), ("residual", C.c_void_p), ("relu", C.c_int),
+                        ("pool2x2", C.c_int)]
 
         ep = Ep()
         if bn is not None:
@@ -313,6 +316,7 @@ class Backend:
             ep.bn_eps = float(bn[4])
         ep.residual = residual.data_ptr() if residual is not None else None
         ep.relu = 1 if relu else 0
+        ep.pool2x2 = 1 if pool else 0
         self._call("conv2d_bf16", _p(out), _p(x), _p(fp), _p(bias), _dims(odims), _dims(x.shape), _dims(fp.shape),
                    _dims(kernels), _dims(strides), _dims(pads), C.byref(ep))
         return out

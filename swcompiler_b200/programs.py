@@ -223,18 +223,22 @@ class ResStageProgram:
 
     Each Conv -> BatchNormalization [-> ElementAdd] -> Relu chain of the graph is ONE tensor-core launch (the
     batch-norm becomes a per-channel affine map in the epilogue, the skip tensor is added there too); the
-    pool is one bandwidth-bound launch.  2 * blocks + 1 launches per forward instead of 7 * blocks + 1.
+    pool is one bandwidth-bound launch, or, where the row-interleaved convolution kernel runs, part of the last
+    convolution's epilogue.  2 * blocks (+ 1) launches per forward instead of 7 * blocks + 1.
     """
 
-    def __init__(self, be: Backend, convs, bns, max_batch: int, hw: int, ch: int):
+    def __init__(self, be: Backend, convs, bns, max_batch: int, hw: int, ch: int, fuse_pool: bool | None = None):
+        """`fuse_pool`: the final MaxPool inside the last convolution's launch (default: wherever that kernel takes
+        the shape: 64 channels and an even image size)."""
         self.be = be
+        self.fuse_pool = (ch == 64 and hw % 2 == 0) if fuse_pool is None else fuse_pool
         self.fp = [be.pack_filter_bf16(c["w"]) for c in convs]
         self.cb = [c["b"].contiguous() for c in convs]
         self.bn = [(b["scale"], b["bias"], b["mean"], b["var"], float(b["eps"])) for b in bns]
         shape = (max_batch, hw, hw, ch)
         self.buf = [torch.empty(shape, dtype=torch.bfloat16, device=be.device) for _ in range(3)]
         self.pooled = torch.empty((max_batch, hw // 2, hw // 2, ch), dtype=torch.bfloat16, device=be.device)
-        self.launches_per_forward = len(self.fp) + 1
+        self.launches_per_forward = len(self.fp) + (0 if self.fuse_pool else 1)
         self.hw, self.ch = hw, ch
         be.sync()
 
@@ -265,7 +269,8 @@ class ResStageProgram:
         be, cur = self.be, x_bf16
         free = [b[:n] for b in self.buf]
         li = 0
-        for blk in range(len(self.fp) // 2):
+        blocks = len(self.fp) // 2
+        for blk in range(blocks):
             t, o = [b for b in free if b.data_ptr() != cur.data_ptr()][:2]
             if on_launch:
                 on_launch(li, 0)
@@ -273,12 +278,15 @@ class ResStageProgram:
             if on_launch:
                 on_launch(li, 1)
                 on_launch(li + 1, 0)
+            last = self.fuse_pool and blk == blocks - 1   # the stage's MaxPool rides in this launch's epilogue
             be.conv2d_bf16(t, self.fp[2 * blk + 1], self.cb[2 * blk + 1], k3, s1, p1, bn=self.bn[2 * blk + 1],
-                           residual=cur, relu=True, out=o)
+                           residual=cur, relu=True, out=self.pooled[:n] if last else o, pool=last)
             if on_launch:
                 on_launch(li + 1, 1)
             li += 2
             cur = o
+        if self.fuse_pool:
+            return self.pooled[:n]
         if on_launch:
             on_launch(li, 0)
         out = be.maxpool_bf16(cur, (2, 2), (2, 2), (0, 0, 0, 0), out=self.pooled[:n])

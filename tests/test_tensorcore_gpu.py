@@ -323,3 +323,28 @@ def test_res_stage_replayed_as_a_cuda_graph_equals_the_calls(oracle):
             assert torch.equal(pooled, want)
             x.copy_(torch.flip(x, dims=(0,)))   # other contents at the same address
         be.sync()
+
+
+@pytest.mark.parametrize("n,h,w", [(2, 56, 56), (2, 10, 12), (1, 6, 70), (3, 4, 10)])
+def test_conv2d_bf16_with_the_pool_in_its_epilogue(be, n, h, w):
+    """Conv + BN [+ skip] + ReLU + MaxPool 2x2/2 in one launch gives, bit for bit, what the convolution launch followed
+    by the bf16 max-pool launch gives (rounding to bf16 is monotonic, so pooling before or after it is the same)."""
+    r = np.random.default_rng(n * 100 + h)
+    x, f, b = _conv_case(r, n, h, w, 64, 64, (3, 3), (1, 1, 1, 1))
+    tx, tb = _bf16(x), torch.from_numpy(b).cuda()
+    fp = be.pack_filter_bf16(torch.from_numpy(f).cuda())
+    bn = [torch.from_numpy(v).cuda() for v in (r.uniform(0.5, 1.5, 64).astype(np.float32), (r.standard_normal(64) * 0.1).astype(np.float32),
+                                               (r.standard_normal(64) * 0.1).astype(np.float32), r.uniform(0.5, 1.5, 64).astype(np.float32))] + [1e-5]
+    k3, s1, p1 = (3, 3), (1, 1), (1, 1, 1, 1)
+    for res in (None, tx):
+        full = be.conv2d_bf16(tx, fp, tb, k3, s1, p1, bn=bn, residual=res, relu=True)
+        want = be.maxpool_bf16(full, (2, 2), (2, 2), (0, 0, 0, 0))
+        got = be.conv2d_bf16(tx, fp, tb, k3, s1, p1, bn=bn, residual=res, relu=True, pool=True)
+        be.sync()
+        assert got.shape == want.shape == (n, h // 2, w // 2, 64)
+        assert torch.equal(got, want)
+    # a shape the row-interleaved kernel does not take: refused, not silently left unpooled
+    x5 = _bf16(r.standard_normal((1, 5, 8, 64)).astype(np.float32))
+    with pytest.raises(swc.SwcError) as e:
+        be.conv2d_bf16(x5, fp, tb, k3, s1, p1, pool=True)
+    assert e.value.status == swc._lib.ERR_UNSUPPORTED
