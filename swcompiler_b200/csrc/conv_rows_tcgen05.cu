@@ -381,12 +381,14 @@ conv_rows_kernel(const __grid_constant__ CUtensorMap tmIn, const __grid_constant
                 // to bf16 is monotonic, so pooling before the rounding gives the same bits as pooling after it.
 #pragma unroll
                 for (int c = 0; c < 16; c++) vmax[c] = fmaxf(vmax[c], __shfl_xor_sync(0xffffffffu, vmax[c], 1));
-                const int oh = tw.rb * 4 + 2 * trow, ow = tw.cb * kTileCols + tcol;
-                if (!(lane & 1) && !skip && oh < p.OH && ow < p.OW) {
+                // both lanes of a pair now hold the window's maximum: the even one stores channels 0..7 of the slice,
+                // the odd one channels 8..15, so that a pair writes one whole 32-byte sector
+                const int oh = tw.rb * 4 + 2 * trow, pcol = tcol & ~1, ow = tw.cb * kTileCols + pcol;
+                if (pcol < p.bw && oh < p.OH && ow < p.OW) {
                     const size_t pix = ((size_t)tw.n * (p.OH >> 1) + (oh >> 1)) * (p.OW >> 1) + (ow >> 1);
                     uint4 *dst = reinterpret_cast<uint4 *>(reinterpret_cast<__nv_bfloat16 *>(p.pool_out) + pix * 64 + 16 * slice);
-                    dst[0] = pack_bf16x8(vmax);
-                    dst[1] = pack_bf16x8(vmax + 8);
+                    const uint4 lo = pack_bf16x8(vmax), hi = pack_bf16x8(vmax + 8);
+                    dst[lane & 1] = (lane & 1) ? hi : lo;
                 }
             }
             if (++buf == (uint32_t)kAccs) {
