@@ -26,10 +26,27 @@ def _peaks():
         return 6650.0, 1590.0, "fallback"
 
 
-def _time(fn, iters):
+def _time(fn, iters, rest=0.0):
+    """`rest` seconds of idle time first: a tensor-bound kernel is to be measured as a burst, on its own, not at the
+    clocks the power limit has settled on after the kernels measured before it."""
+    if rest:
+        import time
+        torch.cuda.synchronize()
+        time.sleep(rest)
     for _ in range(3):
         fn()
     torch.cuda.synchronize()
+    if rest:
+        # after a rest the clocks take a few milliseconds of work to come back up: short kernels get more warm-up
+        # launches (about 3 ms worth, 20 at most), long ones none beyond the three above
+        import time
+        t0 = time.perf_counter()
+        fn()
+        torch.cuda.synchronize()
+        dt = max(time.perf_counter() - t0, 1e-6)
+        for _ in range(min(20, int(3e-3 / dt))):
+            fn()
+        torch.cuda.synchronize()
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     e0.record()
     for _ in range(iters):
@@ -176,7 +193,7 @@ def op_rows(iters=20, only=None):
         wp = (torch.randn((n, k), generator=g, device=dev) / k ** 0.5).to(torch.bfloat16)
         b = torch.randn(n, generator=g, device=dev)
         o = torch.empty((m, n), device=dev, dtype=torch.bfloat16)
-        t = _time(lambda: be.fc_bf16(a, wp, b, swc.ACT_RELU, out=o), iters)
+        t = _time(lambda: be.fc_bf16(a, wp, b, swc.ACT_RELU, out=o), iters, rest=1.0)
         fl = 2.0 * m * n * k
         rows.append(({"kernel": name, "bound": "tensor", "us": t * 1e6, "achieved": fl / t / 1e12, "unit": "TFLOP/s",
                           "peak": tflops, "frac": fl / t / 1e12 / tflops, "peak_source": src + " (burst)", "flops": fl}))
@@ -201,11 +218,11 @@ def op_rows(iters=20, only=None):
              lambda: be.conv2d_bf16(xin, prog.fp[1], prog.cb[1], (3, 3), (1, 1), (1, 1, 1, 1), bn=prog.bn[1], residual=xin,
                                     relu=True, out=o)),
         ]:
-            t = _time(fn, iters)
+            t = _time(fn, iters, rest=1.5)
             rows.append(({"kernel": name, "bound": "tensor", "us": t * 1e6, "achieved": fl / t / 1e12, "unit": "TFLOP/s",
                               "peak": tflops, "frac": fl / t / 1e12 / tflops, "peak_source": src + " (burst)", "flops": fl,
                               "hbm_GBps": (2 * xin.numel() * 2) / t / 1e9}))
-        t = _time(lambda: prog.forward(xin), iters)
+        t = _time(lambda: prog.forward(xin), iters, rest=1.5)
         rows.append(({"kernel": "res stage forward (config 5): 6 fused convs + maxpool, batch 256", "bound": "tensor",
                           "us": t * 1e6, "achieved": prog.flops(n) / t / 1e12, "unit": "TFLOP/s", "peak": tflops,
                           "frac": prog.flops(n) / t / 1e12 / tflops, "peak_source": src + " (burst)",
