@@ -788,7 +788,9 @@ def run_resstage(env, args):
                                            "skip tensor read 103 MB and wrote 55 MB (the rest of the output was still in L2)",
                          "kernel": "conv_rows_kernel (3x3 64->64 + BN [+ skip] + ReLU, one launch; mean of the stage's six)",
                          "launch_ms": conv_avg, "flops_per_launch": flops,
-                         "peak_source": pk["source"] + " bf16_tflops (burst: the launches are short)"},
+                         "frac_of_sustained": achieved / pk["sustained"],
+                         "peak_source": pk["source"] + " bf16_tflops (burst: the launches are short; frac_of_sustained is the "
+                                        "same against bf16_tflops_sustained, the clocks these back-to-back steps run at)"},
             "per_launch_ms": per_launch, "gather_check": check, "gpu_launches": launches, "clocks": clocks.summary(),
             "timing": "value: graph replays (one CUDA-graph launch per step); per_launch_ms and the roofline: the same steps "
                       "issued call by call right after (behind a spinning kernel, so that they are queued before they run), one "
