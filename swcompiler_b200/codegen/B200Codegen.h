@@ -95,6 +95,10 @@ class B200Codegen : public swc::codegen::Codegen {
         swc::Tensor *out = nullptr;          // the chain's last tensor
         // A row-split FC whose partial products a Reduce node sums: the pair is printed as the peer-memory join
         // (the GEMM's epilogue stores each row block into its owner's slots, the owners add, the master gathers).
+        // Conv chain followed by MaxPool 2x2 / 2 where the row-interleaved convolution kernel runs: the pool is the
+        // last step of the fused call's epilogue.
+        swc::OpNode *pool = nullptr;         // the MaxPool node
+        swc::Tensor *conv_out = nullptr;     // the convolution's own (un-pooled) result: its dims go into the call
         swc::OpNode *join = nullptr;         // the Reduce node
         swc::Tensor *join_out = nullptr;     // its result, on the master
     };

@@ -212,7 +212,9 @@ class Interp:
     def op_conv2d_bf16(self, out, x, fp, b, od, idm, fd, kd, sd, pd, ep):
         y = self.o.conv2d_f(self._get(x).reshape(self.dims[idm]), self._get(fp).reshape(self.dims[fd]), self._get(b),
                             self.dims[kd], self.dims[sd], self.dims[pd])
-        scale, bias, mean, var, eps, res, relu = self.epi[ep.lstrip("&")]
+        fields = self.epi[ep.lstrip("&")]
+        scale, bias, mean, var, eps, res, relu = fields[:7]
+        pool = len(fields) > 7 and int(fields[7])
         if scale != "nullptr":
             y = self.o.batchnormalization_f(y, self._get(mean), self._get(var), self._get(scale), self._get(bias),
                                             float(eps.rstrip("f")))
@@ -221,6 +223,10 @@ class Interp:
         if int(relu):
             y = np.maximum(y, 0)
         assert y.shape == self.dims[od]
+        if pool:   # MaxPool 2x2 / 2 as the epilogue's last step
+            n, h, w, c = y.shape
+            y = self.o.maxpool_f(np.ascontiguousarray(y.astype(np.float32)), (2, 2), (2, 2), (0, 0, 0, 0))
+            assert y.shape == (n, h // 2, w // 2, c)
         self.t[out] = cases.bf16_round(y.astype(np.float32)).reshape(-1)
 
     def op_maxpool_bf16(self, x, out, idm, od, kd, sd, pd):

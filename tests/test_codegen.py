@@ -43,15 +43,18 @@ def test_fused_mlp8_is_two_fused_calls_with_bf16_between_them():
     assert "swcb200_init(0, SWCB200_TC_BF16" in text
 
 
-def test_fused_resblock_is_five_calls():
-    """Conv -> BN -> ReLU and Conv -> BN -> Add(skip) -> ReLU are one swcb200_conv2d_bf16 each, the pool runs on bf16
-    storage, the FC reads the pooled bf16 tensor through the Reshape view: 15 op nodes, 5 calls and one input cast."""
+def test_fused_resblock_is_four_calls():
+    """Conv -> BN -> ReLU is one swcb200_conv2d_bf16, Conv -> BN -> Add(skip) -> ReLU -> MaxPool 2x2/2 another (the
+    pool is the last step of its epilogue: 3x3 filter, 64 -> 64 channels, even sizes), the FC reads the pooled bf16
+    tensor through the Reshape view: 15 op nodes, 4 calls and one input cast."""
     assert _calls("resblock_fused") == ["init", "pack_filter_bf16", "pack_filter_bf16", "pack_weight_bf16", "cast_f32_to_bf16",
-                                        "conv2d_bf16", "conv2d_bf16", "maxpool_bf16", "fc_bf16", "matrixSoftmax_f", "argMax_i",
+                                        "conv2d_bf16", "conv2d_bf16", "fc_bf16", "matrixSoftmax_f", "argMax_i",
                                         "sync", "destroy"]
     text = open(os.path.join(EMITTED, "resblock_fused_Graph.cpp")).read()
     assert "{bn0_scale, bn0_bias, bn0_mean, bn0_var, 1e-05f, nullptr, 1}" in text
-    assert "{bn1_scale, bn1_bias, bn1_mean, bn1_var, 1e-05f, image_bf16, 1}" in text   # the skip tensor, in bf16
+    assert "{bn1_scale, bn1_bias, bn1_mean, bn1_var, 1e-05f, image_bf16, 1, 1}" in text   # the skip tensor in bf16; relu; pool2x2
+    assert "relu1_out" not in text                                                        # the un-pooled result is never stored
+    assert "swcb200_conv2d_bf16(ctx, pool_out_bf16, relu0_out_bf16" in text and "conv1_odims_9[] = {2, 8, 8, 64}" in text
     assert "pool_out_bf16, 1024, fc_w_packed" in text
     offs = [int(l.split("gpu_arena + ")[1].split(")")[0]) for l in text.splitlines() if "gpu_arena + " in l]
     assert offs and all(o % 256 == 0 for o in offs)
@@ -229,7 +232,7 @@ def test_projection_shortcut_block_and_conv_with_activation(oracle, tmp_path):
     assert calls.count("conv2d_bf16") == 3 and "vecAdd_f" not in calls and "relu_f" not in calls
     text = open(os.path.join(EMITTED, "resproj_fused_Graph.cpp")).read()
     assert "{bnS_scale, bnS_bias, bnS_mean, bnS_var, 1e-05f, nullptr, 0}" in text             # shortcut: conv + bn only
-    assert "{bn1_scale, bn1_bias, bn1_mean, bn1_var, 1e-05f, bnS_out_bf16, 1}" in text        # main branch takes add + relu
+    assert "{bn1_scale, bn1_bias, bn1_mean, bn1_var, 1e-05f, bnS_out_bf16, 1, 1}" in text     # main branch takes add + relu (+ pool)
     assert text.index("convS_epilogue") < text.index("conv1_epilogue")                         # the skip exists by then
     t = resproj_inputs()
     assert np.array_equal(bits(_interpret("resproj", t, oracle, tmp_path)["probs"]), bits(resproj_oracle(oracle, t)))
