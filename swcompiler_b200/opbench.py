@@ -62,6 +62,9 @@ def latency_rows(iters=50):
     Conv5x5 16->32 -> ReLU -> MaxPool -> FC 1568->10 -> Softmax.  One table call per op node, strict fp32 kernels and
     the tensor-core mode of the same entry points; microseconds per forward pass and samples per second, launched call
     by call and replayed as a CUDA graph (the form the generator prints with graph_replays)."""
+    import time
+    torch.cuda.synchronize()
+    time.sleep(2.0)   # not at the clocks a power-limited workload measured just before has left behind
     dev = torch.device("cuda", torch.cuda.current_device())
     g = torch.Generator(device=dev).manual_seed(1001)
     rn = lambda *shape, s=1.0: torch.randn(shape, generator=g, device=dev) * s
@@ -90,13 +93,13 @@ def latency_rows(iters=50):
                 n0 = be.launches
                 fn()
                 per_forward = be.launches - n0
-                t = _time(fn, iters)
+                t = _time(fn, iters, rest=0.3)
                 # the same calls captured once and replayed: what remains is the kernels' own time
                 stream.synchronize()
                 graph = torch.cuda.CUDAGraph()
                 with torch.cuda.graph(graph, stream=stream):
                     fn()
-                tg = _time(graph.replay, iters)
+                tg = _time(graph.replay, iters, rest=0.3)
                 rows.append({"config": label, "mode": name, "us_per_forward": t * 1e6, "samples_per_s": batch / t,
                              "graph_us_per_forward": tg * 1e6, "graph_samples_per_s": batch / tg,
                              "launches_per_forward": per_forward})
